@@ -1,0 +1,337 @@
+/*
+ * b200moe.h - C ABI of the B200 (sm_100a) block-quantized MoE FFN path.
+ *
+ * The path: router top-k -> dequant-fused expert gate/up projection with SwiGLU and A8 re-quantisation -> down
+ * projection -> weighted combine, on GGUF Q8_0 / Q4_K expert tensors kept in their stored byte layout.
+ *
+ * Conventions (the reference CUDA operator layer's, include/strix/cuda/ds41_common.hpp:6-19):
+ *   - every entry point only ENQUEUES on the caller's stream (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream): no synchronisation, no allocation, no hidden threads;
+ *   - views are plain structs of device pointers, sizes and strides; storage and lifetime belong to the caller;
+ *     scratch comes from the caller and is sized by the matching *_workspace_bytes function;
+ *   - rows are independent tokens: a row's bits never depend on how many rows the call carries;
+ *   - argument errors return a non-zero status BEFORE anything is written or launched (the reference throws
+ *     std::invalid_argument there, ds41_common.hpp:33-35; exceptions do not cross a C ABI) and the text is kept in a
+ *     thread-local string read with b200moe_last_error();
+ *   - data errors (non-finite activations, invalid routes) never fail a call: they set per-row status bits and a
+ *     job summary word, later stages return early, exactly like include/strix/cuda/qwen_moe.hpp:30-31.
+ * All pointers are device pointers unless a name ends in _host.
+ *
+ * There is no CPU fallback behind this interface: without a CUDA device (or without the sm_100a image) every
+ * compute entry point fails with B200MOE_ERR_CUDA.
+ */
+#ifndef B200MOE_H
+#define B200MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_ABI_VERSION 1
+
+/* Status codes (values follow strix::weight::Error's role, include/strix/weight/types.hpp:35-40). */
+enum {
+    B200MOE_OK = 0,
+    B200MOE_ERR_INVALID_ARGUMENT = 1, /* a view is inconsistent (sizes, alignment, null pointers) */
+    B200MOE_ERR_UNSUPPORTED = 2,      /* a format / policy this build does not bind */
+    B200MOE_ERR_WORKSPACE = 3,        /* caller-owned scratch is missing or too small */
+    B200MOE_ERR_CUDA = 4,             /* a CUDA runtime call failed (text in b200moe_last_error) */
+    B200MOE_ERR_COMM = 5              /* an NCCL call failed */
+};
+
+/* ggml tensor type ids of the stored expert tensors (include/strix/cuda/qwen_moe.hpp:33). */
+#define B200MOE_TYPE_Q8_0 8u  /* 34-byte blocks {fp16 d, int8 q[32]} */
+#define B200MOE_TYPE_Q4_K 12u /* 144-byte super-blocks {fp16 d, fp16 dmin, 12 B 6-bit scales/mins, 128 B nibbles} */
+
+/* Row status / job summary bits (include/strix/cuda/qwen_moe.hpp:31). */
+#define B200MOE_ROW_INVALID_ROUTE 1u
+#define B200MOE_ROW_NONFINITE_ACTIVATION 2u
+#define B200MOE_ROW_INVALID_DELTA 4u
+#define B200MOE_ROW_PROJECTION_NONFINITE 8u
+
+int b200moe_abi_version(void);
+/* Text of the last failure on the calling thread ("" when none). Valid until the thread's next failing call. */
+const char* b200moe_last_error(void);
+/* Number of kernels this library has launched in the calling process (all threads); a plain counter for reports. */
+uint64_t b200moe_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------------ A8 activations
+ * A8 rows: codes [row][stride] int8, deltas / sums [row][stride / 32]; width <= stride, both multiples of 32.
+ * Mirrors strix::cuda::core::A8Rows (include/strix/cuda/core/types.hpp:16-21). */
+typedef struct b200moe_a8_rows {
+    int8_t* codes;
+    float* deltas;
+    int32_t* sums; /* optional (NULL) where a consumer does not read sums */
+    uint32_t rows, width, stride; /* stride 0 = width */
+} b200moe_a8_rows;
+
+/* out row r = quantize_a8(x[r * x_stride .. + width)): per 32 values delta = amax / 127 (1 when amax == 0 or
+ * amax < 2^-119, codes then 0), code = clamp(rint(x / delta), +-127), sum = sum of codes. Bitwise the host rule
+ * (src/cpu/core/reference.cpp:35-55, src/ds41_formats.cpp:146-165).
+ * Replaces strix::ds41::cuda::enqueue_quantize_a8(QuantizeA8View) (include/strix/cuda/ds41_core.hpp:17-22) and
+ * strix::cpu::Kernels::quantize_a8 (src/cpu/core/backend.hpp:68-69). x_is_bf16 != 0: x holds bfloat16 bit patterns
+ * (uint16) widened exactly, the input form of the Qwen prologue (src/cuda/models/qwen/qwen_moe.cu:60-99). */
+typedef struct b200moe_quantize_a8_view {
+    const void* x;
+    uint32_t rows, width, x_stride; /* x_stride in elements, 0 = width */
+    uint32_t x_is_bf16;
+    b200moe_a8_rows out;
+    uint32_t* status; /* optional [rows]: |= NONFINITE_ACTIVATION for a row holding a NaN / Inf */
+} b200moe_quantize_a8_view;
+int b200moe_quantize_a8(const b200moe_quantize_a8_view* view, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ Q8_0 x A8 GEMV
+ * out[r * out_stride + o] = product_q8_0(weight row (first + o), A8 row r) for o in [0, count): per 32-weight group
+ * float(int32 dot) * (scale * delta); group g into lane class g % 32, classes accumulated ascending from +0, combined
+ * by the butterfly v[l] += v[l ^ d], d = 16..1, result lane 0; accumulate != 0: out = out + product.
+ * Replaces strix::ds41::cuda::enqueue_q8_0_a8(Q8A8View) (include/strix/cuda/ds41_core.hpp:46-74) and
+ * strix::cpu::Kernels::gemv_q8_0_a8(Q8a8View) (src/cpu/core/backend.hpp:47-55, :70). */
+typedef struct b200moe_q8a8_view {
+    const uint8_t* weight; /* row o at weight + o * row_bytes */
+    uint32_t row_bytes;    /* >= width / 32 * 34, a multiple of 2 */
+    uint32_t width;        /* K, a multiple of 32 */
+    uint32_t first, count;
+    b200moe_a8_rows x;
+    float* out;
+    uint32_t out_stride; /* 0 = count */
+    uint32_t accumulate;
+} b200moe_q8a8_view;
+int b200moe_q8_0_a8(const b200moe_q8a8_view* view, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ router
+ * Mirrors strix::moe::RoutePolicy (include/strix/moe/route_policy.hpp:40-53), enum values included. */
+enum { B200MOE_SCORE_SOFTMAX = 0, B200MOE_SCORE_SIGMOID = 1, B200MOE_SCORE_SQRT_SOFTPLUS = 2 };
+enum { B200MOE_KEY_FLOAT_SERIAL = 0, B200MOE_KEY_ORDERED_BITS = 1 };
+enum { B200MOE_ORDER_SELECTION = 0, B200MOE_ORDER_ASCENDING_ID = 1 };
+typedef struct b200moe_route_policy {
+    uint32_t score;
+    uint32_t selection_bias; /* choice = score + bias[e] (selection only; weights use the unbiased score) */
+    uint32_t key;
+    uint32_t order;
+    uint32_t experts, top_k;
+    /* n_group > 1: group-limited selection. The reference rejects it (route_policy.hpp:56-60); here it is an
+     * extension in the same declared style: experts split into n_group contiguous groups, group score = c1 + c2 of
+     * the group's two best choices (picked with the policy's key), topk_group groups kept by k passes (ties -> lower
+     * group id), then the usual k-pass expert selection over the kept groups only. */
+    uint32_t n_group, topk_group;
+    uint32_t renormalize;
+    uint32_t renorm_single;
+    float renorm_eps;
+    float scale;
+} b200moe_route_policy;
+
+/* logits[r][e] = lane-strided FP32 dot of weight row e with x[r] (lane l takes elements l, l + 32, ... ascending,
+ * acc = acc + w * x with no fused multiply-add, then the butterfly d = 16..1), + logit_bias[e] when given; scores by
+ * the policy transform (declared_exp / declared_log1p, include/strix/ds41_moe.hpp:38-100); k-pass selection
+ * (choice desc, id asc; a NaN stays only as a first candidate); weights = score / (sum + eps) * scale, the sum in
+ * output order. Expert ids and weight bits equal strix::ds41::reference_router (src/ds41_moe.cpp:63-97) +
+ * strix::moe::route_select_ref (route_policy.hpp:99-129).
+ * Replaces strix::ds41::cuda::enqueue_router(RouterView) (include/strix/cuda/ds41_core.hpp:153-167) and
+ * hc::route_logits / route_select (src/cuda/models/qwen/qwen_hc.cu:1131-1361). */
+typedef struct b200moe_router_view {
+    const float* x;          /* [rows][x_stride] FP32; NULL when logits are given */
+    uint32_t x_stride;       /* 0 = hidden */
+    uint32_t rows, hidden;   /* hidden a multiple of 32 */
+    const float* weight;     /* [experts][hidden] FP32 */
+    const float* logit_bias; /* optional [experts], added to the logit before the score transform */
+    const float* bias;       /* [experts] when policy.selection_bias */
+    b200moe_route_policy policy;
+    float* logits;           /* [rows][experts]: written when x is given, read otherwise */
+    float* scores;           /* [rows][experts] output (may alias logits) */
+    uint32_t* ids;           /* [rows][top_k] */
+    float* weights;          /* [rows][top_k] */
+} b200moe_router_view;
+int b200moe_router(const b200moe_router_view* view, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ routes (permute)
+ * Expert-major CSR over the union of the window's experts; activations are never moved, kernels gather through it.
+ * Mirrors strix::ds41::cuda::MoeRoutes / MoeRoutesView (include/strix/cuda/ds41_moe.hpp:41-72) =
+ * build_window_routes + restrict_routes (src/ds41_moe.cpp:11-61): experts ascending, entries of an expert in
+ * ascending row; slots[i] = row * top_k + k; order[row][k] = the row's slots in ascending expert id;
+ * low_counts[row] = how many of them have id < split; counts[0] = union experts, counts[1] = most entries of one
+ * expert, counts[2] = entries. Only experts in [first, end) get entries (end 0 = all); experts[] holds id - base.
+ * Sizes: rows * top_k for experts / rows / slots / order, + 1 for begins, rows for low_counts, 4 for counts. */
+typedef struct b200moe_routes {
+    uint32_t* experts;
+    uint32_t* begins;
+    uint32_t* rows;
+    uint32_t* slots;
+    uint32_t* order;
+    uint32_t* low_counts;
+    uint32_t* counts;
+} b200moe_routes;
+typedef struct b200moe_routes_view {
+    const uint32_t* ids;
+    uint32_t rows, top_k, experts, split;
+    uint32_t first, end, base;
+    uint32_t* scratch;    /* [2 * experts + 2] words */
+    uint32_t* row_status; /* optional [rows]: |= INVALID_ROUTE for an id >= experts or repeated within a row */
+    b200moe_routes out;
+} b200moe_routes_view;
+int b200moe_build_routes(const b200moe_routes_view* view, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ experts
+ * Geometry and formats of the routed experts of one layer. The gate/up type fixes the arithmetic family:
+ *   Q8_0 (DS41 family, src/ds41_formats.cpp:188-197, src/ds41_moe.cpp:124-165): product_q8_0 lane classes and
+ *     butterfly for gate, up and down; h = swiglu_clamped(g, u, limit) with declared_exp; quantize_a8 per 32 outputs.
+ *   Q4_K (Qwen A8 family, src/cpu/core/routed_expert.hpp:9-15): x_j = E_g * ((d*sc_j) * float(dot_j) - (dmin*m_j) *
+ *     float(S_g)), pair sums into four chains over ascending super-blocks, (a0 + a1) + (a2 + a3);
+ *     h = (g / (1 + exp(-g))) * u with the gfx1151 v_exp twin at zero correction tables
+ *     (src/cpu/core/routed_expert.cpp:208-261); down Q4_K with the same row rule over K = inter
+ *     (src/moe_a8_down_contract.cpp:141-146) or Q8_0 with the four-chain rule (routed_expert.cpp:110-144).
+ * Tensors keep their GGUF bytes: gate, up [experts][inter][hidden / B blocks]; down [experts][hidden][inter / B]. */
+typedef struct b200moe_shape {
+    uint32_t hidden, inter, experts, top_k;
+    uint32_t gate_type, down_type;
+    float limit; /* SwiGLU clamp of the DS41 family (+inf = none); ignored by the Qwen family */
+} b200moe_shape;
+typedef struct b200moe_expert_weights {
+    const uint8_t* gate;
+    const uint8_t* up;
+    const uint8_t* down;
+} b200moe_expert_weights;
+uint64_t b200moe_gate_row_bytes(const b200moe_shape* shape);
+uint64_t b200moe_down_row_bytes(const b200moe_shape* shape);
+uint64_t b200moe_expert_bytes(const b200moe_shape* shape);
+
+/* act[slot] = quantize_a8(swiglu(gate . x[row], up . x[row])) for every routed entry.
+ * Replaces enqueue_routed_gate_up(RoutedGateUpView) (include/strix/cuda/ds41_moe.hpp:78-107), qwen_moe::enqueue_project
+ * (include/strix/cuda/qwen_moe.hpp:100) and phase 1 of strix::cpu::expert::Executor::run
+ * (src/cpu/core/routed_expert.cpp:403-427). */
+typedef struct b200moe_gate_up_view {
+    b200moe_shape shape;
+    b200moe_expert_weights weights;
+    b200moe_routes routes;
+    uint32_t max_union;     /* a bound of counts[0]: min(rows * top_k, experts) */
+    b200moe_a8_rows x;      /* [rows][hidden] */
+    b200moe_a8_rows act;    /* [slots][inter] */
+    float* gate_out;        /* optional [slots][inter] FP32 taps (both or neither) */
+    float* up_out;
+    uint32_t* row_status;   /* optional [rows] */
+    uint32_t* summary;      /* optional [1]: OR of every status bit set by the job */
+} b200moe_gate_up_view;
+int b200moe_gate_up(const b200moe_gate_up_view* view, void* stream);
+
+/* raw[slot][o] = down row o of the slot's expert . act[slot] (unweighted raw slot vector).
+ * Replaces enqueue_routed_down(RoutedDownView) (include/strix/cuda/ds41_moe.hpp:91-107), qwen_moe::enqueue_down
+ * (qwen_moe.hpp:101) and phase 2 of Executor::run (routed_expert.cpp:429-447). */
+typedef struct b200moe_down_view {
+    b200moe_shape shape;
+    b200moe_expert_weights weights;
+    b200moe_routes routes;
+    uint32_t max_union;
+    b200moe_a8_rows act;
+    float* raw;          /* [slots][hidden] */
+    const uint32_t* summary; /* optional: a non-zero word skips the whole stage (routed_expert.hpp:17-19) */
+} b200moe_down_view;
+int b200moe_down(const b200moe_down_view* view, void* stream);
+
+/* Combine forms.
+ *   PARTS (DS41, src/ds41_moe.cpp:152-163 generalised to `parts` expert ranges): y = (((shared + S_0) + S_1) ... ),
+ *     S_p = sum over the row's slots whose expert id lies in part p (p = min(id / part_experts, parts - 1)), in
+ *     ascending expert id from +0, each step one product then one add. parts = 2, part_experts = split is
+ *     (shared + low) + high. `only_part` >= 0 writes S_only_part alone (reference_half_sum, ds41_moe.cpp:99-115:
+ *     what a rank owning that part sends).
+ *   FMA_SLOTS (Qwen merge, src/cuda/models/qwen/qwen_moe.cu:286-310 = combine_ref fma_f32,
+ *     include/strix/moe/combine.hpp:36-59): acc = +0; acc = fma(w[k], raw[k], acc) in slot order; y = acc (+ shared).
+ * y_bf16 (optional) receives the bfloat16 RNE commit of y (qwen_moe.cu:330-335). */
+enum { B200MOE_COMBINE_PARTS = 0, B200MOE_COMBINE_FMA_SLOTS = 1 };
+typedef struct b200moe_combine_view {
+    const float* raw;          /* [rows * top_k][hidden] */
+    const float* shared;       /* optional [rows][hidden] */
+    const float* weights;      /* [rows * top_k] */
+    const uint32_t* ids;       /* [rows * top_k] expert id of each slot (PARTS) */
+    const uint32_t* order;     /* [rows * top_k] slots in ascending expert id (PARTS) */
+    uint32_t rows, top_k, hidden;
+    uint32_t form;
+    uint32_t parts, part_experts;
+    int32_t only_part;         /* -1: the whole combine */
+    float* y;                  /* [rows][hidden] */
+    uint16_t* y_bf16;          /* optional */
+    const uint32_t* row_status; /* optional: a row with status != 0 is not written (fail closed) */
+} b200moe_combine_view;
+int b200moe_combine(const b200moe_combine_view* view, void* stream);
+
+/* y = (a + b) + c elementwise (enqueue_moe_canonical_sum, include/strix/cuda/ds41_moe.hpp:135-137); c may be NULL. */
+int b200moe_canonical_sum(const float* a, const float* b, const float* c, uint64_t count, float* y, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ whole layer
+ * Routes from the router's ids, gate/up, down and the combine. Decode GEMVs below grouped_min_rows rows, the grouped
+ * tensor-core GEMM from there (0 = never). Replaces enqueue_moe_layer(MoeLayerView)
+ * (include/strix/cuda/ds41_moe.hpp:139-156) and qwen_moe::enqueue_routed + enqueue_combine (qwen_moe.hpp:105-107). */
+typedef struct b200moe_layer_view {
+    b200moe_shape shape;
+    b200moe_expert_weights weights;
+    uint32_t rows;
+    b200moe_a8_rows x;
+    const uint32_t* ids;        /* [rows][top_k] */
+    const float* route_weights; /* [rows][top_k] */
+    const float* shared;        /* optional [rows][hidden] */
+    uint32_t first, end, base;  /* expert range owned by this call (end 0 = all) */
+    uint32_t combine_form, parts, part_experts;
+    int32_t only_part;
+    float* raw;                 /* optional [rows * top_k][hidden] (else in the workspace) */
+    float* y;                   /* [rows][hidden]; NULL skips the combine */
+    uint16_t* y_bf16;
+    uint32_t* row_status;       /* optional [rows] */
+    void* workspace;
+    uint64_t workspace_bytes;
+    uint32_t capacity;          /* rows <= capacity */
+    uint32_t grouped_min_rows;
+} b200moe_layer_view;
+uint64_t b200moe_layer_workspace_bytes(const b200moe_shape* shape, uint32_t capacity);
+int b200moe_layer(const b200moe_layer_view* view, void* stream);
+
+/* Router + A8 + layer from FP32 (or bfloat16) activations: one token block through the whole FFN. */
+typedef struct b200moe_ffn_view {
+    b200moe_shape shape;
+    b200moe_expert_weights weights;
+    b200moe_route_policy policy;
+    const float* router_weight;  /* [experts][hidden] */
+    const float* logit_bias;     /* optional */
+    const float* select_bias;    /* when policy.selection_bias */
+    const void* x;               /* [rows][hidden] FP32 or bfloat16 */
+    uint32_t x_is_bf16;
+    uint32_t rows;
+    const float* shared;         /* optional [rows][hidden] */
+    uint32_t combine_form, parts, part_experts;
+    float* y;                    /* [rows][hidden] */
+    uint16_t* y_bf16;
+    uint32_t* ids;               /* optional outputs [rows][top_k] */
+    float* route_weights;
+    uint32_t* row_status;
+    void* workspace;
+    uint64_t workspace_bytes;    /* b200moe_ffn_workspace_bytes(shape, capacity) */
+    uint32_t capacity;
+    uint32_t grouped_min_rows;
+} b200moe_ffn_view;
+uint64_t b200moe_ffn_workspace_bytes(const b200moe_shape* shape, uint32_t capacity);
+int b200moe_ffn(const b200moe_ffn_view* view, void* stream);
+/* The same call from HOST activations: x_host / y_host are host buffers (pinned for overlap); the call copies
+ * x to the workspace, runs b200moe_ffn, copies y back and waits for the stream: what a caller holding tokens in host
+ * memory pays end to end. view->x and view->y are ignored. */
+int b200moe_ffn_host(const b200moe_ffn_view* view, const void* x_host, float* y_host, void* stream);
+
+/* Dense SwiGLU FFN block (one "expert" applied to every row): y_partial[r] = down . A8(swiglu(gate . x_r, up . x_r))
+ * over this call's slice of inter (tensor parallel: gate/up column shares and the matching down K share are stored
+ * compacted, so a rank passes its own tensors and inter = its share; the partials are summed by the caller's
+ * allreduce). Row rule as the routed experts of the same types. */
+typedef struct b200moe_dense_view {
+    b200moe_shape shape;          /* experts = 1, top_k = 1 */
+    b200moe_expert_weights weights;
+    uint32_t rows;
+    b200moe_a8_rows x;
+    float* y;                     /* [rows][hidden] FP32 */
+    uint16_t* y_bf16;             /* optional bfloat16 RNE copy (the allreduce payload) */
+    void* workspace;
+    uint64_t workspace_bytes;     /* b200moe_layer_workspace_bytes(shape, rows) */
+} b200moe_dense_view;
+int b200moe_dense_ffn(const b200moe_dense_view* view, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H */

@@ -1,0 +1,408 @@
+// TEST INFRASTRUCTURE - not part of the shipped library.
+//
+// C entry points around the reference engine's OWN CPU code for the MoE FFN path. This file holds no arithmetic of
+// its own (apart from the clearly marked threaded driver at the end, used only to time the reference's row kernels):
+// it includes the reference's headers and is linked with object files compiled from the reference's source files
+// where they lie (see oracle/Makefile); nothing of the reference is copied into this repository. The result,
+// oracle/_ref/libstrixref.so, validates the restatement in oracle/moe_oracle.cpp, generates the vectors under
+// tests/golden/, and is the "reference" CPU baseline of the benchmark.
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <filesystem>
+#include <functional>
+#include <limits>
+#include <unistd.h>
+#include <memory>
+#include <optional>
+#include <span>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "cpu/arch/avx2/routed_expert_avx2.hpp"
+#include "cpu/core/backend.hpp"
+#include "cpu/core/routed_expert.hpp"
+#include "cpu/core/routed_expert_kernels.hpp"
+#include "strix/ds41_formats.hpp"
+#include "strix/ds41_moe.hpp"
+#include "strix/gguf_reader.hpp"
+#include "strix/moe/combine.hpp"
+#include "strix/moe/route_policy.hpp"
+#include "strix/moe_a8_down_contract.hpp"
+#include "strix/moe_plan.hpp"
+#include "strix/moe_q4k_a8_contract.hpp"
+
+// src/moe_plan.cpp references this symbol from the GGUF reader (storage planning only, never on the routing path);
+// the reader itself drags in the whole weight library, so the link is closed with an empty answer.
+namespace strix::gguf {
+std::optional<TensorTypeGeometry> tensor_type_geometry(std::uint32_t) noexcept { return std::nullopt; }
+}
+
+namespace {
+using u8 = std::uint8_t;
+using u32 = std::uint32_t;
+using i8 = std::int8_t;
+using i32 = std::int32_t;
+namespace ex = strix::cpu::expert;
+
+struct Ds41Math {
+    static float exp(float x) { return strix::ds41::declared_exp(x); }
+    static float log1p(float x) { return strix::ds41::declared_log1p(x); }
+    static float sqrt(float x) { return strix::ds41::declared_sqrt(x); }
+};
+
+const ex::Gfx1151Exp& zero_exp() {
+    static const std::unique_ptr<ex::Gfx1151Exp> exp = [] {
+        const auto dir = std::filesystem::temp_directory_path() / ("b200moe_exp_tables_" + std::to_string(::getpid()));
+        std::filesystem::create_directories(dir);
+        const u32 zero[2] = {0, 0};  // the bench's zero tables (scripts/bench/residency/cpu_expert_bench.cpp:78-89)
+        for (const char* n : {"tbl_exp_pm.bin", "hard_v_exp_f32.bin"}) {
+            FILE* f = std::fopen((dir / n).c_str(), "wb");
+            std::fwrite(zero, 4, 2, f);
+            std::fclose(f);
+        }
+        return std::make_unique<ex::Gfx1151Exp>(dir.string());
+    }();
+    return *exp;
+}
+
+strix::moe::RoutePolicy to_policy(const u32* p, float eps, float scale) {
+    strix::moe::RoutePolicy r;
+    r.score = static_cast<strix::moe::RouteScore>(p[0]);
+    r.selection_bias = p[1] != 0;
+    r.key = static_cast<strix::moe::RouteKey>(p[2]);
+    r.order = static_cast<strix::moe::RouteOrder>(p[3]);
+    r.experts = p[4]; r.top_k = p[5]; r.n_group = p[6]; r.topk_group = p[7];
+    r.renormalize = p[8] != 0; r.renorm_single = p[9] != 0;
+    r.renorm_eps = eps; r.scale = scale;
+    return r;
+}
+}  // namespace
+
+extern "C" {
+
+float ref_half_to_float(std::uint16_t h) { return strix::cpu::half_to_float(h); }
+float ref_declared_exp(float x) { return strix::ds41::declared_exp(x); }
+float ref_router_score(float z) { return strix::ds41::router_score(z); }
+float ref_swiglu_clamped(float g, float u, float limit) { return strix::ds41::swiglu_clamped(g, u, limit); }
+float ref_gfx1151_expf(float x) { return zero_exp().expf(x); }
+const char* ref_cpu_isa() { return strix::cpu::isa_name(strix::cpu::select(strix::cpu::caps()).isa); }
+
+// strix::cpu reference table (src/cpu/core/reference.cpp). 1 = rejected (std::invalid_argument).
+int ref_quantize_a8(const float* x, std::size_t width, i8* codes, float* deltas, i32* sums) {
+    try { strix::cpu::reference_kernels().quantize_a8(x, width, codes, deltas, sums); } catch (const std::invalid_argument&) { return 1; }
+    return 0;
+}
+int ref_gemv_q8_0_a8(const u8* weight, u32 row_bytes, u32 in, u32 count, u32 rows, const i8* codes, const float* deltas,
+                     u32 x_stride, float* out, u32 out_stride, u32 accumulate) {
+    const strix::cpu::Q8a8View v{weight, codes, deltas, out, row_bytes, in, count, rows, x_stride, out_stride, accumulate};
+    try { strix::cpu::reference_kernels().gemv_q8_0_a8(v, {}); } catch (const std::invalid_argument&) { return 1; }
+    return 0;
+}
+// strix::ds41 host references (src/ds41_formats.cpp).
+void ref_ds41_quantize_a8(const float* x, std::size_t width, i8* codes, float* deltas, i32* sums) {
+    const auto a = strix::ds41::quantize_a8(std::span<const float>(x, width));
+    std::memcpy(codes, a.codes.data(), width);
+    std::memcpy(deltas, a.deltas.data(), width / 32 * 4);
+    std::memcpy(sums, a.sums.data(), width / 32 * 4);
+}
+float ref_product_q8_0(const u8* row, const i8* codes, const float* deltas, std::size_t width) {
+    strix::ds41::A8Activation a;
+    a.codes.assign(codes, codes + width);
+    a.deltas.assign(deltas, deltas + width / 32);
+    a.sums.assign(width / 32, 0);
+    return strix::ds41::product_q8_0(std::span<const u8>(row, width / 32 * 34), a, width);
+}
+
+// strix::ds41::reference_router (src/ds41_moe.cpp:63-97): sqrt-softplus scores, ds41 preset.
+int ref_reference_router(const float* x, u32 rows, u32 hidden, const float* weight, u32 experts, const float* bias,
+                         const float* bias_image, const u8* image_rows, u32 top_k, float scale, float* scores, u32* ids,
+                         float* weights) {
+    try {
+        const auto out = strix::ds41::reference_router(
+            std::span<const float>(x, (std::size_t)rows * hidden), rows, hidden,
+            std::span<const float>(weight, (std::size_t)experts * hidden), experts, std::span<const float>(bias, experts),
+            bias_image ? std::span<const float>(bias_image, experts) : std::span<const float>(),
+            image_rows ? std::span<const u8>(image_rows, rows) : std::span<const u8>(), top_k, scale);
+        if (scores) std::memcpy(scores, out.scores.data(), out.scores.size() * 4);
+        std::memcpy(ids, out.ids.data(), out.ids.size() * 4);
+        std::memcpy(weights, out.weights.data(), out.weights.size() * 4);
+    } catch (const std::invalid_argument&) { return 1; }
+    return 0;
+}
+// strix::moe::route_scores_ref<Ds41Math> / route_select_ref (include/strix/moe/route_policy.hpp:99-156).
+// policy words: score, selection_bias, key, order, experts, top_k, n_group, topk_group, renormalize, renorm_single.
+int ref_route_scores(u32 score, const float* logits, u32 n, float* scores) {
+    try {
+        strix::moe::route_scores_ref<Ds41Math>(static_cast<strix::moe::RouteScore>(score), std::span<const float>(logits, n),
+                                               std::span<float>(scores, n));
+    } catch (const std::invalid_argument&) { return 1; }
+    return 0;
+}
+int ref_route_select(const u32* policy, float eps, float scale, const float* scores, const float* bias, u32* ids, float* weights) {
+    const auto p = to_policy(policy, eps, scale);
+    try {
+        strix::moe::route_select_ref(p, std::span<const float>(scores, p.experts),
+                                     bias ? std::span<const float>(bias, p.experts) : std::span<const float>(),
+                                     std::span<u32>(ids, p.top_k), std::span<float>(weights, p.top_k));
+    } catch (const std::invalid_argument&) { return 1; }
+    return 0;
+}
+// strix::select_moe_experts_deterministic (src/moe_plan.cpp:101-162): std::exp softmax cross-check.
+int ref_select_softmax(const float* logits, u32 n, u32 top_k, int normalize, u32* ids, float* weights) {
+    try {
+        const auto s = strix::select_moe_experts_deterministic(std::span<const float>(logits, n), top_k, normalize != 0);
+        std::memcpy(ids, s.experts.data(), top_k * 4);
+        std::memcpy(weights, s.weights.data(), top_k * 4);
+    } catch (const std::exception&) { return 1; }
+    return 0;
+}
+
+// build_window_routes + restrict_routes (src/ds41_moe.cpp:11-61). Output arrays as include/b200moe.h; experts are NOT
+// rebased here. Returns the union count or -1 (std::invalid_argument).
+int ref_window_routes(const u32* ids, u32 rows, u32 top_k, u32 split, u32 first, u32 end, u32* experts, u32* begins, u32* out_rows,
+                      u32* slots, u32* order, u32* low_counts, u32* max_rows) {
+    try {
+        auto r = strix::ds41::build_window_routes(std::span<const u32>(ids, (std::size_t)rows * top_k), rows, top_k, split);
+        if (end) r = strix::ds41::restrict_routes(r, first, end);
+        std::memcpy(experts, r.experts.data(), r.experts.size() * 4);
+        std::memcpy(begins, r.begins.data(), r.begins.size() * 4);
+        std::memcpy(out_rows, r.rows.data(), r.rows.size() * 4);
+        std::memcpy(slots, r.slots.data(), r.slots.size() * 4);
+        std::memcpy(order, r.order.data(), r.order.size() * 4);
+        std::memcpy(low_counts, r.low_counts.data(), r.low_counts.size() * 4);
+        *max_rows = r.max_rows;
+        return (int)r.experts.size();
+    } catch (const std::invalid_argument&) { return -1; }
+}
+
+// strix::ds41::reference_window with Q8_0 tensors (src/ds41_moe.cpp:124-165). x: FP32 rows quantised with
+// ds41::quantize_a8. Outputs: gate / up [slot][inter], act codes [slot][inter] / deltas / sums, raw [slot][hidden], y.
+int ref_window_q8_0(const u8* gate, const u8* up, const u8* down, u32 experts, u32 hidden, u32 inter, float limit, const float* x,
+                    u32 rows, const u32* ids, const float* weights, const float* shared, u32 top_k, u32 split, u32 first, u32 end,
+                    float* gate_out, float* up_out, i8* act_codes, float* act_deltas, i32* act_sums, float* raw, float* y) {
+    try {
+        strix::ds41::ExpertTensors t;
+        t.gate_up_format = t.down_format = strix::ds41::WeightFormat::q8_0;
+        t.hidden = hidden; t.inter = inter; t.limit = limit;
+        t.gate = std::span<const u8>(gate, (std::size_t)experts * inter * (hidden / 32 * 34));
+        t.up = std::span<const u8>(up, t.gate.size());
+        t.down = std::span<const u8>(down, (std::size_t)experts * hidden * (inter / 32 * 34));
+        std::vector<strix::ds41::A8Activation> xa;
+        for (u32 r = 0; r < rows; ++r) xa.push_back(strix::ds41::quantize_a8(std::span<const float>(x + (std::size_t)r * hidden, hidden)));
+        auto routes = strix::ds41::build_window_routes(std::span<const u32>(ids, (std::size_t)rows * top_k), rows, top_k, split);
+        if (end) routes = strix::ds41::restrict_routes(routes, first, end);
+        const auto out = strix::ds41::reference_window(t, xa, routes, std::span<const float>(weights, (std::size_t)rows * top_k),
+                                                       std::span<const float>(shared, (std::size_t)rows * hidden), top_k);
+        const std::size_t slots = (std::size_t)rows * top_k;
+        if (gate_out) std::memcpy(gate_out, out.gate.data(), slots * inter * 4);
+        if (up_out) std::memcpy(up_out, out.up.data(), slots * inter * 4);
+        for (std::size_t s = 0; s < slots; ++s) {
+            if (out.activation[s].codes.empty()) continue;
+            if (act_codes) std::memcpy(act_codes + s * inter, out.activation[s].codes.data(), inter);
+            if (act_deltas) std::memcpy(act_deltas + s * (inter / 32), out.activation[s].deltas.data(), inter / 32 * 4);
+            if (act_sums) std::memcpy(act_sums + s * (inter / 32), out.activation[s].sums.data(), inter / 32 * 4);
+        }
+        if (raw) std::memcpy(raw, out.raw.data(), slots * hidden * 4);
+        if (y) std::memcpy(y, out.y.data(), (std::size_t)rows * hidden * 4);
+    } catch (const std::invalid_argument&) { return 1; }
+    return 0;
+}
+// reference_half_sum (src/ds41_moe.cpp:99-115).
+int ref_half_sum(const u32* ids, u32 rows, u32 top_k, u32 split, const float* weights, const float* raw, u32 hidden, unsigned half, float* out) {
+    try {
+        const auto routes = strix::ds41::build_window_routes(std::span<const u32>(ids, (std::size_t)rows * top_k), rows, top_k, split);
+        const auto v = strix::ds41::reference_half_sum(routes, std::span<const float>(weights, (std::size_t)rows * top_k),
+                                                       std::span<const float>(raw, (std::size_t)rows * top_k * hidden), rows, top_k, hidden, half);
+        std::memcpy(out, v.data(), v.size() * 4);
+    } catch (const std::invalid_argument&) { return 1; }
+    return 0;
+}
+
+// strix::cpu::expert (src/cpu/core/routed_expert.cpp): reference_run (threads == 0) or Executor(threads, simd).
+// gate_format 0 q4_k / 1 q5_k; down_format 0 q5_1 / 1 q8_0. assignments: count x {row, slot, expert}.
+// rawdots [rows][slots_per_row][hidden]; status [rows].
+int ref_expert_run(const u8* gate, const u8* up, const u8* down, u32 gate_format, u32 down_format, u32 hidden, u32 ffn,
+                   const i8* codes, const float* deltas, const i32* sums, u32 rows, const u32* assignments, u32 count,
+                   u32 slots_per_row, float* rawdots, u32* status, u32 threads, int simd) {
+    std::vector<ex::RowA8> ra(rows);
+    for (u32 r = 0; r < rows; ++r)
+        ra[r] = {codes + (std::size_t)r * hidden, deltas + (std::size_t)r * (hidden / 32), sums + (std::size_t)r * (hidden / 32)};
+    std::vector<ex::Assignment> as(count);
+    for (u32 a = 0; a < count; ++a) as[a] = {assignments[3 * a], assignments[3 * a + 1], assignments[3 * a + 2]};
+    ex::Job job;
+    job.weights.gate = gate; job.weights.up = up; job.weights.down = down;
+    job.weights.gate_format = static_cast<ex::GateFormat>(gate_format);
+    job.weights.down_format = static_cast<ex::DownFormat>(down_format);
+    job.weights.shape = {hidden, ffn};
+    job.rows = ra.data(); job.assignments = as.data(); job.count = count;
+    job.rawdots = rawdots; job.rawdot_row_stride = (std::uint64_t)slots_per_row * hidden; job.status = status;
+    if (threads == 0) ex::reference_run(job, zero_exp());
+    else { ex::Executor e(threads, zero_exp(), simd != 0); e.run(job); }
+    return 0;
+}
+// One gate/up row through the executor's kernel tables (scalar oracle table or the AVX2 table).
+float ref_gate_row_q4k(const u8* wrow, u32 blocks, const i8* codes, const float* deltas, const i32* sums, int simd) {
+    const ex::RowA8 row{codes, deltas, sums};
+    const ex::RowA8* rp = &row;
+    const ex::detail::Kernels* k = &ex::detail::scalar_kernels();
+    if (simd) if (const auto* a = strix::cpu::arch::avx2::expert_kernels()) k = a;
+    float out = 0.0f;
+    k->gate[0](wrow, blocks, &rp, 1, &out);
+    return out;
+}
+float ref_down_row_q8_0(const u8* wrow, u32 groups, const i8* codes, const float* deltas, const i32* sums) {
+    float out = 0.0f;
+    ex::detail::scalar_kernels().down[1](wrow, groups, &codes, &deltas, &sums, 1, &out);
+    return out;
+}
+// Contract-level oracles (src/moe_q4k_a8_contract.cpp:126-141; src/moe_a8_down_contract.cpp:141-211). NaN on a
+// rejected row (width limits: 2560 gate/up, 1536 K-quant down).
+float ref_evaluate_row_q4k(const u8* w, const i8* codes, const float* deltas, const i32* sums, u32 width) {
+    strix::moe_q4k_a8::QuantizedRow q;
+    q.codes.assign(codes, codes + width); q.deltas.assign(deltas, deltas + width / 32); q.sums.assign(sums, sums + width / 32);
+    try { return strix::moe_q4k_a8::evaluate_row(std::span<const std::byte>(reinterpret_cast<const std::byte*>(w), width / 256 * 144), q); }
+    catch (const std::exception&) { return std::numeric_limits<float>::quiet_NaN(); }
+}
+float ref_evaluate_down_row(const u8* w, const i8* codes, const float* deltas, const i32* sums, u32 width, u32 type) {
+    strix::moe_q4k_a8::QuantizedRow q;
+    q.codes.assign(codes, codes + width); q.deltas.assign(deltas, deltas + width / 32); q.sums.assign(sums, sums + width / 32);
+    try {
+        const auto bytes = strix::moe_q4k_a8::down_row_bytes(type, width);
+        return strix::moe_q4k_a8::evaluate_down_row(std::span<const std::byte>(reinterpret_cast<const std::byte*>(w), type == 12 ? width / 256 * 144 : bytes), q, type);
+    } catch (const std::exception&) { return std::numeric_limits<float>::quiet_NaN(); }
+}
+// strix::moe::combine_ref (include/strix/moe/combine.hpp:36-59). form 0 fma_f32, 1 bf16_steps.
+int ref_combine(u32 form, u32 rows, u32 top_k, u32 width, const float* w, const float* eo, const float* base, float* y) {
+    const std::size_t n = (std::size_t)rows * width;
+    try {
+        strix::moe::combine_ref(static_cast<strix::moe::CombineForm>(form), rows, top_k, width,
+                                w ? std::span<const float>(w, (std::size_t)rows * top_k) : std::span<const float>(),
+                                std::span<const float>(eo, n * top_k), base ? std::span<const float>(base, n) : std::span<const float>(),
+                                std::span<float>(y, n));
+    } catch (const std::invalid_argument&) { return 1; }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Timing driver (the benchmark's reference arm). It runs the reference's own row kernels - the executor's table
+// (AVX2 / AVX-VNNI when the host has it, else scalar) for Q4_K gate/up AND for the Q4_K down rows (the reference's
+// Q4_K down contract is the gate/up row rule over K = inter, include/strix/moe_a8_down_contract.hpp:9-11; its executor
+// itself only binds Q5_1 / Q8_0 down, src/cpu/core/routed_expert.hpp:27-28), its Gfx1151Exp and its A8 rule, its
+// router (reference_router's dot order + route_scores_ref / route_select_ref) - over all host threads with the
+// executor's item split ((expert, 32-output group), then (expert, 16 hidden outputs)). Returns seconds for `reps`
+// layer calls; y receives the last call's output (Qwen merge form) so the caller can check it.
+static void parallel_items(unsigned threads, u32 n, const std::function<void(u32)>& fn) {
+    std::atomic<u32> next{0};
+    auto work = [&] { for (;;) { const u32 i = next.fetch_add(1, std::memory_order_relaxed); if (i >= n) break; fn(i); } };
+    std::vector<std::thread> pool;
+    for (unsigned t = 1; t < threads; ++t) pool.emplace_back(work);
+    work();
+    for (auto& t : pool) t.join();
+}
+
+double ref_time_layer_q4k(const u8* gate, const u8* up, const u8* down, u32 experts, u32 hidden, u32 inter, u32 top_k,
+                          const float* router_w, const float* x, u32 rows, unsigned threads, u32 reps, float* y, u32* ids_out) {
+    const ex::detail::Kernels* k = &ex::detail::scalar_kernels();
+    if (strix::cpu::caps().avx2) if (const auto* a = strix::cpu::arch::avx2::expert_kernels()) k = a;
+    const u32 blocks = hidden / 256, groups = inter / 32, dblocks = inter / 256;
+    const std::size_t grow = (std::size_t)blocks * 144, drow = (std::size_t)dblocks * 144;
+    const strix::moe::RoutePolicy policy{strix::moe::RouteScore::softmax, false, strix::moe::RouteKey::float_serial,
+                                         strix::moe::RouteOrder::selection, experts, top_k, 1U, 1U, true, true, 1e-20F, 1.0F};
+    const auto& exp = zero_exp();
+    const auto t0 = std::chrono::steady_clock::now();
+    for (u32 rep = 0; rep < reps; ++rep) {
+        // A8 of the input (strix::cpu reference table)
+        std::vector<i8> xc((std::size_t)rows * hidden);
+        std::vector<float> xd((std::size_t)rows * hidden / 32);
+        std::vector<i32> xs(xd.size());
+        for (u32 r = 0; r < rows; ++r)
+            strix::cpu::reference_kernels().quantize_a8(x + (std::size_t)r * hidden, hidden, xc.data() + (std::size_t)r * hidden,
+                                                       xd.data() + (std::size_t)r * hidden / 32, xs.data() + (std::size_t)r * hidden / 32);
+        // router: declared dot order (src/ds41_moe.cpp:72-82), softmax transform, k-pass selection
+        std::vector<float> logits((std::size_t)rows * experts);
+        parallel_items(threads, rows * experts, [&](u32 i) {
+            const u32 r = i / experts, e = i % experts;
+            float lanes[32] = {};
+            for (u32 c = 0; c < hidden; ++c) lanes[c % 32] = lanes[c % 32] + router_w[(std::size_t)e * hidden + c] * x[(std::size_t)r * hidden + c];
+            for (unsigned d = 16; d; d /= 2) { float n[32]; for (unsigned l = 0; l < 32; ++l) n[l] = lanes[l] + lanes[l ^ d]; std::memcpy(lanes, n, sizeof n); }
+            logits[i] = lanes[0];
+        });
+        std::vector<u32> ids((std::size_t)rows * top_k);
+        std::vector<float> rw(ids.size());
+        for (u32 r = 0; r < rows; ++r) {
+            std::vector<float> s(experts);
+            strix::moe::route_scores_ref<Ds41Math>(policy.score, std::span<const float>(logits.data() + (std::size_t)r * experts, experts), s);
+            strix::moe::route_select_ref(policy, s, {}, std::span<u32>(ids.data() + (std::size_t)r * top_k, top_k),
+                                         std::span<float>(rw.data() + (std::size_t)r * top_k, top_k));
+        }
+        // group slots by expert (stable), as Executor::prepare
+        std::vector<u32> order(ids.size());
+        for (u32 i = 0; i < order.size(); ++i) order[i] = i;
+        std::stable_sort(order.begin(), order.end(), [&](u32 a, u32 b) { return ids[a] < ids[b]; });
+        std::vector<u32> ex_begin, ex_id;
+        for (u32 p = 0; p < order.size(); ++p)
+            if (p == 0 || ids[order[p]] != ids[order[p - 1]]) { ex_id.push_back(ids[order[p]]); ex_begin.push_back(p); }
+        ex_begin.push_back((u32)order.size());
+        std::vector<ex::RowA8> rowa(rows);
+        for (u32 r = 0; r < rows; ++r) rowa[r] = {xc.data() + (std::size_t)r * hidden, xd.data() + (std::size_t)r * hidden / 32, xs.data() + (std::size_t)r * hidden / 32};
+        const std::size_t slots = order.size();
+        std::vector<i8> hc(slots * inter);
+        std::vector<float> hd(slots * groups);
+        std::vector<i32> hs(slots * groups);
+        const u32 n_ex = (u32)ex_id.size();
+        parallel_items(threads, n_ex * groups, [&](u32 item) {
+            const u32 e = item / groups, grp = item % groups, expert = ex_id[e];
+            for (u32 p = ex_begin[e]; p < ex_begin[e + 1]; p += ex::detail::kMaxAssign) {
+                const u32 na = std::min(ex::detail::kMaxAssign, ex_begin[e + 1] - p);
+                const ex::RowA8* rp[ex::detail::kMaxAssign];
+                for (u32 a = 0; a < na; ++a) rp[a] = &rowa[order[p + a] / top_k];
+                float g[ex::detail::kMaxAssign][32], u[ex::detail::kMaxAssign][32];
+                for (u32 l = 0; l < 32; ++l) {
+                    float tg[ex::detail::kMaxAssign], tu[ex::detail::kMaxAssign];
+                    const std::size_t off = ((std::size_t)expert * inter + grp * 32 + l) * grow;
+                    k->gate[0](gate + off, blocks, rp, na, tg);
+                    k->gate[0](up + off, blocks, rp, na, tu);
+                    for (u32 a = 0; a < na; ++a) { g[a][l] = tg[a]; u[a][l] = tu[a]; }
+                }
+                for (u32 a = 0; a < na; ++a) {
+                    float hv[32];
+                    for (u32 l = 0; l < 32; ++l) hv[l] = (g[a][l] / (1.0F + exp.expf(-g[a][l]))) * u[a][l];
+                    const std::size_t s = order[p + a];
+                    strix::cpu::reference_kernels().quantize_a8(hv, 32, hc.data() + s * inter + grp * 32, &hd[s * groups + grp], &hs[s * groups + grp]);
+                }
+            }
+        });
+        std::vector<float> raw(slots * hidden);
+        parallel_items(threads, n_ex * (hidden / 16), [&](u32 item) {
+            const u32 per = hidden / 16, e = item / per, o0 = (item % per) * 16, expert = ex_id[e];
+            for (u32 p = ex_begin[e]; p < ex_begin[e + 1]; p += ex::detail::kMaxAssign) {
+                const u32 na = std::min(ex::detail::kMaxAssign, ex_begin[e + 1] - p);
+                ex::RowA8 ha[ex::detail::kMaxAssign];
+                const ex::RowA8* rp[ex::detail::kMaxAssign];
+                for (u32 a = 0; a < na; ++a) {
+                    const std::size_t s = order[p + a];
+                    ha[a] = {hc.data() + s * inter, hd.data() + s * groups, hs.data() + s * groups};
+                    rp[a] = &ha[a];
+                }
+                for (u32 l = 0; l < 16; ++l) {
+                    float t[ex::detail::kMaxAssign];
+                    k->gate[0](down + ((std::size_t)expert * hidden + o0 + l) * drow, dblocks, rp, na, t);
+                    for (u32 a = 0; a < na; ++a) raw[(std::size_t)order[p + a] * hidden + o0 + l] = t[a];
+                }
+            }
+        });
+        // Qwen merge (combine_ref fma_f32, base 0)
+        std::vector<float> zero((std::size_t)rows * hidden, 0.0F);
+        strix::moe::combine_ref(strix::moe::CombineForm::fma_f32, rows, top_k, hidden, rw, raw, zero, std::span<float>(y, (std::size_t)rows * hidden));
+        if (ids_out) std::memcpy(ids_out, ids.data(), ids.size() * 4);
+    }
+    return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+}
+
+}  // extern "C"

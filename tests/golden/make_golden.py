@@ -1,0 +1,83 @@
+"""Generates tests/golden/moe_golden.npz from the reference's OWN CPU code (oracle/_ref/libstrixref.so, built from
+the reference checkout by oracle/Makefile). Run where the reference checkout exists:
+
+    make -C oracle && python tests/golden/make_golden.py
+
+The vectors are small seeded cases of every contract on the path; tests/test_oracle_pins.py::test_golden_vectors
+replays them against the restated oracle wherever the reference itself is absent (e.g. on the GPU box).
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path[:0] = [ROOT, os.path.join(ROOT, "strix-halo-engine-lab_b200")]
+from oracle.loader import Ref  # noqa: E402
+from b200moe import synth  # noqa: E402
+
+
+def main():
+    ref = Ref()
+    rng = np.random.default_rng(20250)
+    out = {}
+    # A8
+    x = rng.standard_normal((3, 256), dtype=np.float32) * np.float32(2.5)
+    x[1, :32] = 0.0
+    x[1, 32:64] = 1e-37
+    out["a8_x"] = x
+    out["a8_codes"], out["a8_deltas"], out["a8_sums"] = ref.quantize_a8(x)
+    # Q8_0 x A8 GEMV
+    width, count = 1024, 12
+    w = synth.q8_0_blocks(rng, count * width // 32).reshape(count, -1)
+    xx = rng.standard_normal((2, width), dtype=np.float32)
+    c, d, _ = ref.quantize_a8(xx)
+    out.update(q8_w=w, q8_width=np.int64(width), q8_codes=c, q8_deltas=d, q8_y=ref.gemv_q8_0_a8(w, width, c, d))
+    # Q4_K x A8 rows (executor scalar table)
+    width = 2048
+    w4 = synth.q4_k_blocks(rng, 10 * width // 256, scale=0.002).reshape(10, -1)
+    x4 = rng.standard_normal((1, width), dtype=np.float32)
+    c, d, s = ref.quantize_a8(x4)
+    y4 = np.array([ref.gate_row_q4k(w4[o], c[0], d[0], s[0]) for o in range(10)], np.float32)
+    out.update(q4k_w=w4, q4k_codes=c, q4k_deltas=d, q4k_sums=s, q4k_y=y4)
+    # reference_router (sqrt-softplus, ds41 preset)
+    E, H, K = 64, 512, 6
+    rx = rng.standard_normal((4, H), dtype=np.float32)
+    rw = synth.router_weight(rng, E, H, std=0.05)
+    rb = (rng.standard_normal(E) * 0.1).astype(np.float32)
+    sc, ids, wt = ref.reference_router(rx, rw, rb, K, 1.5)
+    out.update(rt_x=rx, rt_w=rw, rt_bias=rb, rt_scores=sc, rt_ids=ids, rt_weights=wt)
+    # softmax policy through route_scores_ref + route_select_ref
+    from oracle.loader import softmax_policy
+    lg = rng.uniform(-1, 1, size=(6, 128)).astype(np.float32)
+    pol = softmax_policy(128, 8)
+    sc = ref.route_scores(pol.score, lg)
+    ids, wt = ref.route_select(pol, sc)
+    out.update(sm_logits=lg, sm_scores=sc, sm_ids=ids, sm_weights=wt)
+    # DS41 window, Q8_0
+    E, H, I, K, rows = 6, 256, 128, 3, 4
+    g, u, dn = synth.expert_tensors(rng, E, H, I, 8, 8)
+    x = rng.standard_normal((rows, H), dtype=np.float32)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+    wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
+    shared = rng.standard_normal((rows, H), dtype=np.float32)
+    win = ref.window_q8_0(g, u, dn, E, H, I, 10.0, x, ids, wts, shared, split=E // 2)
+    out.update(win_shape=np.array([E, H, I, K]), win_limit=np.float32(10.0), win_gate=g, win_up=u, win_down=dn, win_x=x,
+               win_ids=ids, win_weights=wts, win_shared=shared, win_raw=win["raw"], win_y=win["y"])
+    # Qwen job: Q4_K gate/up, Q8_0 four-chain down (reference_run)
+    E, H, I, K, rows = 4, 256, 128, 2, 3
+    g, u, _ = synth.expert_tensors(rng, E, H, I, 12, 12)
+    dn = synth.q8_0_blocks(rng, E * H * (I // 32)).reshape(-1)
+    x = rng.standard_normal((rows, H), dtype=np.float32)
+    c, d, s = ref.quantize_a8(x)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+    raw, status = ref.expert_run(g, u, dn, 0, 1, H, I, c, d, s, ids, threads=0)
+    assert not status.any()
+    out.update(qw_shape=np.array([E, H, I, K]), qw_gate=g, qw_up=u, qw_down=dn, qw_x=x, qw_ids=ids, qw_raw=raw)
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "moe_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()
