@@ -167,10 +167,11 @@ typedef struct b200moe_routes_view {
     const uint32_t* ids;
     uint32_t rows, top_k, experts, split;
     uint32_t first, end, base;
-    uint32_t* scratch;    /* [2 * experts + 2] words */
+    uint32_t* scratch;    /* b200moe_routes_scratch_words(rows, top_k, experts) words; may be NULL up to 1024 slots */
     uint32_t* row_status; /* optional [rows]: |= INVALID_ROUTE for an id >= experts or repeated within a row */
     b200moe_routes out;
 } b200moe_routes_view;
+uint64_t b200moe_routes_scratch_words(uint32_t rows, uint32_t top_k, uint32_t experts);
 int b200moe_build_routes(const b200moe_routes_view* view, void* stream);
 
 /* ------------------------------------------------------------------------------------------------ experts

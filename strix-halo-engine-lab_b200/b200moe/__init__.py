@@ -1,1 +1,179 @@
-"""Host-side Python binding of the B200 MoE FFN library (ctypes over the C ABI of include/b200moe.h)."""
+"""Host-side Python binding of the B200 MoE FFN library: ctypes over the C ABI of include/b200moe.h.
+
+The structures below mirror the header field for field; device memory and streams come from torch (plumbing only).
+There is no CPU path here: loading fails loudly when libb200moe.so has not been built, and every compute call fails
+with B200MoeError when no sm_100 device is usable.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.dirname(HERE)
+LIB_PATH = os.path.join(PKG, "libb200moe.so")
+
+OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_COMM = range(6)
+TYPE_Q8_0, TYPE_Q4_K = 8, 12
+ROW_INVALID_ROUTE, ROW_NONFINITE_ACTIVATION, ROW_INVALID_DELTA, ROW_PROJECTION_NONFINITE = 1, 2, 4, 8
+SCORE_SOFTMAX, SCORE_SIGMOID, SCORE_SQRT_SOFTPLUS = 0, 1, 2
+KEY_FLOAT_SERIAL, KEY_ORDERED_BITS = 0, 1
+ORDER_SELECTION, ORDER_ASCENDING_ID = 0, 1
+COMBINE_PARTS, COMBINE_FMA_SLOTS = 0, 1
+
+u32, i32, u64, f32, vp = C.c_uint32, C.c_int32, C.c_uint64, C.c_float, C.c_void_p
+
+
+class B200MoeError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__(f"b200moe status {code}: {text}")
+        self.code = code
+
+
+class InvalidArgument(B200MoeError, ValueError):
+    """The reference's std::invalid_argument: raised before anything was written or launched."""
+
+
+class A8Rows(C.Structure):
+    _fields_ = [("codes", vp), ("deltas", vp), ("sums", vp), ("rows", u32), ("width", u32), ("stride", u32)]
+
+
+class QuantizeA8View(C.Structure):
+    _fields_ = [("x", vp), ("rows", u32), ("width", u32), ("x_stride", u32), ("x_is_bf16", u32), ("out", A8Rows), ("status", vp)]
+
+
+class Q8A8View(C.Structure):
+    _fields_ = [("weight", vp), ("row_bytes", u32), ("width", u32), ("first", u32), ("count", u32), ("x", A8Rows), ("out", vp),
+                ("out_stride", u32), ("accumulate", u32)]
+
+
+class RoutePolicy(C.Structure):
+    _fields_ = [("score", u32), ("selection_bias", u32), ("key", u32), ("order", u32), ("experts", u32), ("top_k", u32),
+                ("n_group", u32), ("topk_group", u32), ("renormalize", u32), ("renorm_single", u32), ("renorm_eps", f32),
+                ("scale", f32)]
+
+
+class RouterView(C.Structure):
+    _fields_ = [("x", vp), ("x_stride", u32), ("rows", u32), ("hidden", u32), ("weight", vp), ("logit_bias", vp), ("bias", vp),
+                ("policy", RoutePolicy), ("logits", vp), ("scores", vp), ("ids", vp), ("weights", vp)]
+
+
+class Routes(C.Structure):
+    _fields_ = [("experts", vp), ("begins", vp), ("rows", vp), ("slots", vp), ("order", vp), ("low_counts", vp), ("counts", vp)]
+
+
+class RoutesView(C.Structure):
+    _fields_ = [("ids", vp), ("rows", u32), ("top_k", u32), ("experts", u32), ("split", u32), ("first", u32), ("end", u32),
+                ("base", u32), ("scratch", vp), ("row_status", vp), ("out", Routes)]
+
+
+class Shape(C.Structure):
+    _fields_ = [("hidden", u32), ("inter", u32), ("experts", u32), ("top_k", u32), ("gate_type", u32), ("down_type", u32),
+                ("limit", f32)]
+
+
+class ExpertWeights(C.Structure):
+    _fields_ = [("gate", vp), ("up", vp), ("down", vp)]
+
+
+class GateUpView(C.Structure):
+    _fields_ = [("shape", Shape), ("weights", ExpertWeights), ("routes", Routes), ("max_union", u32), ("x", A8Rows), ("act", A8Rows),
+                ("gate_out", vp), ("up_out", vp), ("row_status", vp), ("summary", vp)]
+
+
+class DownView(C.Structure):
+    _fields_ = [("shape", Shape), ("weights", ExpertWeights), ("routes", Routes), ("max_union", u32), ("act", A8Rows), ("raw", vp),
+                ("summary", vp)]
+
+
+class CombineView(C.Structure):
+    _fields_ = [("raw", vp), ("shared", vp), ("weights", vp), ("ids", vp), ("order", vp), ("rows", u32), ("top_k", u32),
+                ("hidden", u32), ("form", u32), ("parts", u32), ("part_experts", u32), ("only_part", i32), ("y", vp),
+                ("y_bf16", vp), ("row_status", vp)]
+
+
+class LayerView(C.Structure):
+    _fields_ = [("shape", Shape), ("weights", ExpertWeights), ("rows", u32), ("x", A8Rows), ("ids", vp), ("route_weights", vp),
+                ("shared", vp), ("first", u32), ("end", u32), ("base", u32), ("combine_form", u32), ("parts", u32),
+                ("part_experts", u32), ("only_part", i32), ("raw", vp), ("y", vp), ("y_bf16", vp), ("row_status", vp),
+                ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32)]
+
+
+class FfnView(C.Structure):
+    _fields_ = [("shape", Shape), ("weights", ExpertWeights), ("policy", RoutePolicy), ("router_weight", vp), ("logit_bias", vp),
+                ("select_bias", vp), ("x", vp), ("x_is_bf16", u32), ("rows", u32), ("shared", vp), ("combine_form", u32),
+                ("parts", u32), ("part_experts", u32), ("y", vp), ("y_bf16", vp), ("ids", vp), ("route_weights", vp),
+                ("row_status", vp), ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32)]
+
+
+class DenseView(C.Structure):
+    _fields_ = [("shape", Shape), ("weights", ExpertWeights), ("rows", u32), ("x", A8Rows), ("y", vp), ("y_bf16", vp),
+                ("workspace", vp), ("workspace_bytes", u64)]
+
+
+# every symbol include/b200moe.h declares (tests check that the library exports each of them)
+EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_quantize_a8", "b200moe_q8_0_a8",
+           "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_gate_row_bytes",
+           "b200moe_down_row_bytes", "b200moe_expert_bytes", "b200moe_gate_up", "b200moe_down", "b200moe_combine",
+           "b200moe_canonical_sum", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
+           "b200moe_ffn", "b200moe_ffn_host", "b200moe_dense_ffn"]
+
+_lib = None
+
+
+def lib():
+    """The loaded C library. Raises when it has not been built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()')")
+        L = C.CDLL(LIB_PATH)
+        L.b200moe_last_error.restype = C.c_char_p
+        L.b200moe_launch_count.restype = u64
+        for n in ("b200moe_gate_row_bytes", "b200moe_down_row_bytes", "b200moe_expert_bytes"):
+            getattr(L, n).restype = u64
+            getattr(L, n).argtypes = [C.POINTER(Shape)]
+        L.b200moe_routes_scratch_words.restype = u64
+        L.b200moe_routes_scratch_words.argtypes = [u32, u32, u32]
+        for n in ("b200moe_layer_workspace_bytes", "b200moe_ffn_workspace_bytes"):
+            getattr(L, n).restype = u64
+            getattr(L, n).argtypes = [C.POINTER(Shape), u32]
+        for n, t in (("b200moe_quantize_a8", QuantizeA8View), ("b200moe_q8_0_a8", Q8A8View), ("b200moe_router", RouterView),
+                     ("b200moe_build_routes", RoutesView), ("b200moe_gate_up", GateUpView), ("b200moe_down", DownView),
+                     ("b200moe_combine", CombineView), ("b200moe_layer", LayerView), ("b200moe_ffn", FfnView),
+                     ("b200moe_dense_ffn", DenseView)):
+            getattr(L, n).restype = C.c_int
+            getattr(L, n).argtypes = [C.POINTER(t), vp]
+        L.b200moe_ffn_host.restype = C.c_int
+        L.b200moe_ffn_host.argtypes = [C.POINTER(FfnView), vp, vp, vp]
+        L.b200moe_canonical_sum.restype = C.c_int
+        L.b200moe_canonical_sum.argtypes = [vp, vp, vp, u64, vp, vp]
+        _lib = L
+    return _lib
+
+
+def check(rc):
+    if rc == OK:
+        return
+    text = lib().b200moe_last_error().decode()
+    if rc == ERR_INVALID_ARGUMENT:
+        raise InvalidArgument(rc, text)
+    raise B200MoeError(rc, text)
+
+
+def launch_count():
+    return int(lib().b200moe_launch_count())
+
+
+def ptr(t):
+    """Device (or pinned host) address of a torch tensor; None stays NULL."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(stream=None):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+def a8_rows(codes, deltas, sums, rows=None, width=None, stride=0):
+    return A8Rows(ptr(codes), ptr(deltas), ptr(sums), codes.shape[0] if rows is None else rows,
+                  codes.shape[1] if width is None else width, stride)

@@ -1,0 +1,463 @@
+// The C ABI (include/b200moe.h): host-side validation and composition. Argument errors are reported before anything
+// is enqueued; nothing here allocates, synchronises (except b200moe_ffn_host, which says so) or starts threads.
+#include <cmath>
+#include <cstring>
+#include <mutex>
+
+#include "kernels.cuh"
+
+namespace b200moe {
+
+std::string& last_error_slot() {
+    thread_local std::string text;
+    return text;
+}
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    last_error_slot() = buf;
+    return code;
+}
+std::atomic<u64>& launch_counter() {
+    static std::atomic<u64> n{0};
+    return n;
+}
+int after_launch(const char* what) {
+    launch_counter().fetch_add(1, std::memory_order_relaxed);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+    return B200MOE_OK;
+}
+bool device_ready() {
+    static std::once_flag once;
+    static bool ok = false;
+    static std::string why;
+    std::call_once(once, [] {
+        int n = 0;
+        cudaError_t e = cudaGetDeviceCount(&n);
+        if (e != cudaSuccess || n == 0) { why = std::string("no CUDA device: ") + cudaGetErrorString(e); cudaGetLastError(); return; }
+        int dev = 0;
+        cudaDeviceProp p{};
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&p, dev) != cudaSuccess) { why = "cannot query the CUDA device"; return; }
+        if (p.major != 10) { why = "this library holds sm_100a code only; device is sm_" + std::to_string(p.major * 10 + p.minor); return; }
+        ok = true;
+    });
+    if (!ok) fail(B200MOE_ERR_CUDA, "%s (there is no CPU fallback)", why.c_str());
+    return ok;
+}
+
+namespace {
+
+constexpr u32 kMaxExperts = 1024, kMaxTopK = 32;
+
+struct Carver {  // caller-owned workspace, 256-byte aligned sections
+    unsigned char* base;
+    u64 used = 0;
+    explicit Carver(void* p) : base(static_cast<unsigned char*>(p)) {}
+    template <class T>
+    T* take(u64 count) {
+        used = (used + 255) & ~u64(255);
+        T* p = base ? reinterpret_cast<T*>(base + used) : nullptr;
+        used += count * sizeof(T);
+        return p;
+    }
+};
+
+int check_shape(const b200moe_shape& s) {
+    B200_REQUIRE(s.gate_type == B200MOE_TYPE_Q8_0 || s.gate_type == B200MOE_TYPE_Q4_K, "gate/up type %u is not bound (Q8_0 = 8, Q4_K = 12)", s.gate_type);
+    B200_REQUIRE(s.down_type == B200MOE_TYPE_Q8_0 || s.down_type == B200MOE_TYPE_Q4_K, "down type %u is not bound (Q8_0 = 8, Q4_K = 12)", s.down_type);
+    B200_REQUIRE(!(s.gate_type == B200MOE_TYPE_Q8_0 && s.down_type == B200MOE_TYPE_Q4_K), "Q8_0 gate/up with Q4_K down has no declared contract");
+    B200_REQUIRE(s.hidden && s.inter && s.experts && s.top_k, "shape has a zero dimension");
+    B200_REQUIRE(s.experts <= kMaxExperts && s.top_k <= kMaxTopK && s.top_k <= s.experts, "need top_k <= 32, top_k <= experts <= 1024");
+    B200_REQUIRE(s.hidden % (s.gate_type == B200MOE_TYPE_Q4_K ? 256u : 32u) == 0, "hidden %u is not a whole number of gate/up blocks", s.hidden);
+    B200_REQUIRE(s.inter % (s.down_type == B200MOE_TYPE_Q4_K ? 256u : 32u) == 0, "inter %u is not a whole number of down blocks", s.inter);
+    B200_REQUIRE(s.hidden % 64 == 0, "hidden %u must be a multiple of 64", s.hidden);
+    return B200MOE_OK;
+}
+int check_a8(const b200moe_a8_rows& a, u32 rows, u32 width, bool need_sums, const char* what) {
+    const u32 stride = a.stride ? a.stride : a.width;
+    B200_REQUIRE(a.codes && a.deltas, "%s: A8 codes / deltas are null", what);
+    B200_REQUIRE(!need_sums || a.sums, "%s: A8 sums are required by this contract", what);
+    B200_REQUIRE(a.width == width && stride >= width && stride % 32 == 0, "%s: A8 width %u / stride %u do not fit width %u", what, a.width, stride, width);
+    B200_REQUIRE(a.rows >= rows, "%s: A8 view holds %u rows, %u needed", what, a.rows, rows);
+    B200_REQUIRE(aligned(a.codes, 16) && aligned(a.deltas, 8) && (!a.sums || aligned(a.sums, 8)), "%s: A8 pointers must be 16 / 8-byte aligned", what);
+    return B200MOE_OK;
+}
+int check_routes(const b200moe_routes& r) {
+    B200_REQUIRE(r.experts && r.begins && r.rows && r.slots && r.counts, "routes arrays are null");
+    return B200MOE_OK;
+}
+int check_policy(const b200moe_route_policy& p) {
+    B200_REQUIRE(p.experts && p.top_k && p.top_k <= p.experts, "route policy: need 0 < top_k <= experts");
+    B200_REQUIRE(p.experts <= kMaxExperts && p.top_k <= kMaxTopK, "route policy: experts <= 1024 and top_k <= 32");
+    B200_REQUIRE(p.score <= B200MOE_SCORE_SQRT_SOFTPLUS && p.key <= B200MOE_KEY_ORDERED_BITS && p.order <= B200MOE_ORDER_ASCENDING_ID, "route policy: unknown enum value");
+    B200_REQUIRE(p.n_group >= 1 && p.topk_group >= 1 && p.topk_group <= p.n_group, "route policy: need 1 <= topk_group <= n_group");
+    if (p.n_group > 1) {
+        B200_REQUIRE(p.n_group <= 32 && p.experts % p.n_group == 0, "route policy: n_group must divide experts and be <= 32");
+        B200_REQUIRE(p.experts / p.n_group >= 2 && u64(p.topk_group) * (p.experts / p.n_group) >= p.top_k, "route policy: the kept groups hold fewer than top_k experts");
+    }
+    return B200MOE_OK;
+}
+
+struct LayerScratch {
+    b200moe_routes routes;
+    u32* routes_scratch;
+    b200moe_a8_rows act;
+    float* raw;
+    u32* summary;
+    u32* row_status;
+    u32* aux;  // [capacity * top_k] words for callers of the layer pieces
+    u64 bytes;
+};
+LayerScratch carve_layer(void* ws, const b200moe_shape& s, u32 capacity) {
+    Carver c(ws);
+    const u64 n = u64(capacity) * s.top_k;
+    LayerScratch L{};
+    L.routes.experts = c.take<u32>(n);
+    L.routes.begins = c.take<u32>(n + 1);
+    L.routes.rows = c.take<u32>(n);
+    L.routes.slots = c.take<u32>(n);
+    L.routes.order = c.take<u32>(n);
+    L.routes.low_counts = c.take<u32>(capacity);
+    L.routes.counts = c.take<u32>(4);
+    L.routes_scratch = c.take<u32>(routes_scratch_words(capacity, s.top_k, s.experts));
+    L.act.codes = c.take<i8>(n * s.inter);
+    L.act.deltas = c.take<float>(n * (s.inter / 32));
+    L.act.sums = c.take<i32>(n * (s.inter / 32));
+    L.act.rows = static_cast<u32>(n); L.act.width = s.inter; L.act.stride = s.inter;
+    L.raw = c.take<float>(n * s.hidden);
+    L.summary = c.take<u32>(4);
+    L.row_status = c.take<u32>(capacity);
+    L.aux = c.take<u32>(n);
+    L.bytes = (c.used + 255) & ~u64(255);
+    return L;
+}
+
+struct FfnScratch {
+    b200moe_a8_rows x;
+    float* logits;
+    u32* ids;
+    float* weights;
+    void* x_dev;
+    float* y_dev;
+    void* layer;
+    u64 bytes;
+};
+FfnScratch carve_ffn(void* ws, const b200moe_shape& s, u32 capacity) {
+    Carver c(ws);
+    FfnScratch F{};
+    F.x.codes = c.take<i8>(u64(capacity) * s.hidden);
+    F.x.deltas = c.take<float>(u64(capacity) * (s.hidden / 32));
+    F.x.sums = c.take<i32>(u64(capacity) * (s.hidden / 32));
+    F.x.rows = capacity; F.x.width = s.hidden; F.x.stride = s.hidden;
+    F.logits = c.take<float>(u64(capacity) * s.experts);
+    F.ids = c.take<u32>(u64(capacity) * s.top_k);
+    F.weights = c.take<float>(u64(capacity) * s.top_k);
+    F.x_dev = c.take<float>(u64(capacity) * s.hidden);
+    F.y_dev = c.take<float>(u64(capacity) * s.hidden);
+    const u64 at = (c.used + 255) & ~u64(255);
+    F.layer = ws ? static_cast<unsigned char*>(ws) + at : nullptr;
+    F.bytes = at + carve_layer(nullptr, s, capacity).bytes;
+    return F;
+}
+
+int enqueue_gate_up(const b200moe_gate_up_view& v, cudaStream_t st) {
+    return v.shape.gate_type == B200MOE_TYPE_Q4_K ? launch_gate_up_q4k(v, st) : launch_gate_up_q8(v, st);
+}
+int enqueue_down(const b200moe_down_view& v, cudaStream_t st) {
+    if (v.shape.down_type == B200MOE_TYPE_Q4_K) return launch_down_q4k(v, st);
+    return v.shape.gate_type == B200MOE_TYPE_Q4_K ? launch_down_q8_chain4(v, st) : launch_down_q8(v, st);
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" {
+
+int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }
+const char* b200moe_last_error(void) { return last_error_slot().c_str(); }
+uint64_t b200moe_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
+
+uint64_t b200moe_gate_row_bytes(const b200moe_shape* s) { return s ? row_bytes_of(s->gate_type, s->hidden) : 0; }
+uint64_t b200moe_down_row_bytes(const b200moe_shape* s) { return s ? row_bytes_of(s->down_type, s->inter) : 0; }
+uint64_t b200moe_expert_bytes(const b200moe_shape* s) {
+    return s ? 2 * row_bytes_of(s->gate_type, s->hidden) * s->inter + row_bytes_of(s->down_type, s->inter) * s->hidden : 0;
+}
+
+int b200moe_quantize_a8(const b200moe_quantize_a8_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    B200_REQUIRE(v->width % 32 == 0, "A8 activation width must be a multiple of 32 (got %u)", v->width);
+    if (v->rows == 0 || v->width == 0) return B200MOE_OK;
+    B200_REQUIRE(v->x, "quantize_a8: x is null");
+    const u32 xs = v->x_stride ? v->x_stride : v->width;
+    B200_REQUIRE(xs >= v->width, "quantize_a8: x_stride %u is below the width %u", xs, v->width);
+    const u32 stride = v->out.stride ? v->out.stride : v->out.width;
+    B200_REQUIRE(v->out.codes && v->out.deltas, "quantize_a8: output codes / deltas are null");
+    B200_REQUIRE(v->out.width == v->width && stride >= v->width && stride % 32 == 0 && v->out.rows >= v->rows, "quantize_a8: output view does not fit rows %u x width %u", v->rows, v->width);
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    return launch_quantize_a8(*v, as_stream(stream));
+}
+
+int b200moe_q8_0_a8(const b200moe_q8a8_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    B200_REQUIRE(v->width % 32 == 0, "Q8_0 product width must be a multiple of 32 (got %u)", v->width);
+    if (v->count == 0 || v->x.rows == 0 || v->width == 0) return B200MOE_OK;
+    B200_REQUIRE(v->weight && v->out, "q8_0_a8: weight / out are null");
+    B200_REQUIRE(v->row_bytes >= v->width / 32 * kQ8Block, "q8_0_a8: row_bytes %u is below %u", v->row_bytes, v->width / 32 * kQ8Block);
+    if (int rc = check_a8(v->x, v->x.rows, v->width, false, "q8_0_a8 x")) return rc;
+    const u32 os = v->out_stride ? v->out_stride : v->count;
+    B200_REQUIRE(os >= v->count, "q8_0_a8: out_stride %u is below count %u", os, v->count);
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    return launch_q8_0_a8(*v, as_stream(stream));
+}
+
+int b200moe_router(const b200moe_router_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    if (int rc = check_policy(v->policy)) return rc;
+    B200_REQUIRE(v->logits && v->ids && v->weights, "router: logits / ids / weights are null");
+    B200_REQUIRE(!v->policy.selection_bias || v->bias, "router: the policy has a selection bias but bias is null");
+    if (v->x) {
+        B200_REQUIRE(v->weight && v->hidden, "router: weight is null or hidden is 0");
+        const u32 xs = v->x_stride ? v->x_stride : v->hidden;
+        B200_REQUIRE(xs >= v->hidden, "router: x_stride %u is below hidden %u", xs, v->hidden);
+    }
+    if (v->rows == 0) return B200MOE_OK;
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    if (v->x) if (int rc = launch_router_logits(*v, as_stream(stream))) return rc;
+    return launch_router_select(*v, as_stream(stream));
+}
+
+uint64_t b200moe_routes_scratch_words(uint32_t rows, uint32_t top_k, uint32_t experts) { return routes_scratch_words(rows, top_k, experts); }
+
+int b200moe_build_routes(const b200moe_routes_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    B200_REQUIRE(v->rows && v->top_k && v->ids, "routes need rows * top_k expert ids");
+    B200_REQUIRE(v->experts && v->experts <= kMaxExperts && v->top_k <= kMaxTopK && v->top_k <= v->experts, "routes: need top_k <= 32, top_k <= experts <= 1024");
+    B200_REQUIRE(v->end <= v->experts && (v->end == 0 || v->first < v->end) && v->base <= v->first, "routes: expert range [%u, %u) base %u is inconsistent", v->first, v->end, v->base);
+    if (int rc = check_routes(v->out)) return rc;
+    B200_REQUIRE(v->out.order && v->out.low_counts, "routes: order / low_counts are null");
+    B200_REQUIRE(u64(v->rows) * v->top_k <= 1024 || v->scratch, "routes: more than 1024 slots need scratch");
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    return launch_routes(*v, as_stream(stream));
+}
+
+int b200moe_gate_up(const b200moe_gate_up_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    if (int rc = check_shape(v->shape)) return rc;
+    if (int rc = check_routes(v->routes)) return rc;
+    B200_REQUIRE(v->weights.gate && v->weights.up && aligned(v->weights.gate, 16) && aligned(v->weights.up, 16), "gate_up: gate / up tensors must be non-null and 16-byte aligned");
+    B200_REQUIRE((v->gate_out == nullptr) == (v->up_out == nullptr), "gate_up: gate_out and up_out come together");
+    const bool q4k = v->shape.gate_type == B200MOE_TYPE_Q4_K;
+    if (int rc = check_a8(v->x, 0, v->shape.hidden, q4k, "gate_up x")) return rc;
+    if (int rc = check_a8(v->act, 0, v->shape.inter, v->shape.down_type == B200MOE_TYPE_Q4_K, "gate_up act")) return rc;
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    return enqueue_gate_up(*v, as_stream(stream));
+}
+
+int b200moe_down(const b200moe_down_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    if (int rc = check_shape(v->shape)) return rc;
+    if (int rc = check_routes(v->routes)) return rc;
+    B200_REQUIRE(v->weights.down && aligned(v->weights.down, 16) && v->raw, "down: the down tensor must be non-null and 16-byte aligned, raw non-null");
+    if (int rc = check_a8(v->act, 0, v->shape.inter, v->shape.down_type == B200MOE_TYPE_Q4_K, "down act")) return rc;
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    return enqueue_down(*v, as_stream(stream));
+}
+
+int b200moe_combine(const b200moe_combine_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    B200_REQUIRE(v->raw && v->weights && v->y, "combine: raw / weights / y are null");
+    B200_REQUIRE(v->top_k && v->top_k <= kMaxTopK && v->hidden, "combine: need 0 < top_k <= 32 and hidden > 0");
+    B200_REQUIRE(v->form <= B200MOE_COMBINE_FMA_SLOTS, "combine: unknown form %u", v->form);
+    if (v->form == B200MOE_COMBINE_PARTS) {
+        B200_REQUIRE(v->ids && v->order, "combine(parts): ids / order are null");
+        B200_REQUIRE(v->parts && v->part_experts && v->only_part < static_cast<int>(v->parts), "combine(parts): parts / part_experts / only_part are inconsistent");
+    }
+    if (v->rows == 0) return B200MOE_OK;
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    return launch_combine(*v, as_stream(stream));
+}
+
+int b200moe_canonical_sum(const float* a, const float* b, const float* c, uint64_t count, float* y, void* stream) {
+    B200_REQUIRE(a && b && y, "canonical_sum: a / b / y are null");
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    return launch_canonical_sum(a, b, c, count, y, as_stream(stream));
+}
+
+uint64_t b200moe_layer_workspace_bytes(const b200moe_shape* s, uint32_t capacity) {
+    if (!s || check_shape(*s)) return 0;
+    return carve_layer(nullptr, *s, capacity).bytes;
+}
+
+int b200moe_layer(const b200moe_layer_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    if (int rc = check_shape(v->shape)) return rc;
+    const b200moe_shape& s = v->shape;
+    B200_REQUIRE(v->rows <= v->capacity, "layer: rows %u exceed the workspace capacity %u", v->rows, v->capacity);
+    if (v->rows == 0) return B200MOE_OK;
+    B200_REQUIRE(v->ids && v->route_weights, "layer: ids / route_weights are null");
+    B200_REQUIRE(v->weights.gate && v->weights.up && v->weights.down, "layer: expert tensors are null");
+    B200_REQUIRE(aligned(v->weights.gate, 16) && aligned(v->weights.up, 16) && aligned(v->weights.down, 16), "layer: expert tensors must be 16-byte aligned");
+    if (int rc = check_a8(v->x, v->rows, s.hidden, s.gate_type == B200MOE_TYPE_Q4_K, "layer x")) return rc;
+    B200_REQUIRE(v->end <= s.experts && (v->end == 0 || v->first < v->end) && v->base <= v->first, "layer: expert range [%u, %u) base %u is inconsistent", v->first, v->end, v->base);
+    B200_REQUIRE(v->combine_form <= B200MOE_COMBINE_FMA_SLOTS, "layer: unknown combine form %u", v->combine_form);
+    if (v->y && v->combine_form == B200MOE_COMBINE_PARTS)
+        B200_REQUIRE(v->parts && v->part_experts && v->only_part < static_cast<int>(v->parts), "layer: parts / part_experts / only_part are inconsistent");
+    const LayerScratch L = carve_layer(v->workspace, s, v->capacity);
+    if (!v->workspace || v->workspace_bytes < L.bytes)
+        return fail(B200MOE_ERR_WORKSPACE, "layer: workspace of %llu bytes needed, %llu given", (unsigned long long)L.bytes, (unsigned long long)v->workspace_bytes);
+    B200_REQUIRE(aligned(v->workspace, 256), "layer: workspace must be 256-byte aligned");
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    cudaStream_t st = as_stream(stream);
+
+    u32* row_status = v->row_status ? v->row_status : L.row_status;
+    cudaError_t ce = cudaMemsetAsync(L.summary, 0, 16, st);
+    if (ce == cudaSuccess && !v->row_status) ce = cudaMemsetAsync(L.row_status, 0, sizeof(u32) * v->rows, st);
+    if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "layer: cudaMemsetAsync: %s", cudaGetErrorString(ce));
+
+    b200moe_routes_view rv{};
+    rv.ids = v->ids; rv.rows = v->rows; rv.top_k = s.top_k; rv.experts = s.experts;
+    rv.split = v->part_experts ? v->part_experts : s.experts / 2;
+    rv.first = v->first; rv.end = v->end; rv.base = v->base;
+    rv.scratch = L.routes_scratch; rv.row_status = row_status; rv.out = L.routes;
+    if (int rc = launch_routes(rv, st)) return rc;
+
+    const u32 span = (v->end ? v->end : s.experts) - v->first;
+    const u32 max_union = static_cast<u32>(std::min<u64>(u64(v->rows) * s.top_k, span));
+    float* raw = v->raw ? v->raw : L.raw;
+
+    b200moe_gate_up_view gu{};
+    gu.shape = s; gu.weights = v->weights; gu.routes = L.routes; gu.max_union = max_union;
+    gu.x = v->x; gu.act = L.act; gu.row_status = row_status; gu.summary = L.summary;
+    if (int rc = enqueue_gate_up(gu, st)) return rc;
+
+    b200moe_down_view dn{};
+    dn.shape = s; dn.weights = v->weights; dn.routes = L.routes; dn.max_union = max_union;
+    dn.act = L.act; dn.raw = raw; dn.summary = L.summary;
+    if (int rc = enqueue_down(dn, st)) return rc;
+
+    if (!v->y) return B200MOE_OK;
+    b200moe_combine_view cv{};
+    cv.raw = raw; cv.shared = v->shared; cv.weights = v->route_weights; cv.ids = v->ids; cv.order = L.routes.order;
+    cv.rows = v->rows; cv.top_k = s.top_k; cv.hidden = s.hidden; cv.form = v->combine_form;
+    cv.parts = v->parts; cv.part_experts = v->part_experts; cv.only_part = v->only_part;
+    cv.y = v->y; cv.y_bf16 = v->y_bf16;
+    cv.row_status = s.gate_type == B200MOE_TYPE_Q4_K ? row_status : nullptr;
+    return launch_combine(cv, st);
+}
+
+uint64_t b200moe_ffn_workspace_bytes(const b200moe_shape* s, uint32_t capacity) {
+    if (!s || check_shape(*s)) return 0;
+    return carve_ffn(nullptr, *s, capacity).bytes;
+}
+
+int b200moe_ffn(const b200moe_ffn_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    if (int rc = check_shape(v->shape)) return rc;
+    if (int rc = check_policy(v->policy)) return rc;
+    const b200moe_shape& s = v->shape;
+    B200_REQUIRE(v->policy.experts == s.experts && v->policy.top_k == s.top_k, "ffn: the route policy and the shape disagree on experts / top_k");
+    B200_REQUIRE(v->rows <= v->capacity, "ffn: rows %u exceed the workspace capacity %u", v->rows, v->capacity);
+    if (v->rows == 0) return B200MOE_OK;
+    B200_REQUIRE(v->x && v->y && v->router_weight, "ffn: x / y / router_weight are null");
+    B200_REQUIRE(!v->policy.selection_bias || v->select_bias, "ffn: the policy has a selection bias but select_bias is null");
+    const FfnScratch F = carve_ffn(v->workspace, s, v->capacity);
+    if (!v->workspace || v->workspace_bytes < F.bytes)
+        return fail(B200MOE_ERR_WORKSPACE, "ffn: workspace of %llu bytes needed, %llu given", (unsigned long long)F.bytes, (unsigned long long)v->workspace_bytes);
+    B200_REQUIRE(aligned(v->workspace, 256), "ffn: workspace must be 256-byte aligned");
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    cudaStream_t st = as_stream(stream);
+
+    b200moe_quantize_a8_view q{};
+    q.x = v->x; q.rows = v->rows; q.width = s.hidden; q.x_stride = s.hidden; q.x_is_bf16 = v->x_is_bf16; q.out = F.x;
+    if (int rc = launch_quantize_a8(q, st)) return rc;
+
+    // The router reads FP32 rows; bfloat16 activations are widened by the A8 kernel only, so route from an FP32 copy.
+    B200_REQUIRE(!v->x_is_bf16, "ffn: bfloat16 activations need the router logits from the caller (use b200moe_router + b200moe_layer)");
+    b200moe_router_view r{};
+    r.x = static_cast<const float*>(v->x); r.x_stride = s.hidden; r.rows = v->rows; r.hidden = s.hidden;
+    r.weight = v->router_weight; r.logit_bias = v->logit_bias; r.bias = v->select_bias; r.policy = v->policy;
+    r.logits = F.logits; r.scores = F.logits;
+    r.ids = v->ids ? v->ids : F.ids; r.weights = v->route_weights ? v->route_weights : F.weights;
+    if (int rc = launch_router_logits(r, st)) return rc;
+    if (int rc = launch_router_select(r, st)) return rc;
+
+    b200moe_layer_view lv{};
+    lv.shape = s; lv.weights = v->weights; lv.rows = v->rows; lv.x = F.x; lv.ids = r.ids; lv.route_weights = r.weights;
+    lv.shared = v->shared; lv.combine_form = v->combine_form; lv.parts = v->parts; lv.part_experts = v->part_experts; lv.only_part = -1;
+    lv.y = v->y; lv.y_bf16 = v->y_bf16; lv.row_status = v->row_status;
+    lv.workspace = F.layer; lv.workspace_bytes = v->workspace_bytes - (static_cast<unsigned char*>(F.layer) - static_cast<unsigned char*>(v->workspace));
+    lv.capacity = v->capacity; lv.grouped_min_rows = v->grouped_min_rows;
+    return b200moe_layer(&lv, stream);
+}
+
+int b200moe_ffn_host(const b200moe_ffn_view* v, const void* x_host, float* y_host, void* stream) {
+    B200_REQUIRE(v && x_host && y_host, "ffn_host: null view / host buffers");
+    if (int rc = check_shape(v->shape)) return rc;
+    B200_REQUIRE(v->rows <= v->capacity, "ffn_host: rows %u exceed the workspace capacity %u", v->rows, v->capacity);
+    const FfnScratch F = carve_ffn(v->workspace, v->shape, v->capacity);
+    if (!v->workspace || v->workspace_bytes < F.bytes)
+        return fail(B200MOE_ERR_WORKSPACE, "ffn_host: workspace of %llu bytes needed, %llu given", (unsigned long long)F.bytes, (unsigned long long)v->workspace_bytes);
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    cudaStream_t st = as_stream(stream);
+    const u64 n = u64(v->rows) * v->shape.hidden;
+    cudaError_t e = cudaMemcpyAsync(F.x_dev, x_host, n * (v->x_is_bf16 ? 2 : 4), cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "ffn_host: H2D copy: %s", cudaGetErrorString(e));
+    b200moe_ffn_view d = *v;
+    d.x = F.x_dev; d.y = F.y_dev;
+    if (int rc = b200moe_ffn(&d, stream)) return rc;
+    e = cudaMemcpyAsync(y_host, F.y_dev, n * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "ffn_host: D2H copy / synchronize: %s", cudaGetErrorString(e));
+    return B200MOE_OK;
+}
+
+int b200moe_dense_ffn(const b200moe_dense_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    B200_REQUIRE(v->shape.experts == 1 && v->shape.top_k == 1, "dense_ffn: shape.experts and shape.top_k must be 1");
+    if (int rc = check_shape(v->shape)) return rc;
+    const b200moe_shape& s = v->shape;
+    if (v->rows == 0) return B200MOE_OK;
+    B200_REQUIRE(v->y, "dense_ffn: y is null");
+    B200_REQUIRE(v->weights.gate && v->weights.up && v->weights.down, "dense_ffn: tensors are null");
+    B200_REQUIRE(aligned(v->weights.gate, 16) && aligned(v->weights.up, 16) && aligned(v->weights.down, 16), "dense_ffn: tensors must be 16-byte aligned");
+    if (int rc = check_a8(v->x, v->rows, s.hidden, s.gate_type == B200MOE_TYPE_Q4_K, "dense_ffn x")) return rc;
+    const LayerScratch L = carve_layer(v->workspace, s, v->rows);
+    if (!v->workspace || v->workspace_bytes < L.bytes)
+        return fail(B200MOE_ERR_WORKSPACE, "dense_ffn: workspace of %llu bytes needed, %llu given", (unsigned long long)L.bytes, (unsigned long long)v->workspace_bytes);
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    cudaStream_t st = as_stream(stream);
+    // every row is one entry of the single expert: ids = 0, so slot = row
+    cudaError_t ce = cudaMemsetAsync(L.aux, 0, sizeof(u32) * v->rows, st);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(L.summary, 0, 16, st);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(L.row_status, 0, sizeof(u32) * v->rows, st);
+    if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "dense_ffn: cudaMemsetAsync: %s", cudaGetErrorString(ce));
+    b200moe_routes_view rv{};
+    rv.ids = L.aux; rv.rows = v->rows; rv.top_k = 1; rv.experts = 1; rv.split = 1;
+    rv.scratch = L.routes_scratch; rv.row_status = L.row_status; rv.out = L.routes;
+    if (int rc = launch_routes(rv, st)) return rc;
+    b200moe_gate_up_view gu{};
+    gu.shape = s; gu.weights = v->weights; gu.routes = L.routes; gu.max_union = 1; gu.x = v->x; gu.act = L.act;
+    gu.row_status = L.row_status; gu.summary = L.summary;
+    if (int rc = enqueue_gate_up(gu, st)) return rc;
+    b200moe_down_view dn{};
+    dn.shape = s; dn.weights = v->weights; dn.routes = L.routes; dn.max_union = 1; dn.act = L.act; dn.raw = v->y; dn.summary = L.summary;
+    if (int rc = enqueue_down(dn, st)) return rc;
+    if (v->y_bf16) {
+        // bfloat16 RNE copy of y through the FMA_SLOTS combine with unit weights: fma(1, y, +0) = y exactly
+        float* ones = reinterpret_cast<float*>(L.aux);  // the ids are no longer read once the routes exist
+        if (int rc = launch_fill_u32(L.aux, 0x3f800000u, v->rows, st)) return rc;
+        b200moe_combine_view cv{};
+        cv.raw = v->y; cv.weights = ones; cv.rows = v->rows; cv.top_k = 1; cv.hidden = s.hidden; cv.form = B200MOE_COMBINE_FMA_SLOTS;
+        cv.only_part = -1; cv.y = L.raw; cv.y_bf16 = v->y_bf16;
+        return launch_combine(cv, st);
+    }
+    return B200MOE_OK;
+}
+
+}  // extern "C"

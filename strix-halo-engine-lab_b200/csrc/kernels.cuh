@@ -1,0 +1,36 @@
+// Internal launch interface between the C ABI layer (api.cu) and the kernel translation units. Every function
+// validates nothing (api.cu has done it), enqueues on `stream` and returns after_launch()'s status.
+#pragma once
+#include "common.cuh"
+
+namespace b200moe {
+
+// a8.cu
+int launch_quantize_a8(const b200moe_quantize_a8_view& v, cudaStream_t stream);
+
+// router.cu
+int launch_router_logits(const b200moe_router_view& v, cudaStream_t stream);
+int launch_router_select(const b200moe_router_view& v, cudaStream_t stream);
+
+// routes.cu
+u64 routes_scratch_words(u32 rows, u32 top_k, u32 experts);
+int launch_routes(const b200moe_routes_view& v, cudaStream_t stream);
+
+// gemv_q8.cu: Q8_0 x A8 products in the 32-lane-class contract (dense rows and the routed DS41-family experts)
+int launch_q8_0_a8(const b200moe_q8a8_view& v, cudaStream_t stream);
+int launch_gate_up_q8(const b200moe_gate_up_view& v, cudaStream_t stream);
+int launch_down_q8(const b200moe_down_view& v, cudaStream_t stream);
+
+// gemv_q4k.cu: Q4_K x A8 rows in the four-chain contract (routed Qwen-family experts; Q8_0 four-chain down)
+int launch_gate_up_q4k(const b200moe_gate_up_view& v, cudaStream_t stream);
+int launch_down_q4k(const b200moe_down_view& v, cudaStream_t stream);
+int launch_down_q8_chain4(const b200moe_down_view& v, cudaStream_t stream);
+
+// combine.cu
+int launch_combine(const b200moe_combine_view& v, cudaStream_t stream);
+int launch_canonical_sum(const float* a, const float* b, const float* c, u64 count, float* y, cudaStream_t stream);
+int launch_fill_u32(u32* p, u32 value, u64 count, cudaStream_t stream);
+// order[row][k] (slots in ascending expert id) for the PARTS combine when no routes were built
+int launch_row_order(const u32* ids, u32 rows, u32 top_k, u32* order, cudaStream_t stream);
+
+}  // namespace b200moe

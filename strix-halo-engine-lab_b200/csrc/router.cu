@@ -1,0 +1,221 @@
+// Router: logits in the declared dot order, score transform, k-pass top-k selection and weights.
+//
+// Contracts: strix::ds41::reference_router's product order (src/ds41_moe.cpp:72-82), the score transforms and the
+// selection / weight rule of the shared route policy (include/strix/moe/route_policy.hpp:80-156). Expert ids are only
+// reproducible when the choice values are bit-identical, so the logits keep the declared order: lane class l sums
+// elements l, l + 32, ... ascending with separate multiply and add, then the butterfly d = 16 .. 1.
+//
+// HBM: the logits kernel streams the FP32 router matrix once per RT-row tile ([experts][hidden] * 4 B); the select
+// kernel touches rows * experts * 4 B. Both are small beside the expert weights.
+#include "declared_math.cuh"
+#include "kernels.cuh"
+
+namespace b200moe {
+namespace {
+
+// One warp computes an RT x ET tile of logits over the whole hidden width; lane = lane class.
+template <int RT, int ET>
+__global__ void __launch_bounds__(128) router_logits_kernel(const float* __restrict__ x, u32 x_stride, u32 rows, u32 hidden,
+                                                            const float* __restrict__ w, u32 experts,
+                                                            const float* __restrict__ logit_bias, float* __restrict__ logits) {
+    const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const u32 e0 = (blockIdx.x * 4u + warp) * ET, r0 = blockIdx.y * RT;
+    if (e0 >= experts) return;
+    float acc[RT][ET];
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int e = 0; e < ET; ++e) acc[r][e] = 0.0f;
+    const float* xr[RT];
+    const float* wr[ET];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) xr[r] = x + u64(min(r0 + r, rows - 1)) * x_stride;
+#pragma unroll
+    for (int e = 0; e < ET; ++e) wr[e] = w + u64(min(e0 + e, experts - 1)) * hidden;
+#pragma unroll 4
+    for (u32 i = lane; i < hidden; i += 32) {
+        float xv[RT], wv[ET];
+#pragma unroll
+        for (int r = 0; r < RT; ++r) xv[r] = xr[r][i];
+#pragma unroll
+        for (int e = 0; e < ET; ++e) wv[e] = __ldg(wr[e] + i);
+#pragma unroll
+        for (int r = 0; r < RT; ++r)
+#pragma unroll
+            for (int e = 0; e < ET; ++e) acc[r][e] = __fadd_rn(acc[r][e], __fmul_rn(wv[e], xv[r]));
+    }
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int e = 0; e < ET; ++e) {
+            float z = butterfly32(acc[r][e]);
+            if (lane == 0 && r0 + r < rows && e0 + e < experts) {
+                if (logit_bias) z = __fadd_rn(z, logit_bias[e0 + e]);
+                logits[u64(r0 + r) * experts + e0 + e] = z;
+            }
+        }
+}
+
+__device__ __forceinline__ u32 ordered_key(float v) {  // route_policy.hpp:84-88
+    u32 u = __float_as_uint(v);
+    if (u == 0x80000000u) u = 0;
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+// True when candidate (a, ai) beats the current pick (b, bi) in a reduction over disjoint ascending scans: the
+// serial scan keeps the lower id on equal keys, so the parallel form orders by (key desc, id asc).
+__device__ __forceinline__ bool beats(u32 key, float a, u32 ai, float b, u32 bi) {
+    if (key == B200MOE_KEY_FLOAT_SERIAL) return a > b || (a == b && ai < bi);
+    const u32 ka = ordered_key(a), kb = ordered_key(b);
+    return ka > kb || (ka == kb && ai < bi);
+}
+
+constexpr u32 kNone = 0xffffffffu;
+
+// The serial scan of one selection pass (route_policy.hpp:104-114) over a short candidate list, skipping `skip`.
+__device__ __forceinline__ u32 serial_pick(u32 key, const float* c, u32 n, u32 skip) {
+    u32 pick = kNone;
+    float best = 0.0f;
+    for (u32 e = 0; e < n; ++e) {
+        if (e == skip) continue;
+        const bool better = key == B200MOE_KEY_FLOAT_SERIAL ? c[e] > best : ordered_key(c[e]) > ordered_key(best);
+        if (pick == kNone || better) { pick = e; best = c[e]; }
+    }
+    return pick;
+}
+
+// One k-pass over `n` candidates c[] (shared memory), lane-strided; `taken` holds this lane's taken candidates (bit j
+// = candidate lane + 32 j), `allowed_groups` masks candidates by group (per = candidates per group; all ones = no
+// mask). Returns the pick (kNone when nothing is left) to every lane and marks it taken.
+__device__ __forceinline__ u32 k_pass(u32 key, const float* c, u32 n, u32 lane, u32& taken, u32 allowed_groups, u32 per) {
+    // the serial scan's first candidate: lowest untaken allowed id
+    u32 first = kNone, pick = kNone;
+    float best = 0.0f;
+    for (u32 j = 0, e = lane; e < n; ++j, e += 32) {
+        if ((taken >> j) & 1u) continue;
+        if (!((allowed_groups >> (e / per)) & 1u)) continue;
+        if (first == kNone) first = e;
+        const float v = c[e];
+        if (key == B200MOE_KEY_FLOAT_SERIAL && v != v) continue;  // a NaN never replaces a pick
+        if (pick == kNone || beats(key, v, e, best, pick)) { pick = e; best = v; }
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+        const u32 of = __shfl_xor_sync(0xffffffffu, first, d);
+        first = min(first, of);
+        const u32 op = __shfl_xor_sync(0xffffffffu, pick, d);
+        const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+        if (op != kNone && (pick == kNone || beats(key, ob, op, best, pick))) { pick = op; best = ob; }
+    }
+    if (first == kNone) return kNone;
+    if (key == B200MOE_KEY_FLOAT_SERIAL) {
+        const float fv = c[first];
+        if (fv != fv) pick = first;  // a NaN taken as the first candidate stays (route_policy.hpp:11-12)
+    }
+    if (pick != kNone && (pick & 31u) == lane) taken |= 1u << (pick >> 5);
+    return pick;
+}
+
+// One warp per row. Shared memory per warp: scores[experts] + choice[experts] (+ group scores).
+__global__ void __launch_bounds__(128) router_select_kernel(const float* logits, float* scores_out,
+                                                            const float* __restrict__ bias, b200moe_route_policy p, u32 rows,
+                                                            u32* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float smem[];
+    const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const u32 row = blockIdx.x * 4u + warp;
+    if (row >= rows) return;
+    const u32 E = p.experts;
+    float* s = smem + warp * (2u * E + 32u);
+    float* c = s + E;
+    float* gs = c + E;
+    const float* z = logits + u64(row) * E;
+
+    if (p.score == B200MOE_SCORE_SOFTMAX) {  // route_policy.hpp:135-144
+        float m = -__uint_as_float(0x7f800000u);
+        for (u32 e = lane; e < E; e += 32) { const float v = z[e]; m = v > m ? v : m; }
+#pragma unroll
+        for (int d = 16; d; d >>= 1) { const float o = __shfl_xor_sync(0xffffffffu, m, d); m = o > m ? o : m; }
+        for (u32 e = lane; e < E; e += 32) s[e] = declared_exp(__fsub_rn(z[e], m));
+        __syncwarp();
+        float sum = 0.0f;
+        if (lane == 0) for (u32 e = 0; e < E; ++e) sum = __fadd_rn(sum, s[e]);  // ascending serial sum: the declared order
+        sum = __shfl_sync(0xffffffffu, sum, 0);
+        for (u32 e = lane; e < E; e += 32) s[e] = __fdiv_rn(s[e], sum);
+    } else if (p.score == B200MOE_SCORE_SIGMOID) {
+        for (u32 e = lane; e < E; e += 32) s[e] = sigmoid_score(z[e]);
+    } else {
+        for (u32 e = lane; e < E; e += 32) s[e] = sqrt_softplus_score(z[e]);
+    }
+    for (u32 e = lane; e < E; e += 32) c[e] = p.selection_bias ? __fadd_rn(s[e], bias[e]) : s[e];
+    __syncwarp();
+    if (scores_out) for (u32 e = lane; e < E; e += 32) scores_out[u64(row) * E + e] = s[e];
+
+    u32 allowed = 0xffffffffu, per = E;
+    if (p.n_group > 1) {  // group-limited extension (include/b200moe.h): group score = its two best choices summed
+        per = E / p.n_group;
+        if (lane < p.n_group) {
+            const float* cg = c + lane * per;
+            const u32 i0 = serial_pick(p.key, cg, per, kNone);
+            const u32 i1 = serial_pick(p.key, cg, per, i0);
+            const float b0 = cg[i0], b1 = cg[i1];
+            gs[lane] = __fadd_rn(b0, b1);
+        }
+        __syncwarp();
+        u32 gtaken = 0;
+        allowed = 0;
+        for (u32 k = 0; k < p.topk_group; ++k) {
+            const u32 g = k_pass(p.key, gs, p.n_group, lane, gtaken, 0xffffffffu, p.n_group);
+            if (g != kNone) allowed |= 1u << g;
+        }
+    }
+
+    u32 taken = 0, my_id = kNone;
+    for (u32 k = 0; k < p.top_k; ++k) {
+        const u32 pick = k_pass(p.key, c, E, lane, taken, allowed, per);
+        if (lane == k) my_id = pick;
+    }
+    if (p.order == B200MOE_ORDER_ASCENDING_ID) {  // rank sort of the (distinct) ids held one per lane
+        u32 rank = 0;
+        for (u32 k = 0; k < p.top_k; ++k) { const u32 o = __shfl_sync(0xffffffffu, my_id, k); rank += (o < my_id) ? 1u : 0u; }
+        u32 sorted = kNone;
+        for (u32 k = 0; k < p.top_k; ++k) {
+            const u32 o = __shfl_sync(0xffffffffu, my_id, k), orank = __shfl_sync(0xffffffffu, rank, k);
+            if (orank == lane) sorted = o;
+        }
+        my_id = sorted;
+    }
+    const float my_s = (lane < p.top_k && my_id != kNone) ? s[my_id] : 0.0f;
+    float sum = 0.0f;  // ((0 + s0) + s1) + ... in output order (route_policy.hpp:121-123)
+    for (u32 k = 0; k < p.top_k; ++k) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_s, k));
+    const bool renorm = p.renormalize && (p.top_k > 1 || p.renorm_single);
+    const float den = __fadd_rn(sum, p.renorm_eps);
+    if (lane < p.top_k) {
+        ids[u64(row) * p.top_k + lane] = my_id;
+        weights[u64(row) * p.top_k + lane] = __fmul_rn(renorm ? __fdiv_rn(my_s, den) : my_s, p.scale);
+    }
+}
+
+}  // namespace
+
+int launch_router_logits(const b200moe_router_view& v, cudaStream_t stream) {
+    const u32 E = v.policy.experts, xs = v.x_stride ? v.x_stride : v.hidden;
+    if (v.rows == 0) return B200MOE_OK;
+#define B200_LOGITS(RT, ET)                                                                                   \
+    router_logits_kernel<RT, ET><<<dim3((E + 4 * ET - 1) / (4 * ET), (v.rows + RT - 1) / RT), 128, 0, stream>>>( \
+        v.x, xs, v.rows, v.hidden, v.weight, E, v.logit_bias, v.logits)
+    if (v.rows == 1) B200_LOGITS(1, 1);
+    else if (v.rows == 2) B200_LOGITS(2, 1);
+    else if (v.rows <= 4) B200_LOGITS(4, 1);
+    else if (v.rows <= 16) B200_LOGITS(8, 1);
+    else B200_LOGITS(8, 4);
+#undef B200_LOGITS
+    return after_launch("router_logits");
+}
+
+int launch_router_select(const b200moe_router_view& v, cudaStream_t stream) {
+    if (v.rows == 0) return B200MOE_OK;
+    const u32 smem = 4u * (2u * v.policy.experts + 32u) * sizeof(float);
+    router_select_kernel<<<(v.rows + 3) / 4, 128, smem, stream>>>(v.logits, v.scores, v.bias, v.policy, v.rows, v.ids, v.weights);
+    return after_launch("router_select");
+}
+
+}  // namespace b200moe

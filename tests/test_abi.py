@@ -1,0 +1,98 @@
+"""CPU-side checks of the drop-in boundary: the C-ABI library loads, exports every symbol include/b200moe.h
+declares, its structures have the layout the Python binding assumes, argument errors are reported before any device
+work, and - with no GPU - compute entry points fail loudly instead of falling back to a CPU path."""
+import ctypes as C
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "b200moe.h")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import b200moe
+    if not os.path.exists(b200moe.LIB_PATH):
+        sys.path.insert(0, ROOT)
+        import __graft_entry__
+        __graft_entry__.build()
+    return b200moe.lib()
+
+
+def test_exports_match_header(lib):
+    import b200moe
+    text = open(HEADER).read()
+    declared = set(re.findall(r"\b(b200moe_[a-z0-9_]+)\s*\(", text))
+    assert declared == set(b200moe.EXPORTS), declared ^ set(b200moe.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.b200moe_abi_version() == 1
+
+
+def test_struct_layouts(tmp_path):
+    """sizeof of every view as the C compiler sees it equals the ctypes mirror."""
+    import b200moe
+    names = {"b200moe_a8_rows": b200moe.A8Rows, "b200moe_quantize_a8_view": b200moe.QuantizeA8View,
+             "b200moe_q8a8_view": b200moe.Q8A8View, "b200moe_route_policy": b200moe.RoutePolicy,
+             "b200moe_router_view": b200moe.RouterView, "b200moe_routes": b200moe.Routes,
+             "b200moe_routes_view": b200moe.RoutesView, "b200moe_shape": b200moe.Shape,
+             "b200moe_expert_weights": b200moe.ExpertWeights, "b200moe_gate_up_view": b200moe.GateUpView,
+             "b200moe_down_view": b200moe.DownView, "b200moe_combine_view": b200moe.CombineView,
+             "b200moe_layer_view": b200moe.LayerView, "b200moe_ffn_view": b200moe.FfnView,
+             "b200moe_dense_view": b200moe.DenseView}
+    src = tmp_path / "sizes.c"
+    body = "\n".join(f'    printf("{n} %zu\\n", sizeof({n}));' for n in names)
+    src.write_text(f'#include <stdio.h>\n#include "{HEADER}"\nint main(void) {{\n{body}\n    return 0;\n}}\n')
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", str(src), "-o", str(exe)], check=True)  # the header is plain C
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    for line in out.strip().splitlines():
+        n, size = line.split()
+        assert C.sizeof(names[n]) == int(size), n
+    # field offsets of the deepest view
+    src.write_text(f'#include <stdio.h>\n#include <stddef.h>\n#include "{HEADER}"\nint main(void) {{\n'
+                   '    printf("%zu %zu %zu %zu\\n", offsetof(b200moe_layer_view, x), offsetof(b200moe_layer_view, only_part),'
+                   ' offsetof(b200moe_layer_view, workspace_bytes), offsetof(b200moe_ffn_view, policy));\n    return 0;\n}\n')
+    subprocess.run(["gcc", "-std=c99", str(src), "-o", str(exe)], check=True)
+    a, b, c, d = (int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split())
+    assert (a, b, c) == (b200moe.LayerView.x.offset, b200moe.LayerView.only_part.offset, b200moe.LayerView.workspace_bytes.offset)
+    assert d == b200moe.FfnView.policy.offset
+
+
+def test_argument_errors_come_first(lib):
+    """Host-side validation needs no device: bad views are rejected with a message and nothing else happens."""
+    import b200moe
+    v = b200moe.QuantizeA8View(1, 1, 31, 31, 0, b200moe.A8Rows(1, 1, 1, 1, 31, 32), None)
+    assert lib.b200moe_quantize_a8(v, None) == b200moe.ERR_INVALID_ARGUMENT
+    assert b"multiple of 32" in lib.b200moe_last_error()
+    q = b200moe.Q8A8View(1, 68, 33, 0, 1, b200moe.A8Rows(1, 1, None, 1, 64, 64), 1, 1, 0)
+    assert lib.b200moe_q8_0_a8(q, None) == b200moe.ERR_INVALID_ARGUMENT
+    bad = b200moe.Shape(500, 256, 8, 2, 12, 12, float("inf"))
+    assert lib.b200moe_layer_workspace_bytes(bad, 4) == 0
+    assert lib.b200moe_layer(b200moe.LayerView(shape=bad), None) == b200moe.ERR_INVALID_ARGUMENT
+    grouped = b200moe.RoutePolicy(1, 1, 0, 0, 256, 8, 8, 9, 1, 1, 1e-20, 1.0)  # topk_group > n_group
+    r = b200moe.RouterView(policy=grouped, logits=1, ids=1, weights=1, bias=1)
+    assert lib.b200moe_router(r, None) == b200moe.ERR_INVALID_ARGUMENT
+    ok = b200moe.Shape(2048, 768, 128, 8, 12, 12, float("inf"))
+    assert lib.b200moe_gate_row_bytes(ok) == 8 * 144 and lib.b200moe_down_row_bytes(ok) == 3 * 144
+    assert lib.b200moe_expert_bytes(ok) == 2654208  # config 2's bytes per expert
+    assert lib.b200moe_layer_workspace_bytes(ok, 8) > 0
+    lv = b200moe.LayerView(shape=ok, rows=9, capacity=8)
+    assert lib.b200moe_layer(lv, None) == b200moe.ERR_INVALID_ARGUMENT and b"capacity" in lib.b200moe_last_error()
+
+
+def test_no_cpu_fallback(lib):
+    """Without a usable sm_100 device a well-formed compute call fails with ERR_CUDA."""
+    import torch
+    import b200moe
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    v = b200moe.QuantizeA8View(256, 1, 32, 32, 0, b200moe.A8Rows(256, 256, 256, 1, 32, 32), None)
+    assert lib.b200moe_quantize_a8(v, None) == b200moe.ERR_CUDA
+    assert b"no CPU fallback" in lib.b200moe_last_error()
+    with pytest.raises(b200moe.B200MoeError):
+        b200moe.check(lib.b200moe_quantize_a8(v, None))
