@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the block-quantized MoE FFN hot path on B200.
+
+A step = one MoE layer call (router -> A8 -> routes -> Q4_K gate/up + SwiGLU -> Q4_K down -> combine) over one
+batch of synthetic tokens. Default workload = BASELINE.json configs[1]: hidden 2048, 128 experts, top-8, inter 768,
+Q4_K experts, FP32 N(0,1) activations, batch 8 (the largest of the config's 1 / 4 / 8). Between steps the call
+rotates over several layers' worth of distinct expert weights (well over twice the 126 MB L2), so weight bytes come
+from HBM, not L2.
+
+One JSON line on stdout (rank 0):
+  value     whole-job tokens/s with inputs resident in HBM, steps replayed from a CUDA graph (device-timed, max over
+            ranks); `ms_per_step` likewise
+  e2e       the same metric through the host-buffer C-ABI call (pinned host activations in, host outputs back,
+            copies and the stream wait inside the timed region)
+  roofline  the dominant kernel (Q4_K gate/up GEMV): algorithmic bytes / its CUDA-event duration, against the
+            measured HBM copy peak
+  cpu_baseline  the reference's own CPU code (oracle/_ref) or the oracle port, on the host cores, bounded sample
+`--impl reference` times that CPU arm alone on the same config and prints the same line shape.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "strix-halo-engine-lab_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+CONFIGS = {
+    # name: hidden, experts, top_k, inter, gate_type, down_type
+    "c2": dict(hidden=2048, experts=128, top_k=8, inter=768, gate_type=12, down_type=12,
+               desc="MoE decode layer, Q4_K experts: hidden 2048, 128 experts, top-8, inter 768"),
+}
+METRIC = "MoE-layer tokens/s (Q4_K decode)"
+UNIT = "tokens/s"
+L2_BYTES = 126 * 2 ** 20
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """SM clock and throttle reasons sampled through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+            while not self.stop_flag:
+                self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                r = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.reasons |= {n for bit, n in names.items() if r & bit}
+                time.sleep(0.005)
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def make_layer(cfg, seed):
+    from b200moe import synth
+    rng = np.random.default_rng(seed)
+    g, u, d = synth.expert_tensors(rng, cfg["experts"], cfg["hidden"], cfg["inter"], cfg["gate_type"], cfg["down_type"])
+    return g, u, d, synth.router_weight(rng, cfg["experts"], cfg["hidden"])
+
+
+def expert_bytes(cfg):
+    gate_row = cfg["hidden"] // 256 * 144
+    down_row = cfg["inter"] // 256 * 144
+    return 2 * cfg["inter"] * gate_row, cfg["hidden"] * down_row
+
+
+def cpu_arm(cfg, batch, target_s, threads=None):
+    """Times the reference's own CPU code (oracle/_ref) - or the oracle port when that build is absent - on one
+    layer of the workload. Returns (tokens/s, description dict)."""
+    from oracle import loader as O
+    from b200moe import synth
+    g, u, d, rw = make_layer(cfg, 1000)
+    x = synth.activations(np.random.default_rng(7), batch, cfg["hidden"])
+    threads = threads or os.cpu_count() or 1
+    if O.Ref.available():
+        ref = O.Ref()
+        args = (g, u, d, cfg["experts"], cfg["hidden"], cfg["inter"], cfg["top_k"], rw, x, threads)
+        sec, _, _ = ref.time_layer_q4k(*args, 1)
+        reps = max(1, min(5000, int(target_s / max(sec, 1e-6))))
+        sec, _, _ = ref.time_layer_q4k(*args, reps)
+        kind, isa = "reference", ref.isa()
+    else:
+        orc = O.Oracle()
+        sh = O.Shape(cfg["hidden"], cfg["inter"], cfg["experts"], cfg["top_k"], cfg["gate_type"], cfg["down_type"], float("inf"))
+        pol = O.softmax_policy(cfg["experts"], cfg["top_k"])
+        t0 = time.perf_counter()
+        orc.ffn(sh, pol, g, u, d, rw, x, O.COMBINE_FMA_SLOTS)
+        one = time.perf_counter() - t0
+        reps = max(1, int(target_s / max(one, 1e-6)))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            orc.ffn(sh, pol, g, u, d, rw, x, O.COMBINE_FMA_SLOTS)
+        sec = time.perf_counter() - t0
+        kind, isa = "port", "scalar"
+    value = batch * reps / sec
+    return value, {"value": value, "unit": UNIT, "cores": threads, "kind": kind,
+                   "sample": f"{reps} layer calls of batch {batch} on one layer's weights ({sec:.1f} s, isa {isa}, synthetic exp tables)"}
+
+
+def reference_arm(args, cfg, rank, world):
+    if rank != 0:
+        return
+    batch = args.batch
+    total = max(1, args.steps + args.warmup)
+    value, base = cpu_arm(cfg, batch, target_s=min(60.0, 0.02 * total + 15.0))
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1000.0 * batch / value, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {batch}", "l2": "host arm"},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=4, help="distinct layers of weights rotated between steps")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.workload]
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        return reference_arm(args, cfg, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    import b200moe
+    from b200moe import ops, synth
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    K, W, B, L = args.steps, max(args.warmup, 3), args.batch, args.layers
+    H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
+    shape = ops.make_shape(H, I, E, TK, cfg["gate_type"], cfg["down_type"])
+    policy = ops.softmax_policy(E, TK)
+    layers = []
+    for li in range(L):
+        g, u, d, rw = make_layer(cfg, 1000 + li + 100 * rank)
+        layers.append(ops.MoeFfn(shape, policy, *(torch.from_numpy(a).to(dev) for a in (g, u, d, rw)), capacity=B,
+                                 combine_form=b200moe.COMBINE_FMA_SLOTS))
+    rng = np.random.default_rng(7 + rank)
+    NX = 16
+    xs_host = [torch.from_numpy(synth.activations(rng, B, H)).pin_memory() for _ in range(NX)]
+    xs = [x.to(dev) for x in xs_host]
+    y = torch.empty((B, H), dtype=torch.float32, device=dev)
+    ys_host = torch.empty((B, H), dtype=torch.float32).pin_memory()
+    ids = torch.empty((B, TK), dtype=torch.int32, device=dev)
+    wts = torch.empty((B, TK), dtype=torch.float32, device=dev)
+    lib = b200moe.lib()
+
+    def views(events=None):
+        return [layers[s % L]._view(B, xs[s % NX], y, ids, wts, events=events[s] if events else None) for s in range(L * NX)]
+
+    plain = views()
+    stream = torch.cuda.current_stream()
+
+    def run_plain(n, vs, first=0):
+        sp = stream.cuda_stream
+        for s in range(n):
+            rc = lib.b200moe_ffn(C.byref(vs[(first + s) % len(vs)]), sp)
+            if rc:
+                b200moe.check(rc)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    run_plain(W, plain)
+    torch.cuda.synchronize()
+    # distinct experts per step (realised routing) -> algorithmic bytes of the gate/up kernel
+    gate_up_bytes, down_bytes = expert_bytes(cfg)
+    uniq = []
+    for s in range(L * NX):
+        run_plain(1, plain, s)
+        torch.cuda.synchronize()
+        uniq.append(len(np.unique(ids.cpu().numpy())))
+    uniq = np.array(uniq, dtype=np.float64)
+
+    # ---- timed region 1: K steps replayed from CUDA graphs (value) ---------------------------------------------
+    G = min(K, L * NX)
+    cap_stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    launches0 = b200moe.launch_count()
+    with torch.cuda.graph(graph, stream=cap_stream):
+        sp = torch.cuda.current_stream().cuda_stream
+        for s in range(G):
+            rc = lib.b200moe_ffn(C.byref(plain[s]), sp)
+            if rc:
+                b200moe.check(rc)
+    launches_per_step = (b200moe.launch_count() - launches0) / G
+    replays, rest = divmod(K, G)
+    for _ in range(3):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    run_plain(rest, plain)
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+
+    # ---- timed region 2: the same K steps launched one by one, CUDA events around the gate/up kernel -------------
+    evs = []
+    for s in range(L * NX):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    taps = [ops.MoeFfn.stage_events([None, None, a.cuda_event, b.cuda_event, None, None, None, None]) for a, b in evs]
+    tapped = views(taps)
+    kern_ms, plain_ms_total, done = [], 0.0, 0
+    while done < K:
+        n = min(K - done, L * NX)
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        run_plain(n, tapped)
+        p1.record()
+        torch.cuda.synchronize()
+        plain_ms_total += p0.elapsed_time(p1)
+        kern_ms += [evs[s][0].elapsed_time(evs[s][1]) for s in range(n)]
+        done += n
+    kern_ms = np.array(kern_ms)
+    steps_uniq = np.array([uniq[s % (L * NX)] for s in range(K)])
+
+    # ---- timed region 3: end to end through the host-buffer call -------------------------------------------------
+    host_views = [layers[s % L]._view(B, None, None) for s in range(L * NX)]
+
+    def run_host(n):
+        sp = stream.cuda_stream
+        for s in range(n):
+            rc = lib.b200moe_ffn_host(C.byref(host_views[s % len(host_views)]), xs_host[s % NX].data_ptr(), ys_host.data_ptr(), sp)
+            if rc:
+                b200moe.check(rc)
+
+    run_host(min(W, 50))
+    barrier()
+    h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    h0.record()
+    run_host(K)
+    h1.record()
+    barrier()
+    host_ms = max(h0.elapsed_time(h1), 1000.0 * (time.perf_counter() - t0))
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+
+    t = torch.tensor([dev_ms, host_ms, plain_ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, host_ms, plain_ms_total = (float(v) for v in t.cpu())
+    tokens = B * K * world
+    value = tokens / (dev_ms / 1000.0)
+    peak, peak_kind = peaks()
+    algo_bytes = float(np.mean(steps_uniq)) * gate_up_bytes + B * H * 1.25  # weights of the distinct experts + the A8 rows
+    achieved = algo_bytes / (float(np.mean(kern_ms)) * 1e-3) / 1e9
+    step_bytes = float(np.mean(steps_uniq)) * (gate_up_bytes + down_bytes) + E * H * 4
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {B}", "parallelism": f"replicas x{world}" if world > 1 else "1 gpu",
+                   "l2": f"rotating {L} layers of distinct expert weights ({L * E * (gate_up_bytes + down_bytes) / 2**20:.0f} MiB) > 2 x {L2_BYTES // 2**20} MiB L2",
+                   "launch": "CUDA graph replay of the per-step kernel sequence"},
+        "clocks": sampler.summary(),
+        "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
+                "ms_per_step": host_ms / K},
+        "gpu_launches": int(round(launches_per_step * K)),
+        "roofline": {"kernel": "gate_up_q4k_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy", "traffic": None,
+                     "algorithmic_bytes_per_launch": algo_bytes, "avg_launch_us": float(np.mean(kern_ms)) * 1000.0,
+                     "distinct_experts_per_step": float(np.mean(steps_uniq))},
+        "extra": {"step_hbm_gbs_graph": step_bytes / (dev_ms / K * 1e-3) / 1e9, "ms_per_step_no_graph": plain_ms_total / K,
+                  "tokens_per_s_no_graph": tokens / (plain_ms_total / 1000.0), "launches_per_step": launches_per_step},
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            _, base = cpu_arm(cfg, B, target_s=12.0)
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

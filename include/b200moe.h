@@ -282,6 +282,10 @@ typedef struct b200moe_layer_view {
     uint64_t workspace_bytes;
     uint32_t capacity;          /* rows <= capacity */
     uint32_t grouped_min_rows;
+    /* Timing taps (optional, like MoeRange::wait_begin / wait_end, include/strix/cuda/ds41_moe.hpp:172-179): eight
+     * cudaEvent_t handles recorded on the stream before / after the stages routes, gate/up, down, combine
+     * ([2 * stage], [2 * stage + 1]). NULL: nothing is recorded. */
+    void* const* stage_events;
 } b200moe_layer_view;
 uint64_t b200moe_layer_workspace_bytes(const b200moe_shape* shape, uint32_t capacity);
 int b200moe_layer(const b200moe_layer_view* view, void* stream);
@@ -308,6 +312,7 @@ typedef struct b200moe_ffn_view {
     uint64_t workspace_bytes;    /* b200moe_ffn_workspace_bytes(shape, capacity) */
     uint32_t capacity;
     uint32_t grouped_min_rows;
+    void* const* stage_events;   /* passed to the layer (see b200moe_layer_view) */
 } b200moe_ffn_view;
 uint64_t b200moe_ffn_workspace_bytes(const b200moe_shape* shape, uint32_t capacity);
 int b200moe_ffn(const b200moe_ffn_view* view, void* stream);

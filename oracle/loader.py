@@ -254,6 +254,7 @@ class Ref:
         L.ref_evaluate_row_q4k.restype = C.c_float
         L.ref_evaluate_down_row.restype = C.c_float
         L.ref_cpu_isa.restype = C.c_char_p
+        L.ref_expert_isa.restype = C.c_char_p
         L.ref_time_layer_q4k.restype = C.c_double
 
     def quantize_a8(self, x, ds41=False):
@@ -419,4 +420,5 @@ class Ref:
         return sec, y, ids
 
     def isa(self):
-        return self.lib.ref_cpu_isa().decode()
+        """Row-kernel table of the routed-expert executor on this host."""
+        return self.lib.ref_expert_isa().decode()

@@ -92,6 +92,11 @@ float ref_router_score(float z) { return strix::ds41::router_score(z); }
 float ref_swiglu_clamped(float g, float u, float limit) { return strix::ds41::swiglu_clamped(g, u, limit); }
 float ref_gfx1151_expf(float x) { return zero_exp().expf(x); }
 const char* ref_cpu_isa() { return strix::cpu::isa_name(strix::cpu::select(strix::cpu::caps()).isa); }
+// Name of the routed-expert row-kernel table the executor binds on this host ("scalar", "avx2", "avx2+vnni").
+const char* ref_expert_isa() {
+    static const std::string name = [] { ex::Executor e(1, zero_exp(), true); return std::string(e.isa()); }();
+    return name.c_str();
+}
 
 // strix::cpu reference table (src/cpu/core/reference.cpp). 1 = rejected (std::invalid_argument).
 int ref_quantize_a8(const float* x, std::size_t width, i8* codes, float* deltas, i32* sums) {

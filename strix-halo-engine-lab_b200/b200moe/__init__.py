@@ -94,14 +94,15 @@ class LayerView(C.Structure):
     _fields_ = [("shape", Shape), ("weights", ExpertWeights), ("rows", u32), ("x", A8Rows), ("ids", vp), ("route_weights", vp),
                 ("shared", vp), ("first", u32), ("end", u32), ("base", u32), ("combine_form", u32), ("parts", u32),
                 ("part_experts", u32), ("only_part", i32), ("raw", vp), ("y", vp), ("y_bf16", vp), ("row_status", vp),
-                ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32)]
+                ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32), ("stage_events", vp)]
 
 
 class FfnView(C.Structure):
     _fields_ = [("shape", Shape), ("weights", ExpertWeights), ("policy", RoutePolicy), ("router_weight", vp), ("logit_bias", vp),
                 ("select_bias", vp), ("x", vp), ("x_is_bf16", u32), ("rows", u32), ("shared", vp), ("combine_form", u32),
                 ("parts", u32), ("part_experts", u32), ("y", vp), ("y_bf16", vp), ("ids", vp), ("route_weights", vp),
-                ("row_status", vp), ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32)]
+                ("row_status", vp), ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32),
+                ("stage_events", vp)]
 
 
 class DenseView(C.Structure):

@@ -143,7 +143,7 @@ class MoeLayer:
         raw = torch.zeros((rows * self.shape.top_k, self.shape.hidden), dtype=torch.float32, device=dev) if want_raw else None
         v = LayerView(self.shape, ExpertWeights(ptr(self.gate), ptr(self.up), ptr(self.down)), rows, a8_rows(*x_a8), ptr(ids),
                       ptr(route_weights), ptr(shared), first, end, base, self.combine_form, self.parts, self.part_experts, only_part,
-                      ptr(raw), ptr(y), ptr(yb), ptr(row_status), ptr(self.ws), self.ws_bytes, self.capacity, self.grouped_min_rows)
+                      ptr(raw), ptr(y), ptr(yb), ptr(row_status), ptr(self.ws), self.ws_bytes, self.capacity, self.grouped_min_rows, None)
         check(lib().b200moe_layer(C.byref(v), stream_ptr()))
         out = [y]
         if want_raw:
@@ -169,11 +169,17 @@ class MoeFfn:
             check(lib().b200moe_ffn(C.byref(FfnView(shape=shape, policy=policy)), None))
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=gate.device)
 
-    def _view(self, rows, x, y, ids=None, wts=None, shared=None, row_status=None):
+    @staticmethod
+    def stage_events(handles):
+        """Eight cudaEvent_t values (ints or None) as the array the views point to; the caller keeps it alive."""
+        return (C.c_void_p * 8)(*handles)
+
+    def _view(self, rows, x, y, ids=None, wts=None, shared=None, row_status=None, events=None):
+        ev = C.cast(events, C.c_void_p) if events is not None else None
         return FfnView(self.shape, ExpertWeights(ptr(self.gate), ptr(self.up), ptr(self.down)), self.policy, ptr(self.router_weight),
                        ptr(self.logit_bias), ptr(self.select_bias), ptr(x), 0, rows, ptr(shared), self.combine_form, self.parts,
                        self.part_experts, ptr(y), None, ptr(ids), ptr(wts), ptr(row_status), ptr(self.ws), self.ws_bytes,
-                       self.capacity, self.grouped_min_rows)
+                       self.capacity, self.grouped_min_rows, ev)
 
     def __call__(self, x, y=None, shared=None, want_routes=False, row_status=None):
         rows = x.shape[0]

@@ -325,7 +325,12 @@ int b200moe_layer(const b200moe_layer_view* v, void* stream) {
     rv.split = v->part_experts ? v->part_experts : s.experts / 2;
     rv.first = v->first; rv.end = v->end; rv.base = v->base;
     rv.scratch = L.routes_scratch; rv.row_status = row_status; rv.out = L.routes;
+    auto tap = [&](int i) {
+        if (v->stage_events && v->stage_events[i]) cudaEventRecord(static_cast<cudaEvent_t>(v->stage_events[i]), st);
+    };
+    tap(0);
     if (int rc = launch_routes(rv, st)) return rc;
+    tap(1);
 
     const u32 span = (v->end ? v->end : s.experts) - v->first;
     const u32 max_union = static_cast<u32>(std::min<u64>(u64(v->rows) * s.top_k, span));
@@ -334,12 +339,16 @@ int b200moe_layer(const b200moe_layer_view* v, void* stream) {
     b200moe_gate_up_view gu{};
     gu.shape = s; gu.weights = v->weights; gu.routes = L.routes; gu.max_union = max_union;
     gu.x = v->x; gu.act = L.act; gu.row_status = row_status; gu.summary = L.summary;
+    tap(2);
     if (int rc = enqueue_gate_up(gu, st)) return rc;
+    tap(3);
 
     b200moe_down_view dn{};
     dn.shape = s; dn.weights = v->weights; dn.routes = L.routes; dn.max_union = max_union;
     dn.act = L.act; dn.raw = raw; dn.summary = L.summary;
+    tap(4);
     if (int rc = enqueue_down(dn, st)) return rc;
+    tap(5);
 
     if (!v->y) return B200MOE_OK;
     b200moe_combine_view cv{};
@@ -348,7 +357,10 @@ int b200moe_layer(const b200moe_layer_view* v, void* stream) {
     cv.parts = v->parts; cv.part_experts = v->part_experts; cv.only_part = v->only_part;
     cv.y = v->y; cv.y_bf16 = v->y_bf16;
     cv.row_status = s.gate_type == B200MOE_TYPE_Q4_K ? row_status : nullptr;
-    return launch_combine(cv, st);
+    tap(6);
+    const int rc = launch_combine(cv, st);
+    tap(7);
+    return rc;
 }
 
 uint64_t b200moe_ffn_workspace_bytes(const b200moe_shape* s, uint32_t capacity) {
@@ -392,7 +404,7 @@ int b200moe_ffn(const b200moe_ffn_view* v, void* stream) {
     lv.shared = v->shared; lv.combine_form = v->combine_form; lv.parts = v->parts; lv.part_experts = v->part_experts; lv.only_part = -1;
     lv.y = v->y; lv.y_bf16 = v->y_bf16; lv.row_status = v->row_status;
     lv.workspace = F.layer; lv.workspace_bytes = v->workspace_bytes - (static_cast<unsigned char*>(F.layer) - static_cast<unsigned char*>(v->workspace));
-    lv.capacity = v->capacity; lv.grouped_min_rows = v->grouped_min_rows;
+    lv.capacity = v->capacity; lv.grouped_min_rows = v->grouped_min_rows; lv.stage_events = v->stage_events;
     return b200moe_layer(&lv, stream);
 }
 
