@@ -2,6 +2,7 @@
 // is enqueued; nothing here allocates, synchronises (except b200moe_ffn_host, which says so) or starts threads.
 #include <cmath>
 #include <cstring>
+#include <map>
 #include <mutex>
 
 #include "kernels.cuh"
@@ -47,6 +48,21 @@ bool device_ready() {
     });
     if (!ok) fail(B200MOE_ERR_CUDA, "%s (there is no CPU fallback)", why.c_str());
     return ok;
+}
+
+int ensure_dynamic_smem(const void* kernel, u32 bytes) {
+    if (bytes <= 48u * 1024u) return B200MOE_OK;
+    static std::mutex m;
+    static std::map<std::pair<int, const void*>, u32> granted;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(m);
+    u32& have = granted[{dev, kernel}];
+    if (bytes <= have) return B200MOE_OK;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "cudaFuncSetAttribute(dynamic smem %u): %s", bytes, cudaGetErrorString(e));
+    have = bytes;
+    return B200MOE_OK;
 }
 
 namespace {
@@ -164,11 +180,14 @@ FfnScratch carve_ffn(void* ws, const b200moe_shape& s, u32 capacity) {
     return F;
 }
 
-int enqueue_gate_up(const b200moe_gate_up_view& v, cudaStream_t st) {
-    return v.shape.gate_type == B200MOE_TYPE_Q4_K ? launch_gate_up_q4k(v, st) : launch_gate_up_q8(v, st);
+// Plan by window size, chosen on the host from the row count (no environment reads inside numerical code): decode
+// windows of Q4_K experts take the persistent bulk-copy form, everything else the plain per-block form.
+int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st) {
+    if (v.shape.gate_type != B200MOE_TYPE_Q4_K) return launch_gate_up_q8(v, st);
+    return stream_gate_up_fits(v, rows) ? launch_gate_up_q4k_stream(v, rows, st) : launch_gate_up_q4k(v, st);
 }
-int enqueue_down(const b200moe_down_view& v, cudaStream_t st) {
-    if (v.shape.down_type == B200MOE_TYPE_Q4_K) return launch_down_q4k(v, st);
+int enqueue_down(const b200moe_down_view& v, u32 rows, cudaStream_t st) {
+    if (v.shape.down_type == B200MOE_TYPE_Q4_K) return stream_down_fits(v, rows) ? launch_down_q4k_stream(v, rows, st) : launch_down_q4k(v, st);
     return v.shape.gate_type == B200MOE_TYPE_Q4_K ? launch_down_q8_chain4(v, st) : launch_down_q8(v, st);
 }
 
@@ -256,7 +275,7 @@ int b200moe_gate_up(const b200moe_gate_up_view* v, void* stream) {
     if (int rc = check_a8(v->x, 0, v->shape.hidden, q4k, "gate_up x")) return rc;
     if (int rc = check_a8(v->act, 0, v->shape.inter, v->shape.down_type == B200MOE_TYPE_Q4_K, "gate_up act")) return rc;
     if (!device_ready()) return B200MOE_ERR_CUDA;
-    return enqueue_gate_up(*v, as_stream(stream));
+    return enqueue_gate_up(*v, v->x.rows, as_stream(stream));
 }
 
 int b200moe_down(const b200moe_down_view* v, void* stream) {
@@ -266,7 +285,7 @@ int b200moe_down(const b200moe_down_view* v, void* stream) {
     B200_REQUIRE(v->weights.down && aligned(v->weights.down, 16) && v->raw, "down: the down tensor must be non-null and 16-byte aligned, raw non-null");
     if (int rc = check_a8(v->act, 0, v->shape.inter, v->shape.down_type == B200MOE_TYPE_Q4_K, "down act")) return rc;
     if (!device_ready()) return B200MOE_ERR_CUDA;
-    return enqueue_down(*v, as_stream(stream));
+    return enqueue_down(*v, v->act.rows / v->shape.top_k, as_stream(stream));
 }
 
 int b200moe_combine(const b200moe_combine_view* v, void* stream) {
@@ -294,7 +313,12 @@ uint64_t b200moe_layer_workspace_bytes(const b200moe_shape* s, uint32_t capacity
     return carve_layer(nullptr, *s, capacity).bytes;
 }
 
-int b200moe_layer(const b200moe_layer_view* v, void* stream) {
+static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_ready);
+int b200moe_layer(const b200moe_layer_view* v, void* stream) { return layer_impl(v, stream, false); }
+
+// routes_ready: the caller (b200moe_ffn) has already built the routes of v->ids into this workspace and cleared the
+// status words (the fused select + routes launch of decode windows).
+static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_ready) {
     B200_REQUIRE(v, "null view");
     if (int rc = check_shape(v->shape)) return rc;
     const b200moe_shape& s = v->shape;
@@ -316,9 +340,11 @@ int b200moe_layer(const b200moe_layer_view* v, void* stream) {
     cudaStream_t st = as_stream(stream);
 
     u32* row_status = v->row_status ? v->row_status : L.row_status;
-    cudaError_t ce = cudaMemsetAsync(L.summary, 0, 16, st);
-    if (ce == cudaSuccess && !v->row_status) ce = cudaMemsetAsync(L.row_status, 0, sizeof(u32) * v->rows, st);
-    if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "layer: cudaMemsetAsync: %s", cudaGetErrorString(ce));
+    if (!routes_ready) {
+        cudaError_t ce = cudaMemsetAsync(L.summary, 0, 16, st);
+        if (ce == cudaSuccess && !v->row_status) ce = cudaMemsetAsync(L.row_status, 0, sizeof(u32) * v->rows, st);
+        if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "layer: cudaMemsetAsync: %s", cudaGetErrorString(ce));
+    }
 
     b200moe_routes_view rv{};
     rv.ids = v->ids; rv.rows = v->rows; rv.top_k = s.top_k; rv.experts = s.experts;
@@ -329,7 +355,7 @@ int b200moe_layer(const b200moe_layer_view* v, void* stream) {
         if (v->stage_events && v->stage_events[i]) cudaEventRecord(static_cast<cudaEvent_t>(v->stage_events[i]), st);
     };
     tap(0);
-    if (int rc = launch_routes(rv, st)) return rc;
+    if (!routes_ready) if (int rc = launch_routes(rv, st)) return rc;
     tap(1);
 
     const u32 span = (v->end ? v->end : s.experts) - v->first;
@@ -340,14 +366,14 @@ int b200moe_layer(const b200moe_layer_view* v, void* stream) {
     gu.shape = s; gu.weights = v->weights; gu.routes = L.routes; gu.max_union = max_union;
     gu.x = v->x; gu.act = L.act; gu.row_status = row_status; gu.summary = L.summary;
     tap(2);
-    if (int rc = enqueue_gate_up(gu, st)) return rc;
+    if (int rc = enqueue_gate_up(gu, v->rows, st)) return rc;
     tap(3);
 
     b200moe_down_view dn{};
     dn.shape = s; dn.weights = v->weights; dn.routes = L.routes; dn.max_union = max_union;
     dn.act = L.act; dn.raw = raw; dn.summary = L.summary;
     tap(4);
-    if (int rc = enqueue_down(dn, st)) return rc;
+    if (int rc = enqueue_down(dn, v->rows, st)) return rc;
     tap(5);
 
     if (!v->y) return B200MOE_OK;
@@ -385,19 +411,36 @@ int b200moe_ffn(const b200moe_ffn_view* v, void* stream) {
     if (!device_ready()) return B200MOE_ERR_CUDA;
     cudaStream_t st = as_stream(stream);
 
-    b200moe_quantize_a8_view q{};
-    q.x = v->x; q.rows = v->rows; q.width = s.hidden; q.x_stride = s.hidden; q.x_is_bf16 = v->x_is_bf16; q.out = F.x;
-    if (int rc = launch_quantize_a8(q, st)) return rc;
-
-    // The router reads FP32 rows; bfloat16 activations are widened by the A8 kernel only, so route from an FP32 copy.
+    // The router reads FP32 rows (bfloat16 activations are widened by the A8 kernel only).
     B200_REQUIRE(!v->x_is_bf16, "ffn: bfloat16 activations need the router logits from the caller (use b200moe_router + b200moe_layer)");
+    b200moe_quantize_a8_view q{};
+    q.x = v->x; q.rows = v->rows; q.width = s.hidden; q.x_stride = s.hidden; q.x_is_bf16 = 0; q.out = F.x;
     b200moe_router_view r{};
     r.x = static_cast<const float*>(v->x); r.x_stride = s.hidden; r.rows = v->rows; r.hidden = s.hidden;
     r.weight = v->router_weight; r.logit_bias = v->logit_bias; r.bias = v->select_bias; r.policy = v->policy;
     r.logits = F.logits; r.scores = F.logits;
     r.ids = v->ids ? v->ids : F.ids; r.weights = v->route_weights ? v->route_weights : F.weights;
-    if (int rc = launch_router_logits(r, st)) return rc;
-    if (int rc = launch_router_select(r, st)) return rc;
+    // Decode windows: one launch for A8 + logits + selection + routes; 9..32 rows: selection and routes share a launch.
+    const LayerScratch L = carve_layer(F.layer, s, v->capacity);
+    const bool one_launch = prologue_fusable(r, s.top_k);
+    const bool fused = one_launch || select_routes_fusable(r, s.top_k);
+    b200moe_routes_view rv{};
+    if (fused) {
+        u32* row_status = v->row_status ? v->row_status : L.row_status;
+        cudaError_t ce = cudaMemsetAsync(L.summary, 0, 16, st);  // summary word, prologue ticket
+        if (ce == cudaSuccess && !v->row_status) ce = cudaMemsetAsync(L.row_status, 0, sizeof(u32) * v->rows, st);
+        if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "ffn: cudaMemsetAsync: %s", cudaGetErrorString(ce));
+        rv.ids = r.ids; rv.rows = v->rows; rv.top_k = s.top_k; rv.experts = s.experts;
+        rv.split = v->part_experts ? v->part_experts : s.experts / 2;
+        rv.scratch = L.routes_scratch; rv.row_status = row_status; rv.out = L.routes;
+    }
+    if (one_launch) {
+        if (int rc = launch_prologue(r, q, rv, L.summary + 1, st)) return rc;
+    } else {
+        if (int rc = launch_router_logits(r, st, &q)) return rc;
+        if (fused) { if (int rc = launch_select_routes(r, rv, st)) return rc; }
+        else if (int rc = launch_router_select(r, st)) return rc;
+    }
 
     b200moe_layer_view lv{};
     lv.shape = s; lv.weights = v->weights; lv.rows = v->rows; lv.x = F.x; lv.ids = r.ids; lv.route_weights = r.weights;
@@ -405,7 +448,7 @@ int b200moe_ffn(const b200moe_ffn_view* v, void* stream) {
     lv.y = v->y; lv.y_bf16 = v->y_bf16; lv.row_status = v->row_status;
     lv.workspace = F.layer; lv.workspace_bytes = v->workspace_bytes - (static_cast<unsigned char*>(F.layer) - static_cast<unsigned char*>(v->workspace));
     lv.capacity = v->capacity; lv.grouped_min_rows = v->grouped_min_rows; lv.stage_events = v->stage_events;
-    return b200moe_layer(&lv, stream);
+    return layer_impl(&lv, stream, fused);
 }
 
 int b200moe_ffn_host(const b200moe_ffn_view* v, const void* x_host, float* y_host, void* stream) {
@@ -456,10 +499,10 @@ int b200moe_dense_ffn(const b200moe_dense_view* v, void* stream) {
     b200moe_gate_up_view gu{};
     gu.shape = s; gu.weights = v->weights; gu.routes = L.routes; gu.max_union = 1; gu.x = v->x; gu.act = L.act;
     gu.row_status = L.row_status; gu.summary = L.summary;
-    if (int rc = enqueue_gate_up(gu, st)) return rc;
+    if (int rc = enqueue_gate_up(gu, v->rows, st)) return rc;
     b200moe_down_view dn{};
     dn.shape = s; dn.weights = v->weights; dn.routes = L.routes; dn.max_union = 1; dn.act = L.act; dn.raw = v->y; dn.summary = L.summary;
-    if (int rc = enqueue_down(dn, st)) return rc;
+    if (int rc = enqueue_down(dn, v->rows, st)) return rc;
     if (v->y_bf16) {
         // bfloat16 RNE copy of y through the FMA_SLOTS combine with unit weights: fma(1, y, +0) = y exactly
         float* ones = reinterpret_cast<float*>(L.aux);  // the ids are no longer read once the routes exist

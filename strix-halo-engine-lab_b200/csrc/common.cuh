@@ -33,6 +33,8 @@ std::atomic<u64>& launch_counter();
 int after_launch(const char* what);
 // True once a device with the sm_100a image is usable; otherwise records why and returns false.
 bool device_ready();
+// Raises a kernel's dynamic shared memory limit when `bytes` needs more than it has been given so far (per device).
+int ensure_dynamic_smem(const void* kernel, u32 bytes);
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 inline bool aligned(const void* p, std::size_t a) { return (reinterpret_cast<std::uintptr_t>(p) % a) == 0; }

@@ -312,11 +312,7 @@ __global__ void __launch_bounds__(256) down_q8_chain4_kernel(b200moe_down_view v
 
 template <class K>
 int set_smem(K kernel, u32 bytes) {
-    if (bytes > 48u * 1024u) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
-        if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "cudaFuncSetAttribute(smem %u): %s", bytes, cudaGetErrorString(e));
-    }
-    return B200MOE_OK;
+    return ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), bytes);
 }
 inline int lanes_per_row(u32 nblocks) { return nblocks > 4 ? 32 : (nblocks > 2 ? 16 : 8); }
 

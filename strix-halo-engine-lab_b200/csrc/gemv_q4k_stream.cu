@@ -1,0 +1,550 @@
+// Routed experts, Qwen A8 family, decode form on Blackwell: persistent GEMVs fed by the bulk-copy engine.
+//
+// Same arithmetic as gemv_q4k.cu (the contract of src/cpu/core/routed_expert.hpp:9-15, bit for bit); what changes is how
+// the bytes reach the SM and how few instructions touch each byte.
+//
+//  * One persistent CTA per SM walks work items (expert, 32-output group | 64 hidden outputs) round-robin.
+//  * A producer warp streams weight rows - contiguous, 16-byte aligned GGUF bytes - into a ring of shared-memory stages
+//    with cp.async.bulk (global -> shared, completion counted on an mbarrier). A stage holds one OCTET = 8 weight rows;
+//    rows are laid down with a stride whose 16-byte count is odd, which makes the consumers' 128-bit reads conflict free.
+//  * Each consumer warp owns whole octets (octet n goes to warp n mod W): lane = (row of the octet, pair p). A lane walks
+//    its row's super-blocks in ascending order, so the serial chain acc_p += pair_p needs no shuffle at all; the final
+//    (a0 + a1) + (a2 + a3) is two xor-shuffles. Integer -> float conversions use the exact 2^23 magic-number form.
+//  * gate/up: the last warp to finish an item's eight octets (a shared-memory counter) runs SwiGLU + the A8 rule.
+//
+// Every wait on an mbarrier is bounded: after kWaitLimit polls the waiter raises an abort flag, all roles stop waiting
+// (they still walk their loops, doing no work), the producer drains the copies it has in flight (bounded), bit 30 of the
+// job summary is set and the kernel returns: the host reads a status, the GPU never hangs.
+//
+// Roofline: HBM. Algorithmic bytes per item = 64 rows x K / 256 x 144.
+#include "declared_math.cuh"
+#include "kernels.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kR = 4;             // entries per pass over an octet
+constexpr u32 kMaxWarps = 16;     // consumer warps at most
+constexpr u32 kWaitLimit = 1u << 22;
+constexpr u32 kAbortBit = 1u << 30;
+constexpr u32 kOctetsPerItem = 8;
+constexpr u32 kProducers = 4;       // producer warps
+
+// ---- PTX: mbarrier + bulk copy ---------------------------------------------------------------------------------------
+__device__ __forceinline__ u32 saddr(const void* p) { return static_cast<u32>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(u64* bar, u32 count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(u64* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(u64* bar, u32 bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(u64* bar, u32 parity) {
+    u32 ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(saddr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false when the limit ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(u64* bar, u32 parity, volatile u32* abort_flag) {
+    for (u32 i = 0; i < kWaitLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 127u) == 127u) {
+            if (*abort_flag) return false;
+            __nanosleep(32);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(saddr(dst)),
+                 "l"(src), "r"(bytes), "r"(saddr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ int dp4a_us(u32 a, u32 b, int c) {  // unsigned bytes of a times signed bytes of b
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// Exact int -> float for |v| < 2^22 without the conversion pipe: (1.5 * 2^23 + v) - 1.5 * 2^23.
+__device__ __forceinline__ float small_int_to_float(int v) { return __fsub_rn(__int_as_float(0x4b400000 + v), 12582912.0f); }
+
+// ---- shared plan -----------------------------------------------------------------------------------------------------
+struct StreamPlan {
+    u32 stages;        // ring depth (octets)
+    u32 warps;         // consumer warps
+    u32 row_bytes;     // bytes of one weight row
+    u32 row_stride;    // stride of a row inside a stage (odd count of 16-byte units)
+    u32 stage_bytes;   // 8 * row_stride
+    u32 n_chunks;      // items per expert
+    u32 chunk_magic;   // floor(2^32 / n_chunks) + 1: item / n_chunks = umulhi(item, magic) for item < 2^20
+    u32 item_slots;    // power of two: item state ring (gate/up)
+    u32 max_entries;   // bound of the entries of one expert (the window's rows)
+    u32 x_rows;        // rows of the A8 input copied to shared memory (gate/up)
+};
+
+struct Ring {
+    unsigned char* data;
+    u64* full;
+    u64* empty;
+    volatile u32* abort_flag;
+};
+
+__device__ __forceinline__ void ring_init(const Ring& r, u32 stages) {
+    if (threadIdx.x == 0) {
+        for (u32 s = 0; s < stages; ++s) { mbar_init(&r.full[s], 1); mbar_init(&r.empty[s], 1); }
+        *r.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+}
+
+// The producer warps: kProducers warps share the octet stream (octet q goes to producer q mod kProducers); lanes 0..7
+// of a producer issue the eight row copies of its octet. A bulk copy costs its issuing thread a few hundred cycles
+// whatever its size, so one thread - or one warp - issuing 1 KB row copies tops out near half of HBM bandwidth;
+// four warps of eight lanes reach it (measured on B200: 1 warp 3.0 TB/s, 2 warps 5.8, 4 warps 6.5).
+// `row_of(item, octet)` gives the first of the octet's 8 consecutive weight rows.
+template <class RowOf>
+__device__ __forceinline__ void produce(const Ring& ring, const StreamPlan& plan, u32 n_items, u32 pw, RowOf row_of) {
+    const u32 lane = threadIdx.x & 31u;
+    const bool one_copy = plan.row_stride == plan.row_bytes;  // rows already conflict free: one copy per octet
+    const u32 local_octets = (n_items > blockIdx.x ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0) * kOctetsPerItem;
+    u32 slot = pw % plan.stages, phase = (pw / plan.stages) & 1u, q = pw;
+    bool ok = true;
+    for (; q < local_octets; q += kProducers) {
+        if (q >= plan.stages) ok = mbar_wait(&ring.empty[slot], phase ^ 1u, ring.abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const unsigned char* src = row_of(blockIdx.x + (q >> 3) * gridDim.x, q & 7u);
+        unsigned char* dst = ring.data + u64(slot) * plan.stage_bytes;
+        if (lane == 0) mbar_expect_tx(&ring.full[slot], 8u * plan.row_bytes);
+        __syncwarp();
+        if (one_copy) {
+            if (lane == 0) bulk_g2s(dst, src, 8u * plan.row_bytes, &ring.full[slot]);
+        } else if (lane < 8) {
+            bulk_g2s(dst + lane * plan.row_stride, src + u64(lane) * plan.row_bytes, plan.row_bytes, &ring.full[slot]);
+        }
+        slot += kProducers;
+        while (slot >= plan.stages) { slot -= plan.stages; phase ^= 1u; }
+    }
+    if (!ok && lane == 0) {  // wait (bounded) for this producer's copies still in flight before the CTA retires
+        const u32 back = (plan.stages + kProducers - 1) / kProducers * kProducers;  // keeps n on this producer's octets
+        for (u32 n = q > back ? q - back : pw; n < q; n += kProducers)
+            for (u32 i = 0; i < (kWaitLimit >> 6); ++i)
+                if (mbar_try_wait(&ring.full[n % plan.stages], (n / plan.stages) & 1u)) break;
+    }
+}
+
+// item -> (union expert j, chunk) without a hardware division.
+__device__ __forceinline__ void split_item(const StreamPlan& plan, u32 item, u32* j, u32* chunk) {
+    *j = plan.n_chunks == 1 ? item : __umulhi(item, plan.chunk_magic);
+    *chunk = item - *j * plan.n_chunks;
+}
+// A consumer warp's walk over its octets q = warp, warp + W, ...: ring slot and phase kept incrementally.
+struct Cursor {
+    u32 q, slot, phase;
+    __device__ __forceinline__ void advance(const StreamPlan& plan) {
+        q += plan.warps;
+        slot += plan.warps;
+        while (slot >= plan.stages) { slot -= plan.stages; phase ^= 1u; }
+    }
+};
+
+// Entry metadata of the item an octet belongs to, fetched one octet ahead so that its two dependent global loads
+// (begins[j], then the first entries' ids) hide behind the current octet's arithmetic.
+struct Meta { u32 chunk, eb, ne; };
+__device__ __forceinline__ Meta load_meta(const StreamPlan& plan, const b200moe_routes& routes, u32 q) {
+    u32 j;
+    Meta m;
+    split_item(plan, blockIdx.x + (q >> 3) * gridDim.x, &j, &m.chunk);
+    m.eb = __ldg(routes.begins + j);
+    m.ne = __ldg(routes.begins + j + 1) - m.eb;
+    return m;
+}
+__device__ __forceinline__ void load_first(const u32* __restrict__ ids, const Meta& m, u32* first) {
+#pragma unroll
+    for (int r = 0; r < kR; ++r) first[r] = __ldg(ids + m.eb + min(u32(r), m.ne - 1u));
+}
+
+// ---- the row rule over one octet -----------------------------------------------------------------------------------
+// Decoded factors of one super-block for pair p: D / DM of groups 2p (l) and 2p + 1 (h).
+struct Factors { float Dl, DMl, Dh, DMh; };
+__device__ __forceinline__ Factors q4k_factors(const uint4& hdr, u32 p) {
+    const float d = half_bits_to_float(hdr.x & 0xffffu), dm = half_bits_to_float(hdr.x >> 16);
+    // the eight 6-bit scales / mins, four per word (routed_expert.cpp:65-71, vectorised over the four bytes)
+    const u32 sc_lo = hdr.y & 0x3f3f3f3fu, mn_lo = hdr.z & 0x3f3f3f3fu;
+    const u32 sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+    const u32 mn_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+    const u32 scw = p < 2u ? sc_lo : sc_hi, mnw = p < 2u ? mn_lo : mn_hi;
+    const u32 sh = 16u * (p & 1u);
+    const int s0 = (scw >> sh) & 0xffu, s1 = (scw >> (sh + 8u)) & 0xffu;
+    const int m0 = (mnw >> sh) & 0xffu, m1 = (mnw >> (sh + 8u)) & 0xffu;
+    Factors f;
+    f.Dl = __fmul_rn(d, small_int_to_float(s0));
+    f.Dh = __fmul_rn(d, small_int_to_float(s1));
+    f.DMl = __fmul_rn(dm, small_int_to_float(m0));
+    f.DMh = __fmul_rn(dm, small_int_to_float(m1));
+    return f;
+}
+__device__ __forceinline__ void dots(const uint4& q0, const uint4& q1, const uint4& c0, const uint4& c1, const uint4& c2, const uint4& c3,
+                                     int* lo, int* hi) {
+    int l = 0, h = 0;
+    l = __dp4a(static_cast<int>(q0.x & 0x0f0f0f0fu), static_cast<int>(c0.x), l);
+    l = __dp4a(static_cast<int>(q0.y & 0x0f0f0f0fu), static_cast<int>(c0.y), l);
+    l = __dp4a(static_cast<int>(q0.z & 0x0f0f0f0fu), static_cast<int>(c0.z), l);
+    l = __dp4a(static_cast<int>(q0.w & 0x0f0f0f0fu), static_cast<int>(c0.w), l);
+    l = __dp4a(static_cast<int>(q1.x & 0x0f0f0f0fu), static_cast<int>(c1.x), l);
+    l = __dp4a(static_cast<int>(q1.y & 0x0f0f0f0fu), static_cast<int>(c1.y), l);
+    l = __dp4a(static_cast<int>(q1.z & 0x0f0f0f0fu), static_cast<int>(c1.z), l);
+    l = __dp4a(static_cast<int>(q1.w & 0x0f0f0f0fu), static_cast<int>(c1.w), l);
+    // high nibbles in place: bytes 16 * q (unsigned) times signed codes = 16 * dot, an exact shift away
+    h = dp4a_us(q0.x & 0xf0f0f0f0u, c2.x, h);
+    h = dp4a_us(q0.y & 0xf0f0f0f0u, c2.y, h);
+    h = dp4a_us(q0.z & 0xf0f0f0f0u, c2.z, h);
+    h = dp4a_us(q0.w & 0xf0f0f0f0u, c2.w, h);
+    h = dp4a_us(q1.x & 0xf0f0f0f0u, c3.x, h);
+    h = dp4a_us(q1.y & 0xf0f0f0f0u, c3.y, h);
+    h = dp4a_us(q1.z & 0xf0f0f0f0u, c3.z, h);
+    h = dp4a_us(q1.w & 0xf0f0f0f0u, c3.w, h);
+    *lo = l;
+    *hi = h >> 4;
+}
+__device__ __forceinline__ float pair_value(const Factors& f, int lo, int hi, float El, float Eh, float Sl, float Sh) {
+    const float xl = __fmul_rn(El, __fsub_rn(__fmul_rn(f.Dl, small_int_to_float(lo)), __fmul_rn(f.DMl, Sl)));
+    const float xh = __fmul_rn(Eh, __fsub_rn(__fmul_rn(f.Dh, small_int_to_float(hi)), __fmul_rn(f.DMh, Sh)));
+    return __fadd_rn(xl, xh);
+}
+// (a0 + a1) + (a2 + a3) over the four pair lanes of a row; every lane of the row gets the value.
+__device__ __forceinline__ float tree4(float a) {
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    return __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+}
+
+// ---- gate/up ---------------------------------------------------------------------------------------------------------
+// A8 input rows in shared memory, per row: codes[H] with the two 16-byte chunks of every 32-byte half swapped for
+// pairs 2 and 3 (bank spread), then per (super-block, pair) 16 bytes {E_2p, E_2p+1, float(S_2p), float(S_2p+1)}.
+__device__ __forceinline__ void copy_x_rows(const b200moe_a8_rows& x, u32 rows, u32 H, unsigned char* dst, u32 nthreads) {
+    const u32 stride = x.stride ? x.stride : x.width, row_bytes = H + H / 4;
+    for (u32 r = 0; r < rows; ++r) {
+        const uint4* src = reinterpret_cast<const uint4*>(x.codes + u64(r) * stride);
+        uint4* d = reinterpret_cast<uint4*>(dst + u64(r) * row_bytes);
+        for (u32 c = threadIdx.x; c < H / 16; c += nthreads) d[c ^ ((c >> 3) & 1u)] = src[c];
+        float4* es = reinterpret_cast<float4*>(dst + u64(r) * row_bytes + H);
+        for (u32 g2 = threadIdx.x; g2 < H / 64; g2 += nthreads) {
+            const float2 e = *reinterpret_cast<const float2*>(x.deltas + u64(r) * (stride / 32) + 2 * g2);
+            const int2 s = *reinterpret_cast<const int2*>(x.sums + u64(r) * (stride / 32) + 2 * g2);
+            es[g2] = make_float4(e.x, e.y, static_cast<float>(s.x), static_cast<float>(s.y));
+        }
+    }
+}
+
+__global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) gate_up_q4k_stream_kernel(b200moe_gate_up_view v, StreamPlan plan) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const u32 H = v.shape.hidden, I = v.shape.inter, nblocks = H / 256;
+    const u32 ME = plan.max_entries;
+    unsigned char* at = smem + u64(plan.stages) * plan.stage_bytes;
+    float* s_gu = reinterpret_cast<float*>(at);                       // [item_slots][2][ME][32]
+    at += u64(plan.item_slots) * 2 * ME * 32 * 4;
+    u64* bars = reinterpret_cast<u64*>(at);
+    at += 2 * plan.stages * 8;
+    u32* s_done = reinterpret_cast<u32*>(at);                         // [item_slots] octets finished
+    at += plan.item_slots * 4;
+    u32* s_flag = reinterpret_cast<u32*>(at);
+    at += 16;
+    at = smem + ((at - smem + 15) & ~size_t(15));
+    unsigned char* x_copy = at;
+    const Ring ring{smem, bars, bars + plan.stages, s_flag};
+    for (u32 i = threadIdx.x; i < plan.item_slots; i += blockDim.x) s_done[i] = 0;
+    ring_init(ring, plan.stages);
+
+    const u32 warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const u32 n_items = v.routes.counts[0] * plan.n_chunks;
+    const u64 row_bytes = plan.row_bytes;
+
+    if (warp >= plan.warps) {  // ------------------------------------------------------------- producer warps
+        produce(ring, plan, n_items, warp - plan.warps, [&](u32 item, u32 o) {
+            u32 j, gx;
+            split_item(plan, item, &j, &gx);
+            const u64 row = u64(v.routes.experts[j]) * I + 32u * gx + 8u * (o & 3u);
+            return (o < 4 ? v.weights.gate : v.weights.up) + row * row_bytes;
+        });
+        return;
+    }
+
+    // ------------------------------------------------------------------------------------------ consumer warps
+    copy_x_rows(v.x, plan.x_rows, H, x_copy, plan.warps * 32);
+    asm volatile("bar.sync 1, %0;" ::"r"(plan.warps * 32) : "memory");
+    const u32 x_row_bytes = H + H / 4;
+    const u32 rsub = lane >> 2, p = lane & 3u;
+    const u32 swz = p >> 1;  // chunk swap of the staged codes
+    const u32 act_stride = v.act.stride ? v.act.stride : v.act.width;
+    const u32 local_octets = (n_items > blockIdx.x ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0) * kOctetsPerItem;
+    bool ok = true;
+    Meta m{};
+    u32 first[kR];
+    if (warp < local_octets) { m = load_meta(plan, v.routes, warp); load_first(v.routes.rows, m, first); }
+    for (Cursor cur{warp, warp % plan.stages, (warp / plan.stages) & 1u}; cur.q < local_octets; cur.advance(plan)) {
+        const u32 slot = cur.slot, local_item = cur.q >> 3, o = cur.q & 7u;
+        const bool has_next = cur.q + plan.warps < local_octets;
+        Meta nm{};
+        if (has_next) nm = load_meta(plan, v.routes, cur.q + plan.warps);
+        const u32 gx = m.chunk, eb = m.eb, ne = min(m.ne, ME);
+        const u32 islot = local_item & (plan.item_slots - 1);
+        float* s_g = s_gu + u64(islot) * 2 * ME * 32;
+        float* s_u = s_g + ME * 32;
+        if (ok) ok = mbar_wait(&ring.full[slot], cur.phase, ring.abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { m = nm; if (has_next) load_first(v.routes.rows, m, first); continue; }
+        const unsigned char* wrow = ring.data + u64(slot) * plan.stage_bytes + rsub * plan.row_stride;
+        float* dst = (o < 4 ? s_g : s_u) + 8u * (o & 3u) + rsub;
+        for (u32 e0 = 0; e0 < ne; e0 += kR) {
+            const int nr = static_cast<int>(min(u32(kR), ne - e0));
+            const unsigned char* xr[kR];
+#pragma unroll
+            for (int r = 0; r < kR; ++r)
+                xr[r] = x_copy + (e0 == 0 ? first[r] : v.routes.rows[eb + e0 + min(r, nr - 1)]) * x_row_bytes + 64u * p;
+            float acc[kR];
+#pragma unroll
+            for (int r = 0; r < kR; ++r) acc[r] = 0.0f;
+            const uint4* blk = reinterpret_cast<const uint4*>(wrow);
+#pragma unroll 2
+            for (u32 b = 0; b < nblocks; ++b, blk += kQ4KBlock / 16) {
+                const uint4 hdr = blk[0], q0 = blk[1 + 2 * p], q1 = blk[2 + 2 * p];
+                const Factors f = q4k_factors(hdr, p);
+#pragma unroll
+                for (int r = 0; r < kR; ++r) {
+                    if (r < nr) {
+                        const uint4* c = reinterpret_cast<const uint4*>(xr[r] + 256u * b);
+                        const uint4 c0 = c[swz], c1 = c[1 - swz], c2 = c[2 + swz], c3 = c[3 - swz];
+                        const float4 es = *reinterpret_cast<const float4*>(xr[r] + (H - 48u * p) + 64u * b);
+                        int lo, hi;
+                        dots(q0, q1, c0, c1, c2, c3, &lo, &hi);
+                        acc[r] = __fadd_rn(acc[r], pair_value(f, lo, hi, es.x, es.y, es.z, es.w));
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kR; ++r) {
+                if (r < nr) {
+                    const float val = tree4(acc[r]);
+                    if (p == 0) dst[(e0 + r) * 32] = val;
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ring.empty[slot]);  // the stage is free for the producer
+        // item completion: the warp that brings the count to eight runs the epilogue
+        __threadfence_block();
+        u32 done = 0;
+        if (lane == 0) done = atomicAdd(&s_done[islot], 1u) + 1u;
+        done = __shfl_sync(0xffffffffu, done, 0);
+        m = nm;  // the next octet's entries: second hop of the prefetch
+        if (has_next) load_first(v.routes.rows, m, first);
+        if (done != kOctetsPerItem) continue;
+        __threadfence_block();
+        if (lane == 0) s_done[islot] = 0;
+        for (u32 r = 0; r < ne; ++r) {  // SwiGLU + the A8 rule over the item's 32 outputs
+            const float g = s_g[r * 32 + lane], u = s_u[r * 32 + lane];
+            const u32 slot_id = v.routes.slots[eb + r], o_col = 32u * gx + lane;
+            if (v.gate_out) { v.gate_out[u64(slot_id) * I + o_col] = g; v.up_out[u64(slot_id) * I + o_col] = u; }
+            const float h = swiglu_qwen(g, u);
+            const bool bad = __any_sync(0xffffffffu, !finite_f(g) || !finite_f(u) || !finite_f(h));
+            if (bad) {  // fail closed: nothing of the group is written (routed_expert.cpp:147-156)
+                if (lane == 0) {
+                    if (v.row_status) atomicOr(&v.row_status[v.routes.rows[eb + r]], B200MOE_ROW_PROJECTION_NONFINITE);
+                    if (v.summary) atomicOr(v.summary, B200MOE_ROW_PROJECTION_NONFINITE);
+                }
+                continue;
+            }
+            float delta;
+            int sum;
+            const int code = a8_quantize_lane(h, &delta, &sum);
+            v.act.codes[u64(slot_id) * act_stride + o_col] = static_cast<i8>(code);
+            if (lane == 0) {
+                v.act.deltas[u64(slot_id) * (act_stride / 32) + gx] = delta;
+                if (v.act.sums) v.act.sums[u64(slot_id) * (act_stride / 32) + gx] = sum;
+            }
+        }
+    }
+    if (!ok && lane == 0 && v.summary) atomicOr(v.summary, kAbortBit);
+}
+
+// ---- down ------------------------------------------------------------------------------------------------------------
+// Item = (expert, 64 hidden outputs) = 8 octets. Activations (the A8 of h) are read from global memory: every lane of a
+// row group reads the same addresses, so the loads are broadcasts served by L1 / L2.
+__global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_stream_kernel(b200moe_down_view v, StreamPlan plan) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const u32 H = v.shape.hidden, I = v.shape.inter, nblocks = I / 256;
+    u64* bars = reinterpret_cast<u64*>(smem + u64(plan.stages) * plan.stage_bytes);
+    u32* s_flag = reinterpret_cast<u32*>(bars + 2 * plan.stages);
+    const Ring ring{smem, bars, bars + plan.stages, s_flag};
+    ring_init(ring, plan.stages);
+    if (v.summary && (*v.summary & ~kAbortBit)) return;  // a failed projection skips the whole stage (routed_expert.hpp:17-19)
+
+    const u32 warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const u32 n_items = v.routes.counts[0] * plan.n_chunks;
+    const u64 row_bytes = plan.row_bytes;
+    if (warp >= plan.warps) {
+        produce(ring, plan, n_items, warp - plan.warps, [&](u32 item, u32 o) {
+            u32 j, cx;
+            split_item(plan, item, &j, &cx);
+            const u64 row = u64(v.routes.experts[j]) * H + 64u * cx + 8u * o;
+            return v.weights.down + row * row_bytes;
+        });
+        return;
+    }
+
+    const u32 act_stride = v.act.stride ? v.act.stride : v.act.width;
+    const u32 rsub = lane >> 2, p = lane & 3u;
+    const u32 local_octets = (n_items > blockIdx.x ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0) * kOctetsPerItem;
+    bool ok = true;
+    Meta m{};
+    u32 first[kR];
+    if (warp < local_octets) { m = load_meta(plan, v.routes, warp); load_first(v.routes.slots, m, first); }
+    for (Cursor cur{warp, warp % plan.stages, (warp / plan.stages) & 1u}; cur.q < local_octets; cur.advance(plan)) {
+        const u32 slot = cur.slot, o = cur.q & 7u;
+        const bool has_next = cur.q + plan.warps < local_octets;
+        Meta nm{};
+        if (has_next) nm = load_meta(plan, v.routes, cur.q + plan.warps);
+        const u32 cx = m.chunk, eb = m.eb, ne = m.ne;
+        if (ok) ok = mbar_wait(&ring.full[slot], cur.phase, ring.abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { m = nm; if (has_next) load_first(v.routes.slots, m, first); continue; }
+        const unsigned char* wrow = ring.data + u64(slot) * plan.stage_bytes + rsub * plan.row_stride;
+        const u32 out_col = 64u * cx + 8u * o + rsub;
+        for (u32 e0 = 0; e0 < ne; e0 += kR) {
+            const int nr = static_cast<int>(min(u32(kR), ne - e0));
+            u32 sl[kR];
+            const i8* cr[kR];
+            const float* dr[kR];
+            const i32* sr[kR];
+#pragma unroll
+            for (int r = 0; r < kR; ++r) {
+                sl[r] = e0 == 0 ? first[r] : v.routes.slots[eb + e0 + min(r, nr - 1)];
+                cr[r] = v.act.codes + u64(sl[r]) * act_stride + 64u * p;
+                dr[r] = v.act.deltas + u64(sl[r]) * (act_stride / 32) + 2u * p;
+                sr[r] = v.act.sums + u64(sl[r]) * (act_stride / 32) + 2u * p;
+            }
+            float acc[kR];
+#pragma unroll
+            for (int r = 0; r < kR; ++r) acc[r] = 0.0f;
+            const uint4* blk = reinterpret_cast<const uint4*>(wrow);
+#pragma unroll 3
+            for (u32 b = 0; b < nblocks; ++b, blk += kQ4KBlock / 16) {
+                const uint4 hdr = blk[0], q0 = blk[1 + 2 * p], q1 = blk[2 + 2 * p];
+                const Factors f = q4k_factors(hdr, p);
+#pragma unroll
+                for (int r = 0; r < kR; ++r) {
+                    if (r < nr) {
+                        const uint4* c = reinterpret_cast<const uint4*>(cr[r] + 256u * b);
+                        const uint4 c0 = __ldg(c), c1 = __ldg(c + 1), c2 = __ldg(c + 2), c3 = __ldg(c + 3);
+                        const float2 e = __ldg(reinterpret_cast<const float2*>(dr[r] + 8u * b));
+                        const int2 sm = __ldg(reinterpret_cast<const int2*>(sr[r] + 8u * b));
+                        int lo, hi;
+                        dots(q0, q1, c0, c1, c2, c3, &lo, &hi);
+                        acc[r] = __fadd_rn(acc[r], pair_value(f, lo, hi, e.x, e.y, small_int_to_float(sm.x), small_int_to_float(sm.y)));
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kR; ++r) {
+                if (r < nr) {
+                    const float val = tree4(acc[r]);
+                    if (p == 0) v.raw[u64(sl[r]) * H + out_col] = val;
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ring.empty[slot]);
+        m = nm;  // the next octet's entries: second hop of the prefetch
+        if (has_next) load_first(v.routes.slots, m, first);
+    }
+    // an aborted launch leaves raw partly unwritten: flag it in the job summary (held read-only here for the skip test)
+    if (!ok && lane == 0 && v.summary) atomicOr(const_cast<u32*>(v.summary), kAbortBit);
+}
+
+int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        return v;
+    }();
+    return n;
+}
+
+constexpr u32 kSmemBudget = 224u * 1024u;
+
+u32 padded_stride(u32 row_bytes) { return ((row_bytes / 16) & 1u) ? row_bytes : row_bytes + 16; }
+u32 pow2_at_least(u32 v) { u32 p = 1; while (p < v) p <<= 1; return p; }
+
+u32 plan_smem(const StreamPlan& p, u32 fixed_bytes, u32 per_item_slot_bytes) {
+    return p.stages * p.stage_bytes + p.item_slots * per_item_slot_bytes + fixed_bytes + 2 * p.stages * 8 + p.item_slots * 4 + 64;
+}
+// Ring depth, consumer warps and item slots for a row length. Items in flight inside a CTA never exceed
+// (stages + warps) / 8 + 2, so item_slots covers that with room. False when fewer than 4 stages fit.
+bool make_plan(u32 row_bytes, u32 fixed_bytes, u32 per_item_slot_bytes, StreamPlan* p) {
+    p->row_bytes = row_bytes;
+    p->row_stride = padded_stride(row_bytes);
+    p->stage_bytes = 8 * p->row_stride;
+    // The warps hold one octet each while they compute; what the ring holds beyond that is the prefetch depth. Measured
+    // on B200 (config 2, batch 8): time falls with every added consumer warp up to 16 as long as a few stages stay ahead.
+    for (u32 stages = 40; stages >= 4; --stages) {
+        p->stages = stages;
+        p->warps = std::max(2u, std::min(kMaxWarps, stages > 6 ? stages - 3 : stages / 2));
+        p->item_slots = pow2_at_least((stages + p->warps) / kOctetsPerItem + 3);
+        if (plan_smem(*p, fixed_bytes, per_item_slot_bytes) <= kSmemBudget) return true;
+    }
+    return false;
+}
+
+u32 gate_up_x_bytes(const b200moe_gate_up_view& v, u32 rows) { return rows * (v.shape.hidden + v.shape.hidden / 4); }
+
+}  // namespace
+
+bool stream_gate_up_fits(const b200moe_gate_up_view& v, u32 rows) {
+    if (!v.x.sums || rows == 0 || rows > 64 || u64(v.shape.experts) * (v.shape.inter / 32) >= (1u << 20)) return false;
+    StreamPlan p{};
+    return gate_up_x_bytes(v, rows) <= 80u * 1024u && make_plan(v.shape.hidden / 256 * kQ4KBlock, gate_up_x_bytes(v, rows), 2 * rows * 32 * 4, &p);
+}
+bool stream_down_fits(const b200moe_down_view& v, u32 rows) {
+    if (!v.act.sums || rows == 0 || rows > 64 || u64(v.shape.experts) * (v.shape.hidden / 64) >= (1u << 20)) return false;
+    StreamPlan p{};
+    return make_plan(v.shape.inter / 256 * kQ4KBlock, 0, 0, &p);
+}
+
+int launch_gate_up_q4k_stream(const b200moe_gate_up_view& v, u32 rows, cudaStream_t stream) {
+    if (v.max_union == 0) return B200MOE_OK;
+    StreamPlan p{};
+    const u32 x_bytes = gate_up_x_bytes(v, rows), slot_bytes = 2 * rows * 32 * 4;
+    if (!make_plan(v.shape.hidden / 256 * kQ4KBlock, x_bytes, slot_bytes, &p))
+        return fail(B200MOE_ERR_UNSUPPORTED, "gate_up stream form does not fit shared memory");
+    p.n_chunks = v.shape.inter / 32;
+    p.chunk_magic = static_cast<u32>((u64(1) << 32) / p.n_chunks) + 1;
+    p.max_entries = rows;
+    p.x_rows = rows;
+    const u32 smem = plan_smem(p, x_bytes, slot_bytes);
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(gate_up_q4k_stream_kernel), smem)) return rc;
+    gate_up_q4k_stream_kernel<<<sm_count(), (p.warps + kProducers) * 32, smem, stream>>>(v, p);
+    return after_launch("gate_up_q4k_stream");
+}
+
+int launch_down_q4k_stream(const b200moe_down_view& v, u32 rows, cudaStream_t stream) {
+    (void)rows;
+    if (v.max_union == 0) return B200MOE_OK;
+    StreamPlan p{};
+    if (!make_plan(v.shape.inter / 256 * kQ4KBlock, 0, 0, &p)) return fail(B200MOE_ERR_UNSUPPORTED, "down stream form does not fit shared memory");
+    p.n_chunks = v.shape.hidden / 64;
+    p.chunk_magic = static_cast<u32>((u64(1) << 32) / p.n_chunks) + 1;
+    const u32 smem = plan_smem(p, 0, 0);
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(down_q4k_stream_kernel), smem)) return rc;
+    down_q4k_stream_kernel<<<sm_count(), (p.warps + kProducers) * 32, smem, stream>>>(v, p);
+    return after_launch("down_q4k_stream");
+}
+
+}  // namespace b200moe

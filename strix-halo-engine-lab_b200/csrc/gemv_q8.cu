@@ -226,11 +226,7 @@ __global__ void __launch_bounds__(256) down_q8_kernel(b200moe_down_view v, u32 a
 
 template <class K>
 int set_smem(K kernel, u32 bytes) {
-    if (bytes > 48u * 1024u) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
-        if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "cudaFuncSetAttribute(smem %u): %s", bytes, cudaGetErrorString(e));
-    }
-    return B200MOE_OK;
+    return ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), bytes);
 }
 
 }  // namespace

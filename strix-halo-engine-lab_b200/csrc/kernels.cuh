@@ -9,12 +9,16 @@ namespace b200moe {
 int launch_quantize_a8(const b200moe_quantize_a8_view& v, cudaStream_t stream);
 
 // router.cu
-int launch_router_logits(const b200moe_router_view& v, cudaStream_t stream);
+// fused_quantize (optional): the A8 quantiser of the same activations is enqueued first
+int launch_router_logits(const b200moe_router_view& v, cudaStream_t stream, const b200moe_quantize_a8_view* fused_quantize = nullptr);
 int launch_router_select(const b200moe_router_view& v, cudaStream_t stream);
 
 // routes.cu
 u64 routes_scratch_words(u32 rows, u32 top_k, u32 experts);
 int launch_routes(const b200moe_routes_view& v, cudaStream_t stream);
+// decode windows: selection of r (logits already present) and the routes of the selected ids in one launch
+bool select_routes_fusable(const b200moe_router_view& r, u32 top_k);
+int launch_select_routes(const b200moe_router_view& r, const b200moe_routes_view& v, cudaStream_t stream);
 
 // gemv_q8.cu: Q8_0 x A8 products in the 32-lane-class contract (dense rows and the routed DS41-family experts)
 int launch_q8_0_a8(const b200moe_q8a8_view& v, cudaStream_t stream);
@@ -25,6 +29,17 @@ int launch_down_q8(const b200moe_down_view& v, cudaStream_t stream);
 int launch_gate_up_q4k(const b200moe_gate_up_view& v, cudaStream_t stream);
 int launch_down_q4k(const b200moe_down_view& v, cudaStream_t stream);
 int launch_down_q8_chain4(const b200moe_down_view& v, cudaStream_t stream);
+
+// gemv_q4k_stream.cu: the same Q4_K contracts as persistent kernels fed by bulk copies (decode windows up to 64 rows)
+bool stream_gate_up_fits(const b200moe_gate_up_view& v, u32 rows);
+bool stream_down_fits(const b200moe_down_view& v, u32 rows);
+int launch_gate_up_q4k_stream(const b200moe_gate_up_view& v, u32 rows, cudaStream_t stream);
+int launch_down_q4k_stream(const b200moe_down_view& v, u32 rows, cudaStream_t stream);
+
+// prologue.cu: A8 + router + routes of a decode window (rows <= 8) in one launch; ticket: a zeroed workspace word
+bool prologue_fusable(const b200moe_router_view& r, u32 top_k);
+int launch_prologue(const b200moe_router_view& r, const b200moe_quantize_a8_view& q, const b200moe_routes_view& routes, u32* ticket,
+                    cudaStream_t stream);
 
 // combine.cu
 int launch_combine(const b200moe_combine_view& v, cudaStream_t stream);

@@ -1,0 +1,145 @@
+// Score transform, k-pass top-k selection and weights of one router row by one warp: device code shared by the
+// stand-alone select kernel (router.cu) and the fused select + routes kernel of decode windows (routes.cu).
+// Contracts: include/strix/moe/route_policy.hpp:80-156 (see router.cu).
+#pragma once
+#include "declared_math.cuh"
+
+namespace b200moe {
+namespace select_detail {
+
+__device__ __forceinline__ u32 ordered_key(float v) {  // route_policy.hpp:84-88
+    u32 u = __float_as_uint(v);
+    if (u == 0x80000000u) u = 0;
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+// True when candidate (a, ai) beats the current pick (b, bi) in a reduction over disjoint ascending scans: the
+// serial scan keeps the lower id on equal keys, so the parallel form orders by (key desc, id asc).
+__device__ __forceinline__ bool beats(u32 key, float a, u32 ai, float b, u32 bi) {
+    if (key == B200MOE_KEY_FLOAT_SERIAL) return a > b || (a == b && ai < bi);
+    const u32 ka = ordered_key(a), kb = ordered_key(b);
+    return ka > kb || (ka == kb && ai < bi);
+}
+
+constexpr u32 kNone = 0xffffffffu;
+
+// The serial scan of one selection pass (route_policy.hpp:104-114) over a short candidate list, skipping `skip`.
+__device__ __forceinline__ u32 serial_pick(u32 key, const float* c, u32 n, u32 skip) {
+    u32 pick = kNone;
+    float best = 0.0f;
+    for (u32 e = 0; e < n; ++e) {
+        if (e == skip) continue;
+        const bool better = key == B200MOE_KEY_FLOAT_SERIAL ? c[e] > best : ordered_key(c[e]) > ordered_key(best);
+        if (pick == kNone || better) { pick = e; best = c[e]; }
+    }
+    return pick;
+}
+
+// One k-pass over `n` candidates c[] (shared memory), lane-strided; `taken` holds this lane's taken candidates (bit j
+// = candidate lane + 32 j), `allowed_groups` masks candidates by group (per = candidates per group; all ones = no
+// mask). Returns the pick (kNone when nothing is left) to every lane and marks it taken.
+__device__ __forceinline__ u32 k_pass(u32 key, const float* c, u32 n, u32 lane, u32& taken, u32 allowed_groups, u32 per) {
+    // the serial scan's first candidate: lowest untaken allowed id
+    u32 first = kNone, pick = kNone;
+    float best = 0.0f;
+    for (u32 j = 0, e = lane; e < n; ++j, e += 32) {
+        if ((taken >> j) & 1u) continue;
+        if (!((allowed_groups >> (e / per)) & 1u)) continue;
+        if (first == kNone) first = e;
+        const float v = c[e];
+        if (key == B200MOE_KEY_FLOAT_SERIAL && v != v) continue;  // a NaN never replaces a pick
+        if (pick == kNone || beats(key, v, e, best, pick)) { pick = e; best = v; }
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+        const u32 of = __shfl_xor_sync(0xffffffffu, first, d);
+        first = min(first, of);
+        const u32 op = __shfl_xor_sync(0xffffffffu, pick, d);
+        const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+        if (op != kNone && (pick == kNone || beats(key, ob, op, best, pick))) { pick = op; best = ob; }
+    }
+    if (first == kNone) return kNone;
+    if (key == B200MOE_KEY_FLOAT_SERIAL) {
+        const float fv = c[first];
+        if (fv != fv) pick = first;  // a NaN taken as the first candidate stays (route_policy.hpp:11-12)
+    }
+    if (pick != kNone && (pick & 31u) == lane) taken |= 1u << (pick >> 5);
+    return pick;
+}
+
+// One warp selects one row. `s` points to this warp's scratch of 2 * experts + 32 floats (shared memory).
+__device__ __forceinline__ void select_row(const float* logits, float* scores_out, const float* __restrict__ bias,
+                                           const b200moe_route_policy& p, u32 row, u32 lane, float* s,
+                                           u32* __restrict__ ids, float* __restrict__ weights) {
+    const u32 E = p.experts;
+    float* c = s + E;
+    float* gs = c + E;
+    const float* z = logits + u64(row) * E;
+
+    if (p.score == B200MOE_SCORE_SOFTMAX) {  // route_policy.hpp:135-144
+        float m = -__uint_as_float(0x7f800000u);
+        for (u32 e = lane; e < E; e += 32) { const float v = z[e]; m = v > m ? v : m; }
+#pragma unroll
+        for (int d = 16; d; d >>= 1) { const float o = __shfl_xor_sync(0xffffffffu, m, d); m = o > m ? o : m; }
+        for (u32 e = lane; e < E; e += 32) s[e] = declared_exp(__fsub_rn(z[e], m));
+        __syncwarp();
+        float sum = 0.0f;
+#pragma unroll 8
+        for (u32 e = 0; e < E; ++e) sum = __fadd_rn(sum, s[e]);  // ascending serial sum (the declared order), every lane alike
+        for (u32 e = lane; e < E; e += 32) s[e] = __fdiv_rn(s[e], sum);
+    } else if (p.score == B200MOE_SCORE_SIGMOID) {
+        for (u32 e = lane; e < E; e += 32) s[e] = sigmoid_score(z[e]);
+    } else {
+        for (u32 e = lane; e < E; e += 32) s[e] = sqrt_softplus_score(z[e]);
+    }
+    for (u32 e = lane; e < E; e += 32) c[e] = p.selection_bias ? __fadd_rn(s[e], bias[e]) : s[e];
+    __syncwarp();
+    if (scores_out) for (u32 e = lane; e < E; e += 32) scores_out[u64(row) * E + e] = s[e];
+
+    u32 allowed = 0xffffffffu, per = E;
+    if (p.n_group > 1) {  // group-limited extension (include/b200moe.h): group score = its two best choices summed
+        per = E / p.n_group;
+        if (lane < p.n_group) {
+            const float* cg = c + lane * per;
+            const u32 i0 = serial_pick(p.key, cg, per, kNone);
+            const u32 i1 = serial_pick(p.key, cg, per, i0);
+            const float b0 = cg[i0], b1 = cg[i1];
+            gs[lane] = __fadd_rn(b0, b1);
+        }
+        __syncwarp();
+        u32 gtaken = 0;
+        allowed = 0;
+        for (u32 k = 0; k < p.topk_group; ++k) {
+            const u32 g = k_pass(p.key, gs, p.n_group, lane, gtaken, 0xffffffffu, p.n_group);
+            if (g != kNone) allowed |= 1u << g;
+        }
+    }
+
+    u32 taken = 0, my_id = kNone;
+    for (u32 k = 0; k < p.top_k; ++k) {
+        const u32 pick = k_pass(p.key, c, E, lane, taken, allowed, per);
+        if (lane == k) my_id = pick;
+    }
+    if (p.order == B200MOE_ORDER_ASCENDING_ID) {  // rank sort of the (distinct) ids held one per lane
+        u32 rank = 0;
+        for (u32 k = 0; k < p.top_k; ++k) { const u32 o = __shfl_sync(0xffffffffu, my_id, k); rank += (o < my_id) ? 1u : 0u; }
+        u32 sorted = kNone;
+        for (u32 k = 0; k < p.top_k; ++k) {
+            const u32 o = __shfl_sync(0xffffffffu, my_id, k), orank = __shfl_sync(0xffffffffu, rank, k);
+            if (orank == lane) sorted = o;
+        }
+        my_id = sorted;
+    }
+    const float my_s = (lane < p.top_k && my_id != kNone) ? s[my_id] : 0.0f;
+    float sum = 0.0f;  // ((0 + s0) + s1) + ... in output order (route_policy.hpp:121-123)
+    for (u32 k = 0; k < p.top_k; ++k) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_s, k));
+    const bool renorm = p.renormalize && (p.top_k > 1 || p.renorm_single);
+    const float den = __fadd_rn(sum, p.renorm_eps);
+    if (lane < p.top_k) {
+        ids[u64(row) * p.top_k + lane] = my_id;
+        weights[u64(row) * p.top_k + lane] = __fmul_rn(renorm ? __fdiv_rn(my_s, den) : my_s, p.scale);
+    }
+}
+
+
+}  // namespace select_detail
+}  // namespace b200moe

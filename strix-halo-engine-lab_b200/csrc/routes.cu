@@ -9,87 +9,31 @@
 // Two forms: up to 1024 slots (decode windows) one block does everything; above that three launches over chunks of
 // 1024 slots (per-chunk histograms, a scan over chunks and experts, then the stable fill).
 #include "kernels.cuh"
+#include "router_select.cuh"
+#include "routes_small.cuh"
 
 namespace b200moe {
 namespace {
 
-constexpr u32 kChunk = 1024;
+constexpr u32 kChunk = routes_detail::kChunk;
 
-// Exclusive scan of one value per thread over a 1024-thread block; `total` gets the sum. warp_tot: 32 words of smem.
-__device__ __forceinline__ u32 block_exclusive_scan(u32 v, u32* warp_tot, u32* total) {
+using routes_detail::block_exclusive_scan;
+using routes_detail::owned;
+using routes_detail::row_order;
+using routes_detail::routes_small_body;
+
+__global__ void __launch_bounds__(1024) routes_small_kernel(b200moe_routes_view v, u32 end) { routes_small_body(v, end); }
+
+// Decode windows: the router's selection (one warp per row) and the routes of the selected ids in ONE block, so the
+// layer prologue costs one launch less. Dynamic shared memory: rows * (2 * experts + 32) floats.
+__global__ void __launch_bounds__(1024) select_routes_small_kernel(const float* logits, float* scores_out, const float* __restrict__ bias,
+                                                                   b200moe_route_policy p, u32 rows, u32* ids, float* __restrict__ weights,
+                                                                   b200moe_routes_view rv, u32 end) {
+    extern __shared__ float sel_smem[];
     const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    u32 inc = v;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) { const u32 o = __shfl_up_sync(0xffffffffu, inc, d); if (lane >= (u32)d) inc += o; }
-    if (lane == 31) warp_tot[warp] = inc;
-    __syncthreads();
-    if (warp == 0) {
-        u32 t = warp_tot[lane], ti = t;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) { const u32 o = __shfl_up_sync(0xffffffffu, ti, d); if (lane >= (u32)d) ti += o; }
-        warp_tot[lane] = ti - t;
-        if (lane == 31) *total = ti;
-    }
-    __syncthreads();
-    const u32 r = warp_tot[warp] + inc - v;
-    __syncthreads();
-    return r;
-}
-
-// Per row: the slots sorted by expert id (top_k <= 32, insertion sort), the low count and the route check.
-__device__ void row_order(const u32* ids, u32 row, u32 top_k, u32 experts, u32 split, u32* order, u32* low_counts, u32* row_status) {
-    u32 key[32], slot[32];
-    u32 low = 0;
-    bool bad = false;
-    for (u32 k = 0; k < top_k; ++k) {
-        const u32 s = row * top_k + k, e = ids[s];
-        bad |= e >= experts;
-        low += e < split ? 1u : 0u;
-        u32 j = k;
-        while (j > 0 && key[j - 1] > e) { key[j] = key[j - 1]; slot[j] = slot[j - 1]; --j; }
-        bad |= (j > 0 && key[j - 1] == e);
-        key[j] = e; slot[j] = s;
-    }
-    for (u32 k = 0; k < top_k; ++k) order[row * top_k + k] = slot[k];
-    low_counts[row] = low;
-    if (bad && row_status) atomicOr(&row_status[row], B200MOE_ROW_INVALID_ROUTE);
-}
-
-__device__ __forceinline__ bool owned(u32 e, u32 experts, u32 first, u32 end) { return e < experts && e >= first && e < end; }
-
-// ---- one block, <= 1024 slots ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) routes_small_kernel(b200moe_routes_view v, u32 end) {
-    __shared__ u32 cnt[1024], ebegin[1024], sid[1024], warp_tot[32], total_s, union_s, maxc;
-    const u32 t = threadIdx.x, n = v.rows * v.top_k;
-    cnt[t] = 0;
-    if (t == 0) maxc = 0;
-    __syncthreads();
-    u32 e = 0xffffffffu;
-    if (t < n) {
-        e = v.ids[t];
-        if (!owned(e, v.experts, v.first, end)) e = 0xffffffffu;
-        else atomicAdd(&cnt[e], 1u);
-    }
-    sid[t] = e;
-    for (u32 r = t; r < v.rows; r += blockDim.x) row_order(v.ids, r, v.top_k, v.experts, v.split, v.out.order, v.out.low_counts, v.row_status);
-    __syncthreads();
-    const u32 c = t < v.experts ? cnt[t] : 0u;
-    const u32 begin = block_exclusive_scan(c, warp_tot, &total_s);
-    const u32 uidx = block_exclusive_scan(c ? 1u : 0u, warp_tot, &union_s);
-    ebegin[t] = begin;
-    if (c) { v.out.experts[uidx] = t - v.base; v.out.begins[uidx + 1] = begin + c; atomicMax(&maxc, c); }
-    __syncthreads();
-    if (t == 0) {
-        v.out.begins[0] = 0;
-        v.out.counts[0] = union_s; v.out.counts[1] = maxc; v.out.counts[2] = total_s; v.out.counts[3] = 0;
-    }
-    if (e != 0xffffffffu) {
-        u32 rank = 0;
-        for (u32 i = 0; i < t; ++i) rank += sid[i] == e ? 1u : 0u;
-        const u32 pos = ebegin[e] + rank;
-        v.out.rows[pos] = t / v.top_k;
-        v.out.slots[pos] = t;
-    }
+    if (warp < rows) select_detail::select_row(logits, scores_out, bias, p, warp, lane, sel_smem + warp * (2u * p.experts + 32u), ids, weights);
+    __syncthreads();  // the ids written above are read below by the whole block
+    routes_small_body(rv, end);
 }
 
 // ---- chunked form --------------------------------------------------------------------------------------------------
@@ -143,6 +87,17 @@ __global__ void __launch_bounds__(1024) routes_fill_kernel(b200moe_routes_view v
 u64 routes_scratch_words(u32 rows, u32 top_k, u32 experts) {
     const u64 n = u64(rows) * top_k, chunks = (n + kChunk - 1) / kChunk;
     return (chunks + 1) * experts + 4;
+}
+
+bool select_routes_fusable(const b200moe_router_view& r, u32 top_k) {
+    return r.rows <= 32 && u64(r.rows) * top_k <= kChunk && u64(r.rows) * (2u * r.policy.experts + 32u) * 4u <= 96u * 1024u;
+}
+int launch_select_routes(const b200moe_router_view& r, const b200moe_routes_view& v, cudaStream_t stream) {
+    if (r.rows == 0) return B200MOE_OK;
+    const u32 smem = r.rows * (2u * r.policy.experts + 32u) * 4u;
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(select_routes_small_kernel), smem)) return rc;
+    select_routes_small_kernel<<<1, 1024, smem, stream>>>(r.logits, r.scores, r.bias, r.policy, r.rows, r.ids, r.weights, v, v.end ? v.end : v.experts);
+    return after_launch("select_routes_small");
 }
 
 int launch_routes(const b200moe_routes_view& v, cudaStream_t stream) {

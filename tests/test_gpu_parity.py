@@ -390,7 +390,8 @@ def test_experts_q4k_qwen_family(gpu, oracle):
     rng = np.random.default_rng(17)
     exact_all = True
     for E, H, I, K, rows, dt in ((6, 512, 256, 2, 7, 12), (16, 2048, 768, 8, 4, 12), (8, 256, 512, 3, 21, 12), (6, 512, 256, 2, 7, 8),
-                                 (4, 7168, 2048, 2, 3, 12), (4, 1280, 1024, 2, 2, 12), (5, 2560, 640, 3, 3, 8)):
+                                 (4, 7168, 2048, 2, 3, 12), (4, 1280, 1024, 2, 2, 12), (5, 2560, 640, 3, 3, 8),
+                                 (4, 256, 256, 2, 70, 12), (3, 512, 768, 2, 64, 12)):  # 70 rows: beyond the decode-window form
         gate, up, _ = synth.expert_tensors(rng, E, H, I, 12, 12)
         down = (synth.q4_k_blocks(rng, E * H * (I // 256)) if dt == 12 else synth.q8_0_blocks(rng, E * H * (I // 32))).reshape(-1)
         x = rng.standard_normal((rows, H), dtype=np.float32)
