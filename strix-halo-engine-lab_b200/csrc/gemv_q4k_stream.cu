@@ -17,6 +17,7 @@
 // job summary is set and the kernel returns: the host reads a status, the GPU never hangs.
 //
 // Roofline: HBM. Algorithmic bytes per item = 64 rows x K / 256 x 144.
+
 #include "declared_math.cuh"
 #include "kernels.cuh"
 
@@ -34,9 +35,6 @@ constexpr u32 kProducers = 4;       // producer warps
 __device__ __forceinline__ u32 saddr(const void* p) { return static_cast<u32>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(u64* bar, u32 count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(u64* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(u64* bar, u32 bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
@@ -89,20 +87,48 @@ struct StreamPlan {
     u32 x_rows;        // rows of the A8 input copied to shared memory (gate/up)
 };
 
+// Ring of stages. An mbarrier's phase test only tells odd from even uses of a slot, and here the successive uses of a
+// slot belong to different warps (producers and consumers alike), which may drift a whole lap apart. So every slot also
+// carries two generation words: gen = octet index + 1 written by the producer before it arms the barrier, rel = octet
+// index + 1 written by the consumer when it is done. A consumer first waits for ITS generation to be armed and only then
+// for the phase; a producer waits for the previous use's release by exact match. No wait can be satisfied by another lap.
 struct Ring {
     unsigned char* data;
     u64* full;
-    u64* empty;
+    volatile u32* gen;
+    volatile u32* rel;
     volatile u32* abort_flag;
 };
 
 __device__ __forceinline__ void ring_init(const Ring& r, u32 stages) {
     if (threadIdx.x == 0) {
-        for (u32 s = 0; s < stages; ++s) { mbar_init(&r.full[s], 1); mbar_init(&r.empty[s], 1); }
+        for (u32 s = 0; s < stages; ++s) { mbar_init(&r.full[s], 1); r.gen[s] = 0; r.rel[s] = 0; }
         *r.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+}
+// Bounded spin until *word == want; false when the limit ran out or another role aborted.
+__device__ __forceinline__ bool flag_wait(volatile u32* word, u32 want, volatile u32* abort_flag) {
+    for (u32 i = 0; i < kWaitLimit; ++i) {
+        if (*word == want) return true;
+        if ((i & 63u) == 63u) {
+            if (*abort_flag) return false;
+            __nanosleep(32);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+// Consumer side: the octet's generation is armed, then its bytes have landed.
+__device__ __forceinline__ bool stage_wait(const Ring& ring, u32 slot, u32 q, u32 phase) {
+    if (!flag_wait(&ring.gen[slot], q + 1u, ring.abort_flag)) return false;
+    return mbar_wait(&ring.full[slot], phase, ring.abort_flag);
+}
+// Consumer side: done reading the stage.
+__device__ __forceinline__ void stage_release(const Ring& ring, u32 slot, u32 q) {
+    __threadfence_block();
+    ring.rel[slot] = q + 1u;
 }
 
 // The producer warps: kProducers warps share the octet stream (octet q goes to producer q mod kProducers); lanes 0..7
@@ -118,12 +144,17 @@ __device__ __forceinline__ void produce(const Ring& ring, const StreamPlan& plan
     u32 slot = pw % plan.stages, phase = (pw / plan.stages) & 1u, q = pw;
     bool ok = true;
     for (; q < local_octets; q += kProducers) {
-        if (q >= plan.stages) ok = mbar_wait(&ring.empty[slot], phase ^ 1u, ring.abort_flag);
+        if (q >= plan.stages) ok = flag_wait(&ring.rel[slot], q - plan.stages + 1u, ring.abort_flag);  // the slot's previous use is done
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the consumers' reads precede the copies below
         const unsigned char* src = row_of(blockIdx.x + (q >> 3) * gridDim.x, q & 7u);
         unsigned char* dst = ring.data + u64(slot) * plan.stage_bytes;
-        if (lane == 0) mbar_expect_tx(&ring.full[slot], 8u * plan.row_bytes);
+        if (lane == 0) {
+            ring.gen[slot] = q + 1u;
+            __threadfence_block();
+            mbar_expect_tx(&ring.full[slot], 8u * plan.row_bytes);
+        }
         __syncwarp();
         if (one_copy) {
             if (lane == 0) bulk_g2s(dst, src, 8u * plan.row_bytes, &ring.full[slot]);
@@ -192,28 +223,29 @@ __device__ __forceinline__ Factors q4k_factors(const uint4& hdr, u32 p) {
     f.DMh = __fmul_rn(dm, small_int_to_float(m1));
     return f;
 }
-__device__ __forceinline__ void dots(const uint4& q0, const uint4& q1, const uint4& c0, const uint4& c1, const uint4& c2, const uint4& c3,
-                                     int* lo, int* hi) {
-    int l = 0, h = 0;
-    l = __dp4a(static_cast<int>(q0.x & 0x0f0f0f0fu), static_cast<int>(c0.x), l);
-    l = __dp4a(static_cast<int>(q0.y & 0x0f0f0f0fu), static_cast<int>(c0.y), l);
-    l = __dp4a(static_cast<int>(q0.z & 0x0f0f0f0fu), static_cast<int>(c0.z), l);
-    l = __dp4a(static_cast<int>(q0.w & 0x0f0f0f0fu), static_cast<int>(c0.w), l);
-    l = __dp4a(static_cast<int>(q1.x & 0x0f0f0f0fu), static_cast<int>(c1.x), l);
-    l = __dp4a(static_cast<int>(q1.y & 0x0f0f0f0fu), static_cast<int>(c1.y), l);
-    l = __dp4a(static_cast<int>(q1.z & 0x0f0f0f0fu), static_cast<int>(c1.z), l);
-    l = __dp4a(static_cast<int>(q1.w & 0x0f0f0f0fu), static_cast<int>(c1.w), l);
-    // high nibbles in place: bytes 16 * q (unsigned) times signed codes = 16 * dot, an exact shift away
-    h = dp4a_us(q0.x & 0xf0f0f0f0u, c2.x, h);
-    h = dp4a_us(q0.y & 0xf0f0f0f0u, c2.y, h);
-    h = dp4a_us(q0.z & 0xf0f0f0f0u, c2.z, h);
-    h = dp4a_us(q0.w & 0xf0f0f0f0u, c2.w, h);
-    h = dp4a_us(q1.x & 0xf0f0f0f0u, c3.x, h);
-    h = dp4a_us(q1.y & 0xf0f0f0f0u, c3.y, h);
-    h = dp4a_us(q1.z & 0xf0f0f0f0u, c3.z, h);
-    h = dp4a_us(q1.w & 0xf0f0f0f0u, c3.w, h);
-    *lo = l;
-    *hi = h >> 4;
+// The 64 nibbles of one (super-block, pair): low nibbles (group 2p) as bytes, high nibbles (group 2p + 1) left in
+// place as 16 * q. Split once per block, used by every entry.
+struct Nibbles { u32 lo[8], hi[8]; };
+__device__ __forceinline__ Nibbles split_nibbles(const uint4& q0, const uint4& q1) {
+    Nibbles n;
+    const u32 w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { n.lo[i] = w[i] & 0x0f0f0f0fu; n.hi[i] = w[i] & 0xf0f0f0f0u; }
+    return n;
+}
+// Exact group dots: two interleaved chains of four for each group (integer sums are order free).
+__device__ __forceinline__ void dots(const Nibbles& n, const uint4& c0, const uint4& c1, const uint4& c2, const uint4& c3, int* lo, int* hi) {
+    int la = __dp4a(static_cast<int>(n.lo[0]), static_cast<int>(c0.x), 0), lb = __dp4a(static_cast<int>(n.lo[1]), static_cast<int>(c0.y), 0);
+    la = __dp4a(static_cast<int>(n.lo[2]), static_cast<int>(c0.z), la); lb = __dp4a(static_cast<int>(n.lo[3]), static_cast<int>(c0.w), lb);
+    la = __dp4a(static_cast<int>(n.lo[4]), static_cast<int>(c1.x), la); lb = __dp4a(static_cast<int>(n.lo[5]), static_cast<int>(c1.y), lb);
+    la = __dp4a(static_cast<int>(n.lo[6]), static_cast<int>(c1.z), la); lb = __dp4a(static_cast<int>(n.lo[7]), static_cast<int>(c1.w), lb);
+    // bytes 16 * q (unsigned) times signed codes = 16 * dot, an exact shift away
+    int ha = dp4a_us(n.hi[0], c2.x, 0), hb = dp4a_us(n.hi[1], c2.y, 0);
+    ha = dp4a_us(n.hi[2], c2.z, ha); hb = dp4a_us(n.hi[3], c2.w, hb);
+    ha = dp4a_us(n.hi[4], c3.x, ha); hb = dp4a_us(n.hi[5], c3.y, hb);
+    ha = dp4a_us(n.hi[6], c3.z, ha); hb = dp4a_us(n.hi[7], c3.w, hb);
+    *lo = la + lb;
+    *hi = (ha + hb) >> 4;
 }
 __device__ __forceinline__ float pair_value(const Factors& f, int lo, int hi, float El, float Eh, float Sl, float Sh) {
     const float xl = __fmul_rn(El, __fsub_rn(__fmul_rn(f.Dl, small_int_to_float(lo)), __fmul_rn(f.DMl, Sl)));
@@ -224,6 +256,48 @@ __device__ __forceinline__ float pair_value(const Factors& f, int lo, int hi, fl
 __device__ __forceinline__ float tree4(float a) {
     a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
     return __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+}
+
+// One weight row (this lane's pair p of every super-block, ascending) against NR staged A8 rows (gate/up form: codes
+// chunk-swapped and {E, E, S, S} packs in shared memory). acc[r] is the lane's chain acc_p of row r.
+template <int NR>
+__device__ __forceinline__ void row_gate_up(const uint4* blk, u32 nblocks, u32 p, u32 swz, u32 H, const unsigned char* const* xr, float* acc) {
+#pragma unroll(NR <= 2 ? 2 : 1)
+    for (u32 b = 0; b < nblocks; ++b, blk += kQ4KBlock / 16) {
+        const uint4 hdr = blk[0], q0 = blk[1 + 2 * p], q1 = blk[2 + 2 * p];
+        const Factors f = q4k_factors(hdr, p);
+        const Nibbles n = split_nibbles(q0, q1);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const uint4* c = reinterpret_cast<const uint4*>(xr[r] + 256u * b);
+            const uint4 c0 = c[swz], c1 = c[1 - swz], c2 = c[2 + swz], c3 = c[3 - swz];
+            const float4 es = *reinterpret_cast<const float4*>(xr[r] + (H - 48u * p) + 64u * b);
+            int lo, hi;
+            dots(n, c0, c1, c2, c3, &lo, &hi);
+            acc[r] = __fadd_rn(acc[r], pair_value(f, lo, hi, es.x, es.y, es.z, es.w));
+        }
+    }
+}
+// The same against NR A8 rows in global memory (down form: codes / deltas / sums of the slots' activations).
+template <int NR>
+__device__ __forceinline__ void row_down(const uint4* blk, u32 nblocks, u32 p, const i8* const* cr, const float* const* dr, const i32* const* sr,
+                                         float* acc) {
+#pragma unroll(NR == 1 ? 3 : 1)
+    for (u32 b = 0; b < nblocks; ++b, blk += kQ4KBlock / 16) {
+        const uint4 hdr = blk[0], q0 = blk[1 + 2 * p], q1 = blk[2 + 2 * p];
+        const Factors f = q4k_factors(hdr, p);
+        const Nibbles n = split_nibbles(q0, q1);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const uint4* c = reinterpret_cast<const uint4*>(cr[r] + 256u * b);
+            const uint4 c0 = __ldg(c), c1 = __ldg(c + 1), c2 = __ldg(c + 2), c3 = __ldg(c + 3);
+            const float2 e = __ldg(reinterpret_cast<const float2*>(dr[r] + 8u * b));
+            const int2 sm = __ldg(reinterpret_cast<const int2*>(sr[r] + 8u * b));
+            int lo, hi;
+            dots(n, c0, c1, c2, c3, &lo, &hi);
+            acc[r] = __fadd_rn(acc[r], pair_value(f, lo, hi, e.x, e.y, small_int_to_float(sm.x), small_int_to_float(sm.y)));
+        }
+    }
 }
 
 // ---- gate/up ---------------------------------------------------------------------------------------------------------
@@ -259,7 +333,7 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) gate_up_q4k_
     at += 16;
     at = smem + ((at - smem + 15) & ~size_t(15));
     unsigned char* x_copy = at;
-    const Ring ring{smem, bars, bars + plan.stages, s_flag};
+    const Ring ring{smem, bars, reinterpret_cast<volatile u32*>(bars + plan.stages), reinterpret_cast<volatile u32*>(bars + plan.stages) + plan.stages, s_flag};
     for (u32 i = threadIdx.x; i < plan.item_slots; i += blockDim.x) s_done[i] = 0;
     ring_init(ring, plan.stages);
 
@@ -298,7 +372,7 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) gate_up_q4k_
         const u32 islot = local_item & (plan.item_slots - 1);
         float* s_g = s_gu + u64(islot) * 2 * ME * 32;
         float* s_u = s_g + ME * 32;
-        if (ok) ok = mbar_wait(&ring.full[slot], cur.phase, ring.abort_flag);
+        if (ok) ok = stage_wait(ring, slot, cur.q, cur.phase);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { m = nm; if (has_next) load_first(v.routes.rows, m, first); continue; }
         const unsigned char* wrow = ring.data + u64(slot) * plan.stage_bytes + rsub * plan.row_stride;
@@ -313,21 +387,11 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) gate_up_q4k_
 #pragma unroll
             for (int r = 0; r < kR; ++r) acc[r] = 0.0f;
             const uint4* blk = reinterpret_cast<const uint4*>(wrow);
-#pragma unroll 2
-            for (u32 b = 0; b < nblocks; ++b, blk += kQ4KBlock / 16) {
-                const uint4 hdr = blk[0], q0 = blk[1 + 2 * p], q1 = blk[2 + 2 * p];
-                const Factors f = q4k_factors(hdr, p);
-#pragma unroll
-                for (int r = 0; r < kR; ++r) {
-                    if (r < nr) {
-                        const uint4* c = reinterpret_cast<const uint4*>(xr[r] + 256u * b);
-                        const uint4 c0 = c[swz], c1 = c[1 - swz], c2 = c[2 + swz], c3 = c[3 - swz];
-                        const float4 es = *reinterpret_cast<const float4*>(xr[r] + (H - 48u * p) + 64u * b);
-                        int lo, hi;
-                        dots(q0, q1, c0, c1, c2, c3, &lo, &hi);
-                        acc[r] = __fadd_rn(acc[r], pair_value(f, lo, hi, es.x, es.y, es.z, es.w));
-                    }
-                }
+            switch (nr) {  // no per-entry branches inside the block loop
+                case 1: row_gate_up<1>(blk, nblocks, p, swz, H, xr, acc); break;
+                case 2: row_gate_up<2>(blk, nblocks, p, swz, H, xr, acc); break;
+                case 3: row_gate_up<3>(blk, nblocks, p, swz, H, xr, acc); break;
+                default: row_gate_up<4>(blk, nblocks, p, swz, H, xr, acc); break;
             }
 #pragma unroll
             for (int r = 0; r < kR; ++r) {
@@ -338,7 +402,7 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) gate_up_q4k_
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ring.empty[slot]);  // the stage is free for the producer
+        if (lane == 0) stage_release(ring, slot, cur.q);  // the stage is free for the producers
         // item completion: the warp that brings the count to eight runs the epilogue
         __threadfence_block();
         u32 done = 0;
@@ -383,7 +447,7 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_str
     const u32 H = v.shape.hidden, I = v.shape.inter, nblocks = I / 256;
     u64* bars = reinterpret_cast<u64*>(smem + u64(plan.stages) * plan.stage_bytes);
     u32* s_flag = reinterpret_cast<u32*>(bars + 2 * plan.stages);
-    const Ring ring{smem, bars, bars + plan.stages, s_flag};
+    const Ring ring{smem, bars, reinterpret_cast<volatile u32*>(bars + plan.stages), reinterpret_cast<volatile u32*>(bars + plan.stages) + plan.stages, s_flag};
     ring_init(ring, plan.stages);
     if (v.summary && (*v.summary & ~kAbortBit)) return;  // a failed projection skips the whole stage (routed_expert.hpp:17-19)
 
@@ -413,7 +477,7 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_str
         Meta nm{};
         if (has_next) nm = load_meta(plan, v.routes, cur.q + plan.warps);
         const u32 cx = m.chunk, eb = m.eb, ne = m.ne;
-        if (ok) ok = mbar_wait(&ring.full[slot], cur.phase, ring.abort_flag);
+        if (ok) ok = stage_wait(ring, slot, cur.q, cur.phase);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { m = nm; if (has_next) load_first(v.routes.slots, m, first); continue; }
         const unsigned char* wrow = ring.data + u64(slot) * plan.stage_bytes + rsub * plan.row_stride;
@@ -435,22 +499,11 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_str
 #pragma unroll
             for (int r = 0; r < kR; ++r) acc[r] = 0.0f;
             const uint4* blk = reinterpret_cast<const uint4*>(wrow);
-#pragma unroll 3
-            for (u32 b = 0; b < nblocks; ++b, blk += kQ4KBlock / 16) {
-                const uint4 hdr = blk[0], q0 = blk[1 + 2 * p], q1 = blk[2 + 2 * p];
-                const Factors f = q4k_factors(hdr, p);
-#pragma unroll
-                for (int r = 0; r < kR; ++r) {
-                    if (r < nr) {
-                        const uint4* c = reinterpret_cast<const uint4*>(cr[r] + 256u * b);
-                        const uint4 c0 = __ldg(c), c1 = __ldg(c + 1), c2 = __ldg(c + 2), c3 = __ldg(c + 3);
-                        const float2 e = __ldg(reinterpret_cast<const float2*>(dr[r] + 8u * b));
-                        const int2 sm = __ldg(reinterpret_cast<const int2*>(sr[r] + 8u * b));
-                        int lo, hi;
-                        dots(q0, q1, c0, c1, c2, c3, &lo, &hi);
-                        acc[r] = __fadd_rn(acc[r], pair_value(f, lo, hi, e.x, e.y, small_int_to_float(sm.x), small_int_to_float(sm.y)));
-                    }
-                }
+            switch (nr) {
+                case 1: row_down<1>(blk, nblocks, p, cr, dr, sr, acc); break;
+                case 2: row_down<2>(blk, nblocks, p, cr, dr, sr, acc); break;
+                case 3: row_down<3>(blk, nblocks, p, cr, dr, sr, acc); break;
+                default: row_down<4>(blk, nblocks, p, cr, dr, sr, acc); break;
             }
 #pragma unroll
             for (int r = 0; r < kR; ++r) {
@@ -461,7 +514,7 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_str
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ring.empty[slot]);
+        if (lane == 0) stage_release(ring, slot, cur.q);
         m = nm;  // the next octet's entries: second hop of the prefetch
         if (has_next) load_first(v.routes.slots, m, first);
     }

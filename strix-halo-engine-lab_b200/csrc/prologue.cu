@@ -19,6 +19,8 @@ namespace {
 
 constexpr u32 kRunElems = 2048, kWarps = 8;
 
+__device__ __forceinline__ u32 smem_addr(const void* p) { return static_cast<u32>(__cvta_generic_to_shared(p)); }
+
 struct PrologueArgs {
     b200moe_router_view r;
     b200moe_quantize_a8_view q;
@@ -60,6 +62,7 @@ __global__ void __launch_bounds__(kWarps * 32) prologue_decode_kernel(PrologueAr
     const u32 x_stride = rv.x_stride ? rv.x_stride : H;
     const u32 e = blockIdx.x * kWarps + warp;
     const float* wr = rv.weight + u64(min(e, E - 1)) * H;
+    const bool vec4 = (reinterpret_cast<uintptr_t>(rv.x) % 16 == 0) && x_stride % 4 == 0 && H % 4 == 0;
     float acc[RT];
 #pragma unroll
     for (int r = 0; r < RT; ++r) acc[r] = 0.0f;
@@ -69,8 +72,24 @@ __global__ void __launch_bounds__(kWarps * 32) prologue_decode_kernel(PrologueAr
 #pragma unroll
         for (u32 k = 0; k < kRunElems / 32; ++k) wv[k] = (lane + 32u * k < n_el) ? __ldg(wr + c0 + lane + 32u * k) : 0.0f;
         __syncthreads();  // the previous run has been consumed
-        for (u32 r = 0; r < rows; ++r)
-            for (u32 i = threadIdx.x; i < n_el; i += kWarps * 32) xs[r * kRunElems + i] = rv.x[u64(r) * x_stride + c0 + i];
+        // asynchronous copies: every request of the run is in flight at once (a load + store loop would pay the memory
+        // latency once per iteration)
+        if (vec4) {  // rows, strides and run starts are all multiples of four floats
+            for (u32 r = 0; r < rows; ++r) {
+                const float* src = rv.x + u64(r) * x_stride + c0;
+                const u32 dst = smem_addr(xs + r * kRunElems);
+                for (u32 i = threadIdx.x; i < n_el / 4; i += kWarps * 32)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * i), "l"(src + 4u * i) : "memory");
+            }
+        } else {
+            for (u32 r = 0; r < rows; ++r) {
+                const float* src = rv.x + u64(r) * x_stride + c0;
+                const u32 dst = smem_addr(xs + r * kRunElems);
+                for (u32 i = threadIdx.x; i < n_el; i += kWarps * 32)
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * i), "l"(src + i) : "memory");
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();
 #pragma unroll
         for (u32 k = 0; k < kRunElems / 32; ++k) {

@@ -66,11 +66,107 @@ __device__ __forceinline__ u32 k_pass(u32 key, const float* c, u32 n, u32 lane, 
     return pick;
 }
 
+// Fast path of one row, one warp: the row's choices live in registers (EPL per lane), no group limit, and no NaN among
+// the choices (then the serial scan of the contract is plain "largest choice, lowest id on ties", so a warp arg-max
+// per pass gives the same picks). Returns false - having written nothing - when the row needs the general path.
+// `s` = this warp's scratch of at least `experts` floats (shared memory).
+template <int EPL>
+__device__ __forceinline__ bool select_row_fast(const float* logits, float* scores_out, const float* __restrict__ bias,
+                                                const b200moe_route_policy& p, u32 row, u32 lane, float* s,
+                                                u32* __restrict__ ids, float* __restrict__ weights) {
+    const u32 E = p.experts;
+    const float* z = logits + u64(row) * E;
+    float sc[EPL], c[EPL];
+    const float ninf = -__uint_as_float(0x7f800000u);
+    if (p.score == B200MOE_SCORE_SOFTMAX) {  // route_policy.hpp:135-144
+        float zz[EPL];
+        float m = ninf;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) { const u32 e = lane + 32u * j; zz[j] = e < E ? z[e] : ninf; m = zz[j] > m ? zz[j] : m; }
+#pragma unroll
+        for (int d = 16; d; d >>= 1) { const float o = __shfl_xor_sync(0xffffffffu, m, d); m = o > m ? o : m; }
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) { const u32 e = lane + 32u * j; sc[j] = declared_exp(__fsub_rn(zz[j], m)); if (e < E) s[e] = sc[j]; }
+        __syncwarp();
+        float sum = 0.0f;
+#pragma unroll 8
+        for (u32 e = 0; e < E; ++e) sum = __fadd_rn(sum, s[e]);  // ascending serial sum (the declared order), every lane alike
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) sc[j] = __fdiv_rn(sc[j], sum);
+        __syncwarp();
+    } else {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            const u32 e = lane + 32u * j;
+            const float zj = e < E ? z[e] : 0.0f;
+            sc[j] = p.score == B200MOE_SCORE_SIGMOID ? sigmoid_score(zj) : sqrt_softplus_score(zj);
+        }
+    }
+    bool has_nan = false;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const u32 e = lane + 32u * j;
+        c[j] = (p.selection_bias && e < E) ? __fadd_rn(sc[j], bias[e]) : sc[j];
+        has_nan |= e < E && c[j] != c[j];
+    }
+    if (__any_sync(0xffffffffu, has_nan)) return false;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) { const u32 e = lane + 32u * j; if (e < E) s[e] = sc[j]; }  // scores for the weight step
+    if (scores_out) {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) { const u32 e = lane + 32u * j; if (e < E) scores_out[u64(row) * E + e] = sc[j]; }
+    }
+    __syncwarp();
+    u32 taken = 0, my_id = kNone;
+    for (u32 k = 0; k < p.top_k; ++k) {
+        u32 pick = kNone;
+        float best = 0.0f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            const u32 e = lane + 32u * j;
+            if (e < E && !((taken >> j) & 1u) && (pick == kNone || beats(p.key, c[j], e, best, pick))) { pick = e; best = c[j]; }
+        }
+#pragma unroll
+        for (int d = 16; d; d >>= 1) {
+            const u32 op = __shfl_xor_sync(0xffffffffu, pick, d);
+            const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+            if (op != kNone && (pick == kNone || beats(p.key, ob, op, best, pick))) { pick = op; best = ob; }
+        }
+        if ((pick & 31u) == lane) taken |= 1u << (pick >> 5);
+        if (lane == k) my_id = pick;
+    }
+    if (p.order == B200MOE_ORDER_ASCENDING_ID) {
+        u32 rank = 0;
+        for (u32 k = 0; k < p.top_k; ++k) { const u32 o = __shfl_sync(0xffffffffu, my_id, k); rank += (o < my_id) ? 1u : 0u; }
+        u32 sorted = kNone;
+        for (u32 k = 0; k < p.top_k; ++k) {
+            const u32 o = __shfl_sync(0xffffffffu, my_id, k), orank = __shfl_sync(0xffffffffu, rank, k);
+            if (orank == lane) sorted = o;
+        }
+        my_id = sorted;
+    }
+    const float my_s = (lane < p.top_k && my_id != kNone) ? s[my_id] : 0.0f;
+    float sum = 0.0f;  // ((0 + s0) + s1) + ... in output order (route_policy.hpp:121-123)
+    for (u32 k = 0; k < p.top_k; ++k) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_s, k));
+    const bool renorm = p.renormalize && (p.top_k > 1 || p.renorm_single);
+    const float den = __fadd_rn(sum, p.renorm_eps);
+    if (lane < p.top_k) {
+        ids[u64(row) * p.top_k + lane] = my_id;
+        weights[u64(row) * p.top_k + lane] = __fmul_rn(renorm ? __fdiv_rn(my_s, den) : my_s, p.scale);
+    }
+    return true;
+}
+
 // One warp selects one row. `s` points to this warp's scratch of 2 * experts + 32 floats (shared memory).
 __device__ __forceinline__ void select_row(const float* logits, float* scores_out, const float* __restrict__ bias,
                                            const b200moe_route_policy& p, u32 row, u32 lane, float* s,
                                            u32* __restrict__ ids, float* __restrict__ weights) {
     const u32 E = p.experts;
+    if (p.n_group == 1 && E <= 256) {  // registers hold the row: the fast path unless a NaN choice needs the serial rule
+        const bool done = E <= 128 ? select_row_fast<4>(logits, scores_out, bias, p, row, lane, s, ids, weights)
+                                   : select_row_fast<8>(logits, scores_out, bias, p, row, lane, s, ids, weights);
+        if (done) return;
+    }
     float* c = s + E;
     float* gs = c + E;
     const float* z = logits + u64(row) * E;

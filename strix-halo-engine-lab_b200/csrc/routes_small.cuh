@@ -52,10 +52,72 @@ __device__ inline void row_order(const u32* ids, u32 row, u32 top_k, u32 experts
 
 __device__ __forceinline__ bool owned(u32 e, u32 experts, u32 first, u32 end) { return e < experts && e >= first && e < end; }
 
+// Windows of up to 256 slots (decode): every slot's thread counts what it needs directly from the ids in shared memory
+// - O(slots) work per thread, three block barriers, no scans. Same outputs as the general body below.
+__device__ inline void routes_tiny_body(const b200moe_routes_view& v, u32 end) {
+    __shared__ u32 sid[256], srank[256], red[4];
+    const u32 t = threadIdx.x, nt = blockDim.x, n = v.rows * v.top_k, K = v.top_k;
+    if (t < 4) red[t] = 0;
+    for (u32 s = t; s < n; s += nt) {
+        const u32 e = v.ids[s];
+        sid[s] = owned(e, v.experts, v.first, end) ? e : 0xffffffffu;
+    }
+    __syncthreads();
+    for (u32 s = t; s < n; s += nt) {  // rank among the slots of the same expert (ascending slot = ascending row)
+        const u32 e = sid[s];
+        u32 rank = 0;
+        for (u32 i = 0; i < s; ++i) rank += sid[i] == e ? 1u : 0u;
+        srank[s] = rank;
+    }
+    __syncthreads();
+    for (u32 s = t; s < n; s += nt) {
+        const u32 e = sid[s];
+        // the row's order, low count and route check (every slot places itself)
+        {
+            const u32 row = s / K, raw = v.ids[s];
+            u32 pos = 0, low = 0;
+            bool bad = raw >= v.experts;
+            for (u32 k = 0; k < K; ++k) {
+                const u32 o = v.ids[row * K + k], so = row * K + k;
+                pos += (o < raw || (o == raw && so < s)) ? 1u : 0u;
+                bad |= (o == raw && so != s);
+                low += o < v.split ? 1u : 0u;
+            }
+            v.out.order[row * K + pos] = s;
+            if (s == row * K) v.out.low_counts[row] = low;
+            if (bad && v.row_status) atomicOr(&v.row_status[row], B200MOE_ROW_INVALID_ROUTE);
+        }
+        if (e == 0xffffffffu) continue;
+        u32 before = 0, uidx = 0, cnt = 0;
+        for (u32 i = 0; i < n; ++i) {
+            const u32 o = sid[i];
+            before += o < e ? 1u : 0u;                          // 0xffffffff (not owned) is never below e
+            uidx += (o < e && srank[i] == 0) ? 1u : 0u;
+            cnt += o == e ? 1u : 0u;
+        }
+        const u32 rank = srank[s], pos = before + rank;
+        v.out.rows[pos] = s / K;
+        v.out.slots[pos] = s;
+        if (rank == 0) {
+            v.out.experts[uidx] = e - v.base;
+            v.out.begins[uidx + 1] = before + cnt;
+            atomicAdd(&red[0], 1u);
+            atomicMax(&red[1], cnt);
+            atomicAdd(&red[2], cnt);
+        }
+    }
+    __syncthreads();
+    if (t == 0) {
+        v.out.begins[0] = 0;
+        v.out.counts[0] = red[0]; v.out.counts[1] = red[1]; v.out.counts[2] = red[2]; v.out.counts[3] = 0;
+    }
+}
+
 // The whole build by one block. Each thread owns a contiguous run of experts for the scans.
 __device__ inline void routes_small_body(const b200moe_routes_view& v, u32 end) {
     __shared__ u32 cnt[1024], ebegin[1024], sid[1024], warp_tot[32], total_s, union_s, maxc;
     const u32 t = threadIdx.x, nt = blockDim.x, n = v.rows * v.top_k;
+    if (n <= 256) { routes_tiny_body(v, end); return; }
     for (u32 i = t; i < 1024; i += nt) cnt[i] = 0;
     if (t == 0) maxc = 0;
     __syncthreads();
