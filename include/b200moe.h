@@ -174,6 +174,19 @@ typedef struct b200moe_routes_view {
 uint64_t b200moe_routes_scratch_words(uint32_t rows, uint32_t top_k, uint32_t experts);
 int b200moe_build_routes(const b200moe_routes_view* view, void* stream);
 
+/* The same build with the library's own scratch: view->scratch is ignored, and the call allocates no device memory
+ * (no cudaMalloc / cudaFree, no allocating library routine). This entry point has no counterpart in the reference; it
+ * exists for callers that own no device allocator and whose buffers were all fixed when the engine loaded. The scratch
+ * is one fixed array per device inside the library, b200moe_routes_static_max_words() words long: a window whose
+ * b200moe_routes_scratch_words(rows, top_k, experts) exceeds that is refused with B200MOE_ERR_UNSUPPORTED and a message
+ * that names both numbers (65,536 slots at 1024 experts fit). The array keeps whatever the previous call left; no word
+ * of it is read before the same call has written it, so nothing needs clearing. It is shared by every caller of the
+ * process: two calls that overlap in time on one device (two streams, two threads) race on it - serialise them. The
+ * first call on each device looks up the array's address with that device current; make that call during set-up,
+ * before any stream capture begins. Results are identical to b200moe_build_routes. */
+uint64_t b200moe_routes_static_max_words(void);
+int b200moe_build_routes_static(const b200moe_routes_view* view, void* stream);
+
 /* ------------------------------------------------------------------------------------------------ experts
  * Geometry and formats of the routed experts of one layer. The gate/up type fixes the arithmetic family:
  *   Q8_0 (DS41 family, src/ds41_formats.cpp:188-197, src/ds41_moe.cpp:124-165): product_q8_0 lane classes and

@@ -112,7 +112,8 @@ class DenseView(C.Structure):
 
 # every symbol include/b200moe.h declares (tests check that the library exports each of them)
 EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_quantize_a8", "b200moe_q8_0_a8",
-           "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_gate_row_bytes",
+           "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_routes_static_max_words",
+           "b200moe_build_routes_static", "b200moe_gate_row_bytes",
            "b200moe_down_row_bytes", "b200moe_expert_bytes", "b200moe_gate_up", "b200moe_down", "b200moe_combine",
            "b200moe_canonical_sum", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
            "b200moe_ffn", "b200moe_ffn_host", "b200moe_dense_ffn"]
@@ -132,13 +133,16 @@ def lib():
         for n in ("b200moe_gate_row_bytes", "b200moe_down_row_bytes", "b200moe_expert_bytes"):
             getattr(L, n).restype = u64
             getattr(L, n).argtypes = [C.POINTER(Shape)]
+        L.b200moe_routes_static_max_words.restype = u64
+        L.b200moe_routes_static_max_words.argtypes = []
         L.b200moe_routes_scratch_words.restype = u64
         L.b200moe_routes_scratch_words.argtypes = [u32, u32, u32]
         for n in ("b200moe_layer_workspace_bytes", "b200moe_ffn_workspace_bytes"):
             getattr(L, n).restype = u64
             getattr(L, n).argtypes = [C.POINTER(Shape), u32]
         for n, t in (("b200moe_quantize_a8", QuantizeA8View), ("b200moe_q8_0_a8", Q8A8View), ("b200moe_router", RouterView),
-                     ("b200moe_build_routes", RoutesView), ("b200moe_gate_up", GateUpView), ("b200moe_down", DownView),
+                     ("b200moe_build_routes", RoutesView), ("b200moe_build_routes_static", RoutesView),
+                     ("b200moe_gate_up", GateUpView), ("b200moe_down", DownView),
                      ("b200moe_combine", CombineView), ("b200moe_layer", LayerView), ("b200moe_ffn", FfnView),
                      ("b200moe_dense_ffn", DenseView)):
             getattr(L, n).restype = C.c_int

@@ -84,6 +84,15 @@ def enqueue_moe_routes(ids, experts, split, first=0, end=0, base=0, row_status=N
     return r
 
 
+def enqueue_moe_routes_static(ids, experts, split, first=0, end=0, base=0, row_status=None, out=None):
+    """b200moe_build_routes_static: the same routes with the library's built-in scratch (no scratch argument)."""
+    rows, top_k = ids.shape
+    r = out if out is not None else MoeRoutes(rows, top_k, experts, ids.device)
+    v = RoutesView(ptr(ids), rows, top_k, experts, split, first, end, base, None, ptr(row_status), r.struct())
+    check(lib().b200moe_build_routes_static(C.byref(v), stream_ptr()))
+    return r
+
+
 def enqueue_routed_gate_up(shape, gate, up, routes, max_union, x, slots, taps=False, row_status=None, summary=None):
     """x = (codes, deltas, sums) of the MoE input; returns act = (codes, deltas, sums) [slots][inter] (+ gate, up taps)."""
     dev = gate.device
