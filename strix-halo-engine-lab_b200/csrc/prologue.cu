@@ -5,9 +5,9 @@
 // order without fused multiply-add (src/ds41_moe.cpp:72-82), the route policy's transforms and k-pass selection
 // (include/strix/moe/route_policy.hpp:99-156), build_window_routes (src/ds41_moe.cpp:11-61). Bits do not change.
 //
-// Shape: blocks [0, logit_blocks) take eight experts each, one warp per expert. A warp issues the 64 loads of its
-// expert's current 2048-wide run up front (64 independent 128-byte requests in flight), the block stages the same run
-// of every activation row in shared memory meanwhile, then each lane walks its lane class in ascending order. The
+// Shape: blocks [0, logit_blocks) take eight experts each, one warp per expert. A warp copies its expert's current
+// 2048-wide run to shared memory asynchronously, the block does the same with that run of every activation row, then
+// each lane walks its lane class in ascending order. The
 // block that finishes last (a ticket counter in the workspace) runs selection (one warp per row) and the routes.
 // Blocks past logit_blocks quantise the activations. Everything the expert kernels need is ready after this launch.
 #include "kernels.cuh"
@@ -32,7 +32,7 @@ struct PrologueArgs {
 
 template <int RT>
 __global__ void __launch_bounds__(kWarps * 32) prologue_decode_kernel(PrologueArgs a) {
-    extern __shared__ __align__(16) float xs[];  // [rows][kRunElems] while the logits run, select scratch afterwards
+    extern __shared__ __align__(16) float xs[];  // [rows + kWarps][kRunElems] while the logits run, select scratch afterwards
     __shared__ u32 s_last;
     const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
 
@@ -63,41 +63,47 @@ __global__ void __launch_bounds__(kWarps * 32) prologue_decode_kernel(PrologueAr
     const u32 e = blockIdx.x * kWarps + warp;
     const float* wr = rv.weight + u64(min(e, E - 1)) * H;
     const bool vec4 = (reinterpret_cast<uintptr_t>(rv.x) % 16 == 0) && x_stride % 4 == 0 && H % 4 == 0;
+    const bool wvec4 = (reinterpret_cast<uintptr_t>(rv.weight) % 16 == 0) && H % 4 == 0;
+    float* ws = xs + rows * kRunElems + warp * kRunElems;  // this warp's expert row run
     float acc[RT];
 #pragma unroll
     for (int r = 0; r < RT; ++r) acc[r] = 0.0f;
+    // Both operands are staged with asynchronous copies from short rolled loops: every request of the run is in flight
+    // at once, and the code stays small (this kernel runs once per step on cold instruction caches, so straight-line
+    // unrolled code would pay a fetch miss per line).
     for (u32 c0 = 0; c0 < H; c0 += kRunElems) {
         const u32 n_el = min(kRunElems, H - c0);
-        float wv[kRunElems / 32];
-#pragma unroll
-        for (u32 k = 0; k < kRunElems / 32; ++k) wv[k] = (lane + 32u * k < n_el) ? __ldg(wr + c0 + lane + 32u * k) : 0.0f;
         __syncthreads();  // the previous run has been consumed
-        // asynchronous copies: every request of the run is in flight at once (a load + store loop would pay the memory
-        // latency once per iteration)
-        if (vec4) {  // rows, strides and run starts are all multiples of four floats
-            for (u32 r = 0; r < rows; ++r) {
-                const float* src = rv.x + u64(r) * x_stride + c0;
-                const u32 dst = smem_addr(xs + r * kRunElems);
+        {
+            const float* src = wr + c0;
+            const u32 dst = smem_addr(ws);
+            if (wvec4) {
+                for (u32 i = lane; i < n_el / 4; i += 32)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * i), "l"(src + 4u * i) : "memory");
+            } else {
+                for (u32 i = lane; i < n_el; i += 32)
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * i), "l"(src + i) : "memory");
+            }
+        }
+        for (u32 r = 0; r < rows; ++r) {
+            const float* src = rv.x + u64(r) * x_stride + c0;
+            const u32 dst = smem_addr(xs + r * kRunElems);
+            if (vec4) {  // rows, strides and run starts are all multiples of four floats
                 for (u32 i = threadIdx.x; i < n_el / 4; i += kWarps * 32)
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * i), "l"(src + 4u * i) : "memory");
-            }
-        } else {
-            for (u32 r = 0; r < rows; ++r) {
-                const float* src = rv.x + u64(r) * x_stride + c0;
-                const u32 dst = smem_addr(xs + r * kRunElems);
+            } else {
                 for (u32 i = threadIdx.x; i < n_el; i += kWarps * 32)
                     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * i), "l"(src + i) : "memory");
             }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();
+#pragma unroll 4
+        for (u32 i = lane; i < n_el; i += 32) {  // the lane class in ascending order (src/ds41_moe.cpp:72-82)
+            const float w = ws[i];
 #pragma unroll
-        for (u32 k = 0; k < kRunElems / 32; ++k) {
-            if (lane + 32u * k < n_el) {
-#pragma unroll
-                for (int r = 0; r < RT; ++r)
-                    if (r < (int)rows) acc[r] = __fadd_rn(acc[r], __fmul_rn(wv[k], xs[r * kRunElems + lane + 32u * k]));
-            }
+            for (int r = 0; r < RT; ++r)
+                if (r < (int)rows) acc[r] = __fadd_rn(acc[r], __fmul_rn(w, xs[r * kRunElems + i]));
         }
     }
 #pragma unroll
@@ -134,7 +140,7 @@ int launch_prologue(const b200moe_router_view& r, const b200moe_quantize_a8_view
     a.r = r; a.q = q; a.routes = routes; a.routes_end = routes.end ? routes.end : routes.experts; a.ticket = ticket;
     a.logit_blocks = (r.policy.experts + kWarps - 1) / kWarps;
     const u32 quant_blocks = static_cast<u32>((u64(q.rows) * (q.width / 32) + kWarps - 1) / kWarps);
-    const u32 smem = std::max<u32>(r.rows * kRunElems * 4u, kWarps * (2u * r.policy.experts + 32u) * 4u);
+    const u32 smem = std::max<u32>((r.rows + kWarps) * kRunElems * 4u, kWarps * (2u * r.policy.experts + 32u) * 4u);
     const dim3 grid(a.logit_blocks + quant_blocks);
 #define B200_PRO(RT)                                                                                            \
     {                                                                                                           \
