@@ -3,7 +3,8 @@
 // Same arithmetic as gemv_q4k.cu (the contract of src/cpu/core/routed_expert.hpp:9-15, bit for bit); what changes is how
 // the bytes reach the SM and how few instructions touch each byte.
 //
-//  * One persistent CTA per SM walks work items (expert, 32-output group | 64 hidden outputs) round-robin.
+//  * One persistent CTA per SM walks a contiguous run of work items (expert, 32-output group | 64 hidden outputs); the
+//    runs are cut by estimated cost (entries per expert), not by count, so the CTAs finish together.
 //  * A producer warp streams weight rows - contiguous, 16-byte aligned GGUF bytes - into a ring of shared-memory stages
 //    with cp.async.bulk (global -> shared, completion counted on an mbarrier). A stage holds one OCTET = 8 weight rows;
 //    rows are laid down with a stride whose 16-byte count is odd, which makes the consumers' 128-bit reads conflict free.
@@ -101,11 +102,13 @@ struct Ring {
 };
 
 __device__ __forceinline__ void ring_init(const Ring& r, u32 stages) {
-    if (threadIdx.x == 0) {
-        for (u32 s = 0; s < stages; ++s) { mbar_init(&r.full[s], 1); r.gen[s] = 0; r.rel[s] = 0; }
-        *r.abort_flag = 0;
+    if (threadIdx.x < stages) {
+        mbar_init(&r.full[threadIdx.x], 1);
+        r.gen[threadIdx.x] = 0;
+        r.rel[threadIdx.x] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x == 0) *r.abort_flag = 0;
     __syncthreads();
 }
 // Bounded spin until *word == want; false when the limit ran out or another role aborted.
@@ -137,10 +140,10 @@ __device__ __forceinline__ void stage_release(const Ring& ring, u32 slot, u32 q)
 // four warps of eight lanes reach it (measured on B200: 1 warp 3.0 TB/s, 2 warps 5.8, 4 warps 6.5).
 // `row_of(item, octet)` gives the first of the octet's 8 consecutive weight rows.
 template <class RowOf>
-__device__ __forceinline__ void produce(const Ring& ring, const StreamPlan& plan, u32 n_items, u32 pw, RowOf row_of) {
+__device__ __forceinline__ void produce(const Ring& ring, const StreamPlan& plan, u32 first_item, u32 n_local, u32 pw, RowOf row_of) {
     const u32 lane = threadIdx.x & 31u;
     const bool one_copy = plan.row_stride == plan.row_bytes;  // rows already conflict free: one copy per octet
-    const u32 local_octets = (n_items > blockIdx.x ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0) * kOctetsPerItem;
+    const u32 local_octets = n_local * kOctetsPerItem;
     u32 slot = pw % plan.stages, phase = (pw / plan.stages) & 1u, q = pw;
     bool ok = true;
     for (; q < local_octets; q += kProducers) {
@@ -148,7 +151,7 @@ __device__ __forceinline__ void produce(const Ring& ring, const StreamPlan& plan
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the consumers' reads precede the copies below
-        const unsigned char* src = row_of(blockIdx.x + (q >> 3) * gridDim.x, q & 7u);
+        const unsigned char* src = row_of(first_item + (q >> 3), q & 7u);
         unsigned char* dst = ring.data + u64(slot) * plan.stage_bytes;
         if (lane == 0) {
             ring.gen[slot] = q + 1u;
@@ -172,6 +175,43 @@ __device__ __forceinline__ void produce(const Ring& ring, const StreamPlan& plan
     }
 }
 
+// Work split: every CTA takes a contiguous run of items (expert-major, chunks ascending) of about equal COST, not
+// equal count: an item of an expert with ne entries costs the fixed per-block decode once per pass of up to kR entries
+// plus the per-entry dots, roughly 3 * ceil(ne / kR) + 2 * ne. Item i belongs to CTA b when its cumulative cost start
+// lies in [total * b / G, total * (b + 1) / G). Every warp computes the run itself (two short warp scans over the
+// union's counts), so no barrier is involved. Returns the first item and the count.
+__device__ __forceinline__ u32 item_cost(u32 ne) { return 3u * ((ne + kR - 1) / kR) + 2u * ne; }
+__device__ __forceinline__ u32 warp_inclusive_scan(u32 v, u32 lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { const u32 o = __shfl_up_sync(0xffffffffu, v, d); if (lane >= (u32)d) v += o; }
+    return v;
+}
+__device__ __forceinline__ void item_range(const StreamPlan& plan, const b200moe_routes& routes, u32 n_union, u32* first_item, u32* n_local) {
+    const u32 lane = threadIdx.x & 31u, G = gridDim.x, b = blockIdx.x, nc = plan.n_chunks;
+    u32 total = 0;
+    for (u32 j0 = 0; j0 < n_union; j0 += 32) {
+        const u32 j = j0 + lane;
+        const u32 c = j < n_union ? item_cost(__ldg(routes.begins + j + 1) - __ldg(routes.begins + j)) * nc : 0u;
+        total += __shfl_sync(0xffffffffu, warp_inclusive_scan(c, lane), 31);
+    }
+    const u32 n_items = n_union * nc;
+    const u32 B0 = static_cast<u32>(u64(total) * b / G), B1 = static_cast<u32>(u64(total) * (b + 1) / G);
+    u32 lo = n_items, hi = n_items, cum = 0;  // a boundary at `total` means "past the last item"
+    for (u32 j0 = 0; j0 < n_union; j0 += 32) {
+        const u32 j = j0 + lane;
+        const u32 ci = j < n_union ? item_cost(__ldg(routes.begins + j + 1) - __ldg(routes.begins + j)) : 0u;
+        const u32 c = ci * nc, incl = warp_inclusive_scan(c, lane), excl = cum + incl - c;
+        const bool h0 = c && B0 >= excl && B0 < excl + c, h1 = c && B1 >= excl && B1 < excl + c;
+        const u32 c0 = h0 ? j * nc + (B0 - excl + ci - 1) / ci : 0u, c1 = h1 ? j * nc + (B1 - excl + ci - 1) / ci : 0u;
+        const u32 m0 = __ballot_sync(0xffffffffu, h0), m1 = __ballot_sync(0xffffffffu, h1);
+        if (m0) lo = __shfl_sync(0xffffffffu, c0, __ffs(m0) - 1);
+        if (m1) hi = __shfl_sync(0xffffffffu, c1, __ffs(m1) - 1);
+        cum += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    *first_item = lo;
+    *n_local = hi - lo;
+}
+
 // item -> (union expert j, chunk) without a hardware division.
 __device__ __forceinline__ void split_item(const StreamPlan& plan, u32 item, u32* j, u32* chunk) {
     *j = plan.n_chunks == 1 ? item : __umulhi(item, plan.chunk_magic);
@@ -190,10 +230,10 @@ struct Cursor {
 // Entry metadata of the item an octet belongs to, fetched one octet ahead so that its two dependent global loads
 // (begins[j], then the first entries' ids) hide behind the current octet's arithmetic.
 struct Meta { u32 chunk, eb, ne; };
-__device__ __forceinline__ Meta load_meta(const StreamPlan& plan, const b200moe_routes& routes, u32 q) {
+__device__ __forceinline__ Meta load_meta(const StreamPlan& plan, const b200moe_routes& routes, u32 item) {
     u32 j;
     Meta m;
-    split_item(plan, blockIdx.x + (q >> 3) * gridDim.x, &j, &m.chunk);
+    split_item(plan, item, &j, &m.chunk);
     m.eb = __ldg(routes.begins + j);
     m.ne = __ldg(routes.begins + j + 1) - m.eb;
     return m;
@@ -303,18 +343,40 @@ __device__ __forceinline__ void row_down(const uint4* blk, u32 nblocks, u32 p, c
 // ---- gate/up ---------------------------------------------------------------------------------------------------------
 // A8 input rows in shared memory, per row: codes[H] with the two 16-byte chunks of every 32-byte half swapped for
 // pairs 2 and 3 (bank spread), then per (super-block, pair) 16 bytes {E_2p, E_2p+1, float(S_2p), float(S_2p+1)}.
-__device__ __forceinline__ void copy_x_rows(const b200moe_a8_rows& x, u32 rows, u32 H, unsigned char* dst, u32 nthreads) {
-    const u32 stride = x.stride ? x.stride : x.width, row_bytes = H + H / 4;
+// Issued as asynchronous copies from short loops, so that every request is in flight at once; the sums arrive as
+// integers in the pack's last two words and are converted in place by finish_x_rows once the copies have landed.
+__device__ __forceinline__ void cp_async(u32 dst, const void* src, int bytes) {
+    if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    else if (bytes == 8) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_x_rows_async(const b200moe_a8_rows& x, u32 rows, u32 H, unsigned char* dst, u32 nthreads) {
+    const u32 stride = x.stride ? x.stride : x.width, row_bytes = H + H / 4, gs = stride / 32;
+    const bool al8 = (reinterpret_cast<uintptr_t>(x.deltas) % 8 == 0) && (reinterpret_cast<uintptr_t>(x.sums) % 8 == 0) && gs % 2 == 0;
     for (u32 r = 0; r < rows; ++r) {
-        const uint4* src = reinterpret_cast<const uint4*>(x.codes + u64(r) * stride);
-        uint4* d = reinterpret_cast<uint4*>(dst + u64(r) * row_bytes);
-        for (u32 c = threadIdx.x; c < H / 16; c += nthreads) d[c ^ ((c >> 3) & 1u)] = src[c];
-        float4* es = reinterpret_cast<float4*>(dst + u64(r) * row_bytes + H);
-        for (u32 g2 = threadIdx.x; g2 < H / 64; g2 += nthreads) {
-            const float2 e = *reinterpret_cast<const float2*>(x.deltas + u64(r) * (stride / 32) + 2 * g2);
-            const int2 s = *reinterpret_cast<const int2*>(x.sums + u64(r) * (stride / 32) + 2 * g2);
-            es[g2] = make_float4(e.x, e.y, static_cast<float>(s.x), static_cast<float>(s.y));
+        const i8* src = x.codes + u64(r) * stride;  // 16-byte aligned rows (checked by the caller)
+        const u32 d = saddr(dst + u64(r) * row_bytes);
+        for (u32 c = threadIdx.x; c < H / 16; c += nthreads) cp_async(d + 16u * (c ^ ((c >> 3) & 1u)), src + 16u * c, 16);
+        const u32 es = d + H;
+        const float* dl = x.deltas + u64(r) * gs;
+        const i32* sm = x.sums + u64(r) * gs;
+        if (al8) {
+            for (u32 g2 = threadIdx.x; g2 < H / 64; g2 += nthreads) { cp_async(es + 16u * g2, dl + 2 * g2, 8); cp_async(es + 16u * g2 + 8u, sm + 2 * g2, 8); }
+        } else {
+            for (u32 g = threadIdx.x; g < H / 32; g += nthreads) {
+                cp_async(es + 16u * (g >> 1) + 4u * (g & 1u), dl + g, 4);
+                cp_async(es + 16u * (g >> 1) + 8u + 4u * (g & 1u), sm + g, 4);
+            }
         }
+    }
+}
+__device__ __forceinline__ void finish_x_rows(u32 rows, u32 H, unsigned char* dst, u32 nthreads) {
+    const u32 row_bytes = H + H / 4;
+    for (u32 i = threadIdx.x; i < rows * (H / 64); i += nthreads) {
+        const u32 r = i / (H / 64), g2 = i - r * (H / 64);
+        int2* s = reinterpret_cast<int2*>(dst + u64(r) * row_bytes + H + 16u * g2 + 8u);
+        const int2 v = *s;
+        *reinterpret_cast<float2*>(s) = make_float2(static_cast<float>(v.x), static_cast<float>(v.y));
     }
 }
 
@@ -338,11 +400,13 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) gate_up_q4k_
     ring_init(ring, plan.stages);
 
     const u32 warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const u32 n_items = v.routes.counts[0] * plan.n_chunks;
+    const u32 n_union = v.routes.counts[0];
     const u64 row_bytes = plan.row_bytes;
+    u32 first_item, n_local;
 
     if (warp >= plan.warps) {  // ------------------------------------------------------------- producer warps
-        produce(ring, plan, n_items, warp - plan.warps, [&](u32 item, u32 o) {
+        item_range(plan, v.routes, n_union, &first_item, &n_local);
+        produce(ring, plan, first_item, n_local, warp - plan.warps, [&](u32 item, u32 o) {
             u32 j, gx;
             split_item(plan, item, &j, &gx);
             const u64 row = u64(v.routes.experts[j]) * I + 32u * gx + 8u * (o & 3u);
@@ -352,22 +416,27 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) gate_up_q4k_
     }
 
     // ------------------------------------------------------------------------------------------ consumer warps
-    copy_x_rows(v.x, plan.x_rows, H, x_copy, plan.warps * 32);
-    asm volatile("bar.sync 1, %0;" ::"r"(plan.warps * 32) : "memory");
+    copy_x_rows_async(v.x, plan.x_rows, H, x_copy, plan.warps * 32);  // in flight while the item run is worked out
+    item_range(plan, v.routes, n_union, &first_item, &n_local);
     const u32 x_row_bytes = H + H / 4;
     const u32 rsub = lane >> 2, p = lane & 3u;
     const u32 swz = p >> 1;  // chunk swap of the staged codes
     const u32 act_stride = v.act.stride ? v.act.stride : v.act.width;
-    const u32 local_octets = (n_items > blockIdx.x ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0) * kOctetsPerItem;
+    const u32 local_octets = n_local * kOctetsPerItem;
     bool ok = true;
     Meta m{};
     u32 first[kR];
-    if (warp < local_octets) { m = load_meta(plan, v.routes, warp); load_first(v.routes.rows, m, first); }
+    if (warp < local_octets) m = load_meta(plan, v.routes, first_item + (warp >> 3));
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"r"(plan.warps * 32) : "memory");
+    finish_x_rows(plan.x_rows, H, x_copy, plan.warps * 32);
+    asm volatile("bar.sync 1, %0;" ::"r"(plan.warps * 32) : "memory");
+    if (warp < local_octets) load_first(v.routes.rows, m, first);
     for (Cursor cur{warp, warp % plan.stages, (warp / plan.stages) & 1u}; cur.q < local_octets; cur.advance(plan)) {
         const u32 slot = cur.slot, local_item = cur.q >> 3, o = cur.q & 7u;
         const bool has_next = cur.q + plan.warps < local_octets;
         Meta nm{};
-        if (has_next) nm = load_meta(plan, v.routes, cur.q + plan.warps);
+        if (has_next) nm = load_meta(plan, v.routes, first_item + ((cur.q + plan.warps) >> 3));
         const u32 gx = m.chunk, eb = m.eb, ne = min(m.ne, ME);
         const u32 islot = local_item & (plan.item_slots - 1);
         float* s_g = s_gu + u64(islot) * 2 * ME * 32;
@@ -452,10 +521,12 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_str
     if (v.summary && (*v.summary & ~kAbortBit)) return;  // a failed projection skips the whole stage (routed_expert.hpp:17-19)
 
     const u32 warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const u32 n_items = v.routes.counts[0] * plan.n_chunks;
+    const u32 n_union = v.routes.counts[0];
     const u64 row_bytes = plan.row_bytes;
+    u32 first_item, n_local;
+    item_range(plan, v.routes, n_union, &first_item, &n_local);
     if (warp >= plan.warps) {
-        produce(ring, plan, n_items, warp - plan.warps, [&](u32 item, u32 o) {
+        produce(ring, plan, first_item, n_local, warp - plan.warps, [&](u32 item, u32 o) {
             u32 j, cx;
             split_item(plan, item, &j, &cx);
             const u64 row = u64(v.routes.experts[j]) * H + 64u * cx + 8u * o;
@@ -466,16 +537,16 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_str
 
     const u32 act_stride = v.act.stride ? v.act.stride : v.act.width;
     const u32 rsub = lane >> 2, p = lane & 3u;
-    const u32 local_octets = (n_items > blockIdx.x ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0) * kOctetsPerItem;
+    const u32 local_octets = n_local * kOctetsPerItem;
     bool ok = true;
     Meta m{};
     u32 first[kR];
-    if (warp < local_octets) { m = load_meta(plan, v.routes, warp); load_first(v.routes.slots, m, first); }
+    if (warp < local_octets) { m = load_meta(plan, v.routes, first_item + (warp >> 3)); load_first(v.routes.slots, m, first); }
     for (Cursor cur{warp, warp % plan.stages, (warp / plan.stages) & 1u}; cur.q < local_octets; cur.advance(plan)) {
         const u32 slot = cur.slot, o = cur.q & 7u;
         const bool has_next = cur.q + plan.warps < local_octets;
         Meta nm{};
-        if (has_next) nm = load_meta(plan, v.routes, cur.q + plan.warps);
+        if (has_next) nm = load_meta(plan, v.routes, first_item + ((cur.q + plan.warps) >> 3));
         const u32 cx = m.chunk, eb = m.eb, ne = m.ne;
         if (ok) ok = stage_wait(ring, slot, cur.q, cur.phase);
         ok = __all_sync(0xffffffffu, ok);
