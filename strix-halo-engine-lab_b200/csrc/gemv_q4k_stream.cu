@@ -86,6 +86,7 @@ struct StreamPlan {
     u32 item_slots;    // power of two: item state ring (gate/up)
     u32 max_entries;   // bound of the entries of one expert (the window's rows)
     u32 x_rows;        // rows of the A8 input copied to shared memory (gate/up)
+    u32 stage_entries; // entries of the CTA's run whose activations are copied to shared memory (down)
 };
 
 // Ring of stages. An mbarrier's phase test only tells odd from even uses of a slot, and here the successive uses of a
@@ -318,7 +319,8 @@ __device__ __forceinline__ void row_gate_up(const uint4* blk, u32 nblocks, u32 p
         }
     }
 }
-// The same against NR A8 rows in global memory (down form: codes / deltas / sums of the slots' activations).
+// The same against NR A8 rows given by generic pointers (down form: codes / deltas / sums of the slots' activations,
+// staged in shared memory for the first entries of the CTA's run, in global memory beyond).
 template <int NR>
 __device__ __forceinline__ void row_down(const uint4* blk, u32 nblocks, u32 p, const i8* const* cr, const float* const* dr, const i32* const* sr,
                                          float* acc) {
@@ -330,9 +332,9 @@ __device__ __forceinline__ void row_down(const uint4* blk, u32 nblocks, u32 p, c
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
             const uint4* c = reinterpret_cast<const uint4*>(cr[r] + 256u * b);
-            const uint4 c0 = __ldg(c), c1 = __ldg(c + 1), c2 = __ldg(c + 2), c3 = __ldg(c + 3);
-            const float2 e = __ldg(reinterpret_cast<const float2*>(dr[r] + 8u * b));
-            const int2 sm = __ldg(reinterpret_cast<const int2*>(sr[r] + 8u * b));
+            const uint4 c0 = c[0], c1 = c[1], c2 = c[2], c3 = c[3];
+            const float2 e = *reinterpret_cast<const float2*>(dr[r] + 8u * b);
+            const int2 sm = *reinterpret_cast<const int2*>(sr[r] + 8u * b);
             int lo, hi;
             dots(n, c0, c1, c2, c3, &lo, &hi);
             acc[r] = __fadd_rn(acc[r], pair_value(f, lo, hi, e.x, e.y, small_int_to_float(sm.x), small_int_to_float(sm.y)));
@@ -542,6 +544,35 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_str
     Meta m{};
     u32 first[kR];
     if (warp < local_octets) { m = load_meta(plan, v.routes, first_item + (warp >> 3)); load_first(v.routes.slots, m, first); }
+    // The run's entries are contiguous in the routes; the activations of its first stage_entries entries are staged in
+    // shared memory (asynchronous copies, all in flight at once), the rest - rare - is read from global memory.
+    const u32 a_row = I + I / 4;  // codes, deltas, sums of one entry
+    unsigned char* a_copy = reinterpret_cast<unsigned char*>(s_flag + 4);
+    u32 eb_lo = 0, n_stage = 0;
+    if (n_local) {
+        u32 j_lo, j_hi, unused;
+        split_item(plan, first_item, &j_lo, &unused);
+        split_item(plan, first_item + n_local - 1u, &j_hi, &unused);
+        eb_lo = __ldg(v.routes.begins + j_lo);
+        n_stage = min(__ldg(v.routes.begins + j_hi + 1) - eb_lo, plan.stage_entries);
+        const u32 gs = act_stride / 32, nthreads = plan.warps * 32;
+        const bool al16 = (reinterpret_cast<uintptr_t>(v.act.deltas) % 16 == 0) && (reinterpret_cast<uintptr_t>(v.act.sums) % 16 == 0) && gs % 4 == 0 && I % 128 == 0;
+        for (u32 e = 0; e < n_stage; ++e) {
+            const u32 sl = __ldg(v.routes.slots + eb_lo + e);
+            const u32 d = saddr(a_copy + u64(e) * a_row);
+            const i8* src = v.act.codes + u64(sl) * act_stride;
+            for (u32 c = threadIdx.x; c < I / 16; c += nthreads) cp_async(d + 16u * c, src + 16u * c, 16);
+            const float* dl = v.act.deltas + u64(sl) * gs;
+            const i32* sm = v.act.sums + u64(sl) * gs;
+            if (al16) {
+                for (u32 c = threadIdx.x; c < I / 128; c += nthreads) { cp_async(d + I + 16u * c, dl + 4 * c, 16); cp_async(d + I + I / 8 + 16u * c, sm + 4 * c, 16); }
+            } else {
+                for (u32 g = threadIdx.x; g < I / 32; g += nthreads) { cp_async(d + I + 4u * g, dl + g, 4); cp_async(d + I + I / 8 + 4u * g, sm + g, 4); }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"r"(plan.warps * 32) : "memory");
     for (Cursor cur{warp, warp % plan.stages, (warp / plan.stages) & 1u}; cur.q < local_octets; cur.advance(plan)) {
         const u32 slot = cur.slot, o = cur.q & 7u;
         const bool has_next = cur.q + plan.warps < local_octets;
@@ -561,10 +592,18 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_str
             const i32* sr[kR];
 #pragma unroll
             for (int r = 0; r < kR; ++r) {
-                sl[r] = e0 == 0 ? first[r] : v.routes.slots[eb + e0 + min(r, nr - 1)];
-                cr[r] = v.act.codes + u64(sl[r]) * act_stride + 64u * p;
-                dr[r] = v.act.deltas + u64(sl[r]) * (act_stride / 32) + 2u * p;
-                sr[r] = v.act.sums + u64(sl[r]) * (act_stride / 32) + 2u * p;
+                const u32 ent = eb + e0 + min(r, nr - 1);
+                sl[r] = e0 == 0 ? first[r] : v.routes.slots[ent];
+                if (ent - eb_lo < n_stage) {
+                    const unsigned char* a = a_copy + u64(ent - eb_lo) * a_row;
+                    cr[r] = reinterpret_cast<const i8*>(a) + 64u * p;
+                    dr[r] = reinterpret_cast<const float*>(a + I) + 2u * p;
+                    sr[r] = reinterpret_cast<const i32*>(a + I + I / 8) + 2u * p;
+                } else {
+                    cr[r] = v.act.codes + u64(sl[r]) * act_stride + 64u * p;
+                    dr[r] = v.act.deltas + u64(sl[r]) * (act_stride / 32) + 2u * p;
+                    sr[r] = v.act.sums + u64(sl[r]) * (act_stride / 32) + 2u * p;
+                }
             }
             float acc[kR];
 #pragma unroll
@@ -630,16 +669,22 @@ bool make_plan(u32 row_bytes, u32 fixed_bytes, u32 per_item_slot_bytes, StreamPl
 u32 gate_up_x_bytes(const b200moe_gate_up_view& v, u32 rows) { return rows * (v.shape.hidden + v.shape.hidden / 4); }
 
 }  // namespace
-
 bool stream_gate_up_fits(const b200moe_gate_up_view& v, u32 rows) {
     if (!v.x.sums || rows == 0 || rows > 64 || u64(v.shape.experts) * (v.shape.inter / 32) >= (1u << 20)) return false;
     StreamPlan p{};
     return gate_up_x_bytes(v, rows) <= 80u * 1024u && make_plan(v.shape.hidden / 256 * kQ4KBlock, gate_up_x_bytes(v, rows), 2 * rows * 32 * 4, &p);
 }
+namespace {
+// Entries staged per CTA by the down kernel: up to 32, within 48 KB.
+u32 down_stage_entries(const b200moe_down_view& v) { return std::min<u32>(32u, 48u * 1024u / (v.shape.inter + v.shape.inter / 4)); }
+u32 down_fixed_bytes(const b200moe_down_view& v) { return down_stage_entries(v) * (v.shape.inter + v.shape.inter / 4) + 16; }
+
+}  // namespace
+
 bool stream_down_fits(const b200moe_down_view& v, u32 rows) {
     if (!v.act.sums || rows == 0 || rows > 64 || u64(v.shape.experts) * (v.shape.hidden / 64) >= (1u << 20)) return false;
     StreamPlan p{};
-    return make_plan(v.shape.inter / 256 * kQ4KBlock, 0, 0, &p);
+    return make_plan(v.shape.inter / 256 * kQ4KBlock, down_fixed_bytes(v), 0, &p);
 }
 
 int launch_gate_up_q4k_stream(const b200moe_gate_up_view& v, u32 rows, cudaStream_t stream) {
@@ -662,10 +707,11 @@ int launch_down_q4k_stream(const b200moe_down_view& v, u32 rows, cudaStream_t st
     (void)rows;
     if (v.max_union == 0) return B200MOE_OK;
     StreamPlan p{};
-    if (!make_plan(v.shape.inter / 256 * kQ4KBlock, 0, 0, &p)) return fail(B200MOE_ERR_UNSUPPORTED, "down stream form does not fit shared memory");
+    if (!make_plan(v.shape.inter / 256 * kQ4KBlock, down_fixed_bytes(v), 0, &p)) return fail(B200MOE_ERR_UNSUPPORTED, "down stream form does not fit shared memory");
     p.n_chunks = v.shape.hidden / 64;
     p.chunk_magic = static_cast<u32>((u64(1) << 32) / p.n_chunks) + 1;
-    const u32 smem = plan_smem(p, 0, 0);
+    p.stage_entries = down_stage_entries(v);
+    const u32 smem = plan_smem(p, down_fixed_bytes(v), 0);
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(down_q4k_stream_kernel), smem)) return rc;
     down_q4k_stream_kernel<<<sm_count(), (p.warps + kProducers) * 32, smem, stream>>>(v, p);
     return after_launch("down_q4k_stream");
