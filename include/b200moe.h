@@ -272,6 +272,23 @@ int b200moe_combine(const b200moe_combine_view* view, void* stream);
 /* y = (a + b) + c elementwise (enqueue_moe_canonical_sum, include/strix/cuda/ds41_moe.hpp:135-137); c may be NULL. */
 int b200moe_canonical_sum(const float* a, const float* b, const float* c, uint64_t count, float* y, void* stream);
 
+/* ------------------------------------------------------------------------------------------ expert parallelism
+ * What the home rank of a token block does with the pieces its peers return. The reference moves them with
+ * Communicator::exchange (include/strix/dist/communicator.hpp, two ranks); here they arrive by NCCL and these two
+ * calls are the arithmetic either side of it.
+ *
+ * fold_parts: y = (((shared + P_0) + P_1) + ...) + P_{n-1}, one FP32 add per step in rank order; P_r = the partial sum
+ *   of rank r's experts (b200moe_layer with only_part = r: reference_half_sum, src/ds41_moe.cpp:99-115). This is the
+ *   reference's y = (shared + low) + high (include/strix/ds41_moe.hpp:7-11) with n expert ranges instead of two.
+ *   parts: n_parts blocks of `count` floats, `part_stride` floats apart. shared may be NULL (+0). y_bf16 optional.
+ * select_owner_slots: raw[s] = blocks[owner(s)][s] with owner(s) = min(ids[s] / experts_per_block, n_blocks - 1): every
+ *   peer returned a [slots][hidden] block of raw slot vectors of which only its own experts' slots are meaningful
+ *   (include/strix/ds41_moe.hpp:5-8); the result feeds b200moe_combine (the Qwen form's chain cannot be split by rank). */
+int b200moe_fold_parts(const float* parts, uint32_t n_parts, uint64_t part_stride, const float* shared, uint64_t count, float* y,
+                       uint16_t* y_bf16, void* stream);
+int b200moe_select_owner_slots(const float* blocks, uint64_t block_stride, uint32_t n_blocks, uint32_t experts_per_block,
+                               const uint32_t* ids, uint32_t slots, uint32_t hidden, float* raw, void* stream);
+
 /* ------------------------------------------------------------------------------------------------ whole layer
  * Routes from the router's ids, gate/up, down and the combine. Decode GEMVs below grouped_min_rows rows, the grouped
  * tensor-core GEMM from there (0 = never). Replaces enqueue_moe_layer(MoeLayerView)

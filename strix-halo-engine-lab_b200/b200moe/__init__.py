@@ -115,7 +115,7 @@ EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", 
            "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_routes_static_max_words",
            "b200moe_build_routes_static", "b200moe_gate_row_bytes",
            "b200moe_down_row_bytes", "b200moe_expert_bytes", "b200moe_gate_up", "b200moe_down", "b200moe_combine",
-           "b200moe_canonical_sum", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
+           "b200moe_canonical_sum", "b200moe_fold_parts", "b200moe_select_owner_slots", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
            "b200moe_ffn", "b200moe_ffn_host", "b200moe_dense_ffn"]
 
 _lib = None
@@ -149,6 +149,10 @@ def lib():
             getattr(L, n).argtypes = [C.POINTER(t), vp]
         L.b200moe_ffn_host.restype = C.c_int
         L.b200moe_ffn_host.argtypes = [C.POINTER(FfnView), vp, vp, vp]
+        L.b200moe_fold_parts.restype = C.c_int
+        L.b200moe_fold_parts.argtypes = [vp, u32, u64, vp, u64, vp, vp, vp]
+        L.b200moe_select_owner_slots.restype = C.c_int
+        L.b200moe_select_owner_slots.argtypes = [vp, u64, u32, u32, vp, u32, u32, vp, vp]
         L.b200moe_canonical_sum.restype = C.c_int
         L.b200moe_canonical_sum.argtypes = [vp, vp, vp, u64, vp, vp]
         _lib = L

@@ -1,0 +1,57 @@
+"""Tensor parallelism of the dense (shared-expert style) FFN over torch.distributed.
+
+gate / up are split by output (column parallel over `inter`, in whole 256-wide super-blocks so that every share is a
+valid Q4_K row set), SwiGLU and the A8 of h stay local to the share, down is split along K over the same shares and
+yields one [rows][hidden] partial per rank. The partials are summed in RANK ORDER - y = ((+0 + P_0) + P_1) ... - so that
+W GPUs and W virtual ranks on one GPU give the same bits (the reference's rule for its two-rank shared expert:
+include/strix/ds41_shexp_tp.hpp:7-9). That fixed order is why the partials are all-gathered and folded by
+b200moe_fold_parts instead of handed to an all-reduce, whose association order is the library's choice; `allreduce=True`
+takes the all-reduce anyway (one collective less on the wire, sum order not pinned).
+
+x is replicated on every rank. The collectives are torch.distributed's; the arithmetic is the C library's.
+"""
+import torch
+import torch.distributed as dist
+
+from . import check, lib, ptr, stream_ptr
+from . import ops
+
+
+def tp_shares(inter, world):
+    """Whole super-blocks per rank, the larger shares first: 68 blocks over 8 ranks -> 9,9,9,9,8,8,8,8."""
+    blocks = inter // 256
+    base, extra = divmod(blocks, world)
+    sizes = [(base + (1 if r < extra else 0)) * 256 for r in range(world)]
+    starts = [sum(sizes[:r]) for r in range(world)]
+    return list(zip(starts, sizes))
+
+
+class DeviceDenseKernels:
+    """A rank's share of the dense FFN through the C ABI (CUDA only)."""
+
+    def __init__(self, shape_local, gate, up, down):
+        self.shape, self.gate, self.up, self.down = shape_local, gate, up, down
+
+    def partial(self, x):
+        return ops.enqueue_dense_ffn(self.shape, self.gate, self.up, self.down, ops.enqueue_quantize_a8(x))
+
+    def fold(self, parts):
+        world, rows, hidden = parts.shape
+        y = torch.empty((rows, hidden), dtype=torch.float32, device=parts.device)
+        check(lib().b200moe_fold_parts(ptr(parts), world, rows * hidden, None, rows * hidden, ptr(y), None, stream_ptr()))
+        return y
+
+
+class TpDenseFfn:
+    def __init__(self, kernels, group=None, allreduce=False):
+        self.k, self.group, self.allreduce = kernels, group, allreduce
+        self.world = dist.get_world_size(group)
+
+    def __call__(self, x):
+        part = self.k.partial(x)
+        if self.allreduce:
+            dist.all_reduce(part, group=self.group)
+            return part
+        parts = torch.empty((self.world,) + tuple(part.shape), dtype=part.dtype, device=part.device)
+        dist.all_gather(list(parts.unbind(0)), part.contiguous(), group=self.group)
+        return self.k.fold(parts)
