@@ -137,6 +137,97 @@ def reference_arm(args, cfg, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def ep_arm(args, cfg, rank, world, dev):
+    """Expert parallelism: every rank holds experts / world experts of each layer and `batch` local token rows; a step is
+    one EpMoeFfn call (route, all-gather, local experts over the global window, all-to-all, combine). Timed on the device,
+    max over ranks; e2e adds the pinned-host copies of x and y every step."""
+    import torch
+    import torch.distributed as dist
+    import b200moe
+    from b200moe import ep, ops, synth
+
+    K, W, B, L = args.steps, max(args.warmup, 3), args.batch, args.layers
+    H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
+    per = E // world
+    shape = ops.make_shape(H, I, E, TK, cfg["gate_type"], cfg["down_type"])
+    policy = ops.softmax_policy(E, TK)
+    gate_up_bytes, down_bytes = expert_bytes(cfg)
+    layers = []
+    for li in range(L):
+        g, u, d, rw = make_layer(cfg, 1000 + li)          # same seed on every rank: one model, sliced by expert range
+        gb, db = g.size // E, d.size // E
+        sl = lambda t, b: torch.from_numpy(np.ascontiguousarray(t.reshape(-1)[rank * per * b:(rank + 1) * per * b])).to(dev)
+        k = ep.DeviceKernels(shape, policy, torch.from_numpy(rw).to(dev), sl(g, gb), sl(u, gb), sl(d, db), world * B,
+                             b200moe.COMBINE_FMA_SLOTS, world, rank)
+        layers.append(ep.EpMoeFfn(k, B, TK, H, b200moe.COMBINE_FMA_SLOTS))
+    rng = np.random.default_rng(7 + rank)
+    NX = 16
+    xs_host = [torch.from_numpy(synth.activations(rng, B, H)).pin_memory() for _ in range(NX)]
+    xs = [x.to(dev) for x in xs_host]
+    ys_host = torch.empty((B, H), dtype=torch.float32).pin_memory()
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(n):
+        for s in range(n):
+            layers[s % L](xs[s % NX])
+
+    def run_host(n):
+        for s in range(n):
+            ys_host.copy_(layers[s % L](xs_host[s % NX].to(dev, non_blocking=True)), non_blocking=True)
+        torch.cuda.synchronize()
+
+    run(W)
+    barrier()
+    launches0 = b200moe.launch_count()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    run(K)
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    launches = b200moe.launch_count() - launches0
+    run_host(min(W, 50))
+    barrier()
+    h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    h0.record()
+    run_host(K)
+    h1.record()
+    barrier()
+    host_ms = max(h0.elapsed_time(h1), 1000.0 * (time.perf_counter() - t0))
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    t = torch.tensor([dev_ms, host_ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, host_ms = (float(v) for v in t.cpu())
+    tokens = B * K * world
+    peak, peak_kind = peaks()
+    rank_bytes = per * (gate_up_bytes + down_bytes)       # at most: every local expert hit once per step
+    achieved = rank_bytes / (dev_ms / K * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": tokens / (dev_ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {B} per rank", "parallelism": f"ep x{world} ({per} experts per rank)",
+                   "l2": f"rotating {L} layers of distinct expert weights", "launch": "per-step launches + NCCL (no graph)"},
+        "clocks": sampler.summary(),
+        "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
+                "ms_per_step": host_ms / K},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "whole EP step (local expert weights / step time)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy", "traffic": None},
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -147,6 +238,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=4, help="distinct layers of weights rotated between steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
+                    help="N > 1: independent replicas (rows sharded, weights replicated, no collective) or expert parallelism "
+                         "(experts / N per rank, all-gather dispatch + all-to-all return over NCCL)")
     args = ap.parse_args()
     cfg = CONFIGS[args.workload]
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -163,6 +257,8 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if world > 1 and args.parallelism == "ep":
+        return ep_arm(args, cfg, rank, world, dev)
     K, W, B, L = args.steps, max(args.warmup, 3), args.batch, args.layers
     H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
     shape = ops.make_shape(H, I, E, TK, cfg["gate_type"], cfg["down_type"])
@@ -305,7 +401,7 @@ def main():
         "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
                 "ms_per_step": host_ms / K},
         "gpu_launches": int(round(launches_per_step * K)),
-        "roofline": {"kernel": "gate_up_q4k_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "roofline": {"kernel": "gate_up_q4k_stream_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy", "traffic": None,
                      "algorithmic_bytes_per_launch": algo_bytes, "avg_launch_us": float(np.mean(kern_ms)) * 1000.0,
                      "distinct_experts_per_step": float(np.mean(steps_uniq))},

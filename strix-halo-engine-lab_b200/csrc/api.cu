@@ -182,11 +182,19 @@ FfnScratch carve_ffn(void* ws, const b200moe_shape& s, u32 capacity) {
 
 // Plan by window size, chosen on the host from the row count (no environment reads inside numerical code): decode
 // windows of Q4_K experts take the persistent bulk-copy form, everything else the plain per-block form.
-int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st) {
+// grouped_min_rows: 0 = the default threshold; windows of at least that many rows take the tensor-core form.
+constexpr u32 kGroupedDefaultRows = 128;
+bool use_grouped(const b200moe_shape& s, u32 rows, u32 grouped_min_rows, bool have_sums) {
+    const u32 least = grouped_min_rows ? grouped_min_rows : kGroupedDefaultRows;
+    return rows >= least && grouped_fits(s, have_sums);
+}
+int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
     if (v.shape.gate_type != B200MOE_TYPE_Q4_K) return launch_gate_up_q8(v, st);
+    if (use_grouped(v.shape, rows, grouped_min_rows, v.x.sums != nullptr)) return launch_gate_up_q4k_grouped(v, st);
     return stream_gate_up_fits(v, rows) ? launch_gate_up_q4k_stream(v, rows, st) : launch_gate_up_q4k(v, st);
 }
-int enqueue_down(const b200moe_down_view& v, u32 rows, cudaStream_t st) {
+int enqueue_down(const b200moe_down_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
+    if (v.shape.down_type == B200MOE_TYPE_Q4_K && use_grouped(v.shape, rows, grouped_min_rows, v.act.sums != nullptr)) return launch_down_q4k_grouped(v, st);
     if (v.shape.down_type == B200MOE_TYPE_Q4_K) return stream_down_fits(v, rows) ? launch_down_q4k_stream(v, rows, st) : launch_down_q4k(v, st);
     return v.shape.gate_type == B200MOE_TYPE_Q4_K ? launch_down_q8_chain4(v, st) : launch_down_q8(v, st);
 }
@@ -366,14 +374,14 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
     gu.shape = s; gu.weights = v->weights; gu.routes = L.routes; gu.max_union = max_union;
     gu.x = v->x; gu.act = L.act; gu.row_status = row_status; gu.summary = L.summary;
     tap(2);
-    if (int rc = enqueue_gate_up(gu, v->rows, st)) return rc;
+    if (int rc = enqueue_gate_up(gu, v->rows, st, v->grouped_min_rows)) return rc;
     tap(3);
 
     b200moe_down_view dn{};
     dn.shape = s; dn.weights = v->weights; dn.routes = L.routes; dn.max_union = max_union;
     dn.act = L.act; dn.raw = raw; dn.summary = L.summary;
     tap(4);
-    if (int rc = enqueue_down(dn, v->rows, st)) return rc;
+    if (int rc = enqueue_down(dn, v->rows, st, v->grouped_min_rows)) return rc;
     tap(5);
 
     if (!v->y) return B200MOE_OK;

@@ -16,6 +16,10 @@ int launch_router_select(const b200moe_router_view& v, cudaStream_t stream);
 // routes.cu
 u64 routes_scratch_words(u32 rows, u32 top_k, u32 experts);
 int launch_routes(const b200moe_routes_view& v, cudaStream_t stream);
+// grouped (token-block) form of the Q4_K experts on the tensor cores (grouped_q4k.cu)
+bool grouped_fits(const b200moe_shape& s, bool have_sums);
+int launch_gate_up_q4k_grouped(const b200moe_gate_up_view& v, cudaStream_t stream);
+int launch_down_q4k_grouped(const b200moe_down_view& v, cudaStream_t stream);
 // decode windows: selection of r (logits already present) and the routes of the selected ids in one launch
 bool select_routes_fusable(const b200moe_router_view& r, u32 top_k);
 int launch_select_routes(const b200moe_router_view& r, const b200moe_routes_view& v, cudaStream_t stream);

@@ -404,6 +404,26 @@ def test_experts_q4k_qwen_family(gpu, oracle):
     print("qwen family bit-exact on every case:", exact_all)
 
 
+def test_experts_q4k_grouped_tensor_core_form(gpu, oracle):
+    """Windows of 128 rows and more take the grouped form (tcgen05 integer MMAs + the same FP32 chains): stage by stage
+    against the oracle like the decode forms. Cases: several token tiles per expert with a ragged last one, experts with
+    few tokens, an expert range (first / end), K = 256 (two stages per tile) and a wide K."""
+    import b200moe
+    from b200moe import synth
+    rng = np.random.default_rng(31)
+    exact_all = True
+    for E, H, I, K, rows in ((4, 512, 256, 2, 300), (8, 256, 256, 3, 130), (16, 1024, 512, 4, 128), (3, 2048, 768, 2, 200)):
+        gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
+        x = rng.standard_normal((rows, H), dtype=np.float32)
+        ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+        wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
+        sh, osh = shape_pair(H, I, E, K, 12, 12)
+        raw, want = run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, exact=False)
+        exact_all &= qwen_exact(raw, want)
+        run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, first=1, end=E - 1, exact=False)
+    print("grouped form bit-exact on every case:", exact_all)
+
+
 def test_experts_fail_closed(gpu, oracle):
     """A non-finite projection sets status bit 8 on its row, the summary word, and the down stage writes nothing
     (src/cpu/core/routed_expert.hpp:17-19; host-side injection as tests/cpu/routed_expert_host_tests.cpp:393-399)."""
