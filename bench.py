@@ -37,6 +37,8 @@ CONFIGS = {
     "c2": dict(hidden=2048, experts=128, top_k=8, inter=768, gate_type=12, down_type=12,
                desc="MoE decode layer, Q4_K experts: hidden 2048, 128 experts, top-8, inter 768"),
 }
+CONFIGS["c3"] = dict(CONFIGS["c2"], desc="MoE prefill layer, Q4_K experts: hidden 2048, 128 experts, top-8, inter 768, "
+                                           "bf16-rounded activations, Zipf(1.1) expert load", prefill=True)
 METRIC = "MoE-layer tokens/s (Q4_K decode)"
 UNIT = "tokens/s"
 L2_BYTES = 126 * 2 ** 20
@@ -135,6 +137,125 @@ def reference_arm(args, cfg, rank, world):
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def prefill_arm(args, cfg, rank, world, dev):
+    """Token-block (prefill) form: a step is one b200moe_ffn call over `--batch` tokens (default 4096) through the
+    grouped tensor-core kernels. Each rank is a replica with its own tokens. The roofline is the one the path is quoted
+    on - useful FLOP (2 x assignments x 3 x hidden x inter) against the measured dense bf16 rate - although the kernel
+    itself is bound by the FP32 work after the integer MMAs; the gate/up kernel is timed with CUDA events."""
+    import torch
+    import torch.distributed as dist
+    import b200moe
+    from b200moe import ops, synth
+
+    K, W, L = args.steps, max(args.warmup, 3), min(args.layers, 2)
+    B = args.batch if args.batch != 8 else 4096
+    H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
+    shape = ops.make_shape(H, I, E, TK, cfg["gate_type"], cfg["down_type"])
+    policy = ops.softmax_policy(E, TK)
+    layers = []
+    for li in range(L):
+        g, u, d, rw = make_layer(cfg, 1000 + li + 100 * rank)
+        bias = synth.zipf_logit_bias(np.random.default_rng(50 + li), E)
+        layers.append(ops.MoeFfn(shape, policy, *(torch.from_numpy(a).to(dev) for a in (g, u, d, rw)), capacity=B,
+                                 combine_form=b200moe.COMBINE_FMA_SLOTS, logit_bias=torch.from_numpy(bias).to(dev)))
+    rng = np.random.default_rng(7 + rank)
+    NX = 2
+    xs_host = [torch.from_numpy(synth.bf16_round(synth.activations(rng, B, H))).pin_memory() for _ in range(NX)]
+    xs = [x.to(dev) for x in xs_host]
+    y = torch.empty((B, H), dtype=torch.float32, device=dev)
+    ys_host = torch.empty((B, H), dtype=torch.float32).pin_memory()
+    ids = torch.empty((B, TK), dtype=torch.int32, device=dev)
+    wts = torch.empty((B, TK), dtype=torch.float32, device=dev)
+    lib = b200moe.lib()
+    stream = torch.cuda.current_stream()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True),
+            torch.cuda.Event(enable_timing=True)) for _ in range(L * NX)]
+    for e4 in evs:
+        for e in e4:
+            e.record()
+    torch.cuda.synchronize()
+    taps = [ops.MoeFfn.stage_events([None, None, a.cuda_event, b.cuda_event, c.cuda_event, d.cuda_event, None, None]) for a, b, c, d in evs]
+    views = [layers[s % L]._view(B, xs[s % NX], y, ids, wts, events=taps[s]) for s in range(L * NX)]
+    host_views = [layers[s % L]._view(B, None, None) for s in range(L * NX)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(n):
+        for s in range(n):
+            b200moe.check(lib.b200moe_ffn(C.byref(views[s % len(views)]), stream.cuda_stream))
+
+    def run_host(n):
+        for s in range(n):
+            b200moe.check(lib.b200moe_ffn_host(C.byref(host_views[s % len(host_views)]), xs_host[s % NX].data_ptr(), ys_host.data_ptr(),
+                                               stream.cuda_stream))
+
+    run(W)
+    barrier()
+    counts = np.bincount(ids.cpu().numpy().reshape(-1), minlength=E)
+    launches0 = b200moe.launch_count()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gu_ms, dn_ms, done = [], [], 0
+    barrier()
+    e0.record()
+    while done < K:
+        n = min(K - done, len(views))
+        run(n)
+        torch.cuda.synchronize()
+        gu_ms += [evs[s][0].elapsed_time(evs[s][1]) for s in range(n)]
+        dn_ms += [evs[s][2].elapsed_time(evs[s][3]) for s in range(n)]
+        done += n
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    launches = b200moe.launch_count() - launches0
+    run_host(min(W, 3))
+    barrier()
+    t0 = time.perf_counter()
+    run_host(K)
+    barrier()
+    host_ms = 1000.0 * (time.perf_counter() - t0)
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    t = torch.tensor([dev_ms, host_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, host_ms = (float(v) for v in t.cpu())
+    tokens = B * K * world
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak_tf, kind = (float(json.load(open(path))["bf16_tflops_sustained"]), "measured sustained") if os.path.exists(path) else (1400.0, "fallback")
+    gu_flop = 2.0 * B * TK * 2 * I * H          # gate + up
+    achieved = gu_flop / (float(np.mean(gu_ms)) * 1e-3) / 1e12
+    line = {
+        "metric": "MoE-layer tokens/s (Q4_K prefill)", "value": tokens / (dev_ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8xint4->int32 (tcgen05 kind::i8), fp32 chains", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}, {B} tokens per step", "parallelism": f"replicas x{world}" if world > 1 else "1 gpu",
+                   "l2": f"{L} layers of distinct expert weights rotated ({L * 340} MB > 2 x 126 MiB L2)", "launch": "per-step launches",
+                   "expert_load": {"max_rows": int(counts.max()), "mean_rows": float(counts.mean()), "empty_experts": int((counts == 0).sum())}},
+        "clocks": sampler.summary(),
+        "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
+                "ms_per_step": host_ms / K},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "grouped_q4k_kernel<gate/up>", "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+                     "frac": achieved / peak_tf, "peak_kind": f"{kind} dense bf16", "traffic": None,
+                     "algorithmic_flop_per_launch": gu_flop, "avg_launch_us": float(np.mean(gu_ms)) * 1000.0,
+                     "down_avg_launch_us": float(np.mean(dn_ms)) * 1000.0},
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            _, base = cpu_arm(cfg, 256, target_s=12.0)
+            base["sample"] = "256 of the step's tokens: " + base["sample"]
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def ep_arm(args, cfg, rank, world, dev):
@@ -257,6 +378,8 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if cfg.get("prefill"):
+        return prefill_arm(args, cfg, rank, world, dev)
     if world > 1 and args.parallelism == "ep":
         return ep_arm(args, cfg, rank, world, dev)
     K, W, B, L = args.steps, max(args.warmup, 3), args.batch, args.layers

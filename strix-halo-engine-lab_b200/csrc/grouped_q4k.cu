@@ -15,7 +15,7 @@
 //     canonical K-major layout (8-row x 16-byte core matrices), gather the tokens' A8 codes into the same layout, and
 //     stage the tokens' {E_g, S_g} and the rows' 16-byte block headers. Its first thread then issues the 4 MMAs
 //     (M 128, N 64, K 32, s8 x s8 -> s32) into one half of tensor memory and commits them to an mbarrier.
-//   * drain warps (8): thread = (weight row = TMEM lane, 32 of the 64 tokens). tcgen05.ld brings 16 dots at a time;
+//   * drain warps (8): thread = (weight row = TMEM lane, 32 of the 64 tokens). tcgen05.ld brings 8 dots at a time;
 //     x_g = E_g * ((d * sc_g) * float(dot_g) - (dmin * m_g) * float(S_g)), pair sums, the four chains acc_p over
 //     ascending super-blocks, (a0 + a1) + (a2 + a3) at the end - exactly the decode kernels' order.
 //   * tensor memory: 512 columns = 2 buffers x 4 groups x 64 tokens; smem stages follow the same two buffers.
@@ -33,6 +33,7 @@ namespace {
 constexpr u32 kGM = 128, kGN = 64;           // tile: weight rows x tokens
 constexpr u32 kDrainWarps = 8, kLoadWarps = 4, kGThreads = (kDrainWarps + kLoadWarps) * 32;
 constexpr u32 kStageGroups = 4;              // half a super-block per stage
+constexpr u32 kTPT = kGN / (kDrainWarps / 4);   // tokens per drain thread (16)
 constexpr u32 kTmemCols = 512;
 constexpr u32 kABytes = kStageGroups * kGM * 32, kBBytes = kStageGroups * kGN * 32, kEsBytes = kStageGroups * kGN * 8, kHdrBytes = kGM * 16;
 constexpr u32 kStageBytes = kABytes + kBBytes + kEsBytes + kHdrBytes;  // 28672
@@ -94,10 +95,32 @@ __device__ __forceinline__ void tmem_ld16(u32 taddr, u32* v) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(u32 taddr, u32* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tie8(u32* v) {
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]));
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ float small_int_to_float(int v) { return __fsub_rn(__int_as_float(0x4b400000 + v), 12582912.0f); }
+// Tie registers to the point after tcgen05.wait::ld, so that no use of a loaded value is scheduled before the wait.
+__device__ __forceinline__ void tie16(u32* v) {
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]));
+    asm volatile("" : "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]));
+}
+// Two FP32 lanes per instruction (Blackwell packed FP32): each lane is one IEEE round-to-nearest multiplication, the
+// same result as two scalar instructions at half the issue slots. Only the multiplications are packed: a packed add
+// fed by a packed multiply did not reproduce the scalar bits on B200 (it behaves as contracted), so the adds stay scalar.
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 c;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<u64&>(c)) : "l"(reinterpret_cast<const u64&>(a)), "l"(reinterpret_cast<const u64&>(b)));
+    return c;
+}
 
 struct Factors { float Dl, DMl, Dh, DMh; };
 __device__ __forceinline__ Factors q4k_factors(const uint4& hdr, u32 p) {  // routed_expert.cpp:65-71, as in gemv_q4k_stream.cu
@@ -201,7 +224,10 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
 
     if (warp >= kDrainWarps) {
         // ===================================================================================== loader + MMA issue
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");   // the drain threads hold 128 accumulators each
+        // Register split (the CTA holds 384 x 168): the loaders give registers up, the drain threads - 128 accumulators
+        // each - take them: 128 x 72 + 256 x 216 = 384 x 168.
+        static_assert(kLoadWarps * 32 * 72 + kDrainWarps * 32 * 216 <= kGThreads * 168, "setmaxnreg split exceeds the register file share");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         const u32 lt = tid - kDrainWarps * 32;            // 0..127 = weight row of the tile
         for (u32 id = blockIdx.x; id < n_tiles; id += gridDim.x) {
             const Tile t = find_tile(a, cum, n_union, id);
@@ -228,9 +254,9 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
                 uint4 cc[4];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) cc[c] = __ldg(cq + c);
-                const u32 g0 = 8u * b + 4u * hf + ge;
-                const float e0 = __ldg(deltas + g0), e1 = __ldg(deltas + g0 + 2);
-                const i32 s0 = __ldg(sums + g0), s1 = __ldg(sums + g0 + 2);
+                const u32 g0 = 8u * b + 4u * hf + 2u * ge;   // this thread stages pair ge of the stage for token tok_e
+                const float e0 = __ldg(deltas + g0), e1 = __ldg(deltas + g0 + 1);
+                const i32 s0 = __ldg(sums + g0), s1 = __ldg(sums + g0 + 1);
                 if (ok) ok = mbar_wait(&empty[buf], (use & 1u) ^ 1u, s_abort);  // the drain is done with this buffer
                 unsigned char* st = stage0 + buf * kStageBytes;
                 if (ok) {
@@ -252,9 +278,8 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
                         const u32 ch = 4 * half + c, gi = ch >> 1, kc = ch & 1u;
                         *reinterpret_cast<uint4*>(sb + gi * (kGN * 32) + kc * 128u) = cc[c];
                     }
-                    float2* es = reinterpret_cast<float2*>(st + kABytes + kBBytes);
-                    es[ge * kGN + tok_e] = make_float2(e0, static_cast<float>(s0));
-                    es[(ge + 2) * kGN + tok_e] = make_float2(e1, static_cast<float>(s1));
+                    reinterpret_cast<float4*>(st + kABytes + kBBytes)[ge * kGN + tok_e] =
+                        make_float4(e0, e1, static_cast<float>(s0), static_cast<float>(s1));
                     reinterpret_cast<uint4*>(st + kABytes + kBBytes + kEsBytes)[lt] = hdr;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> the tensor core's reads
@@ -279,9 +304,9 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
         const u32 act_stride = a.act.stride ? a.act.stride : a.act.width;
         for (u32 id = blockIdx.x; id < n_tiles; id += gridDim.x) {
             const Tile t = find_tile(a, cum, n_union, id);
-            float acc[32][4];
+            float acc[kTPT][4];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
+            for (int i = 0; i < (int)kTPT; ++i) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
             for (u32 b = 0; b < nblocks; ++b) {
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf, ++n) {
@@ -291,27 +316,30 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
                     if (!ok) continue;
                     tc_fence_after();
                     const unsigned char* st = stage0 + buf * kStageBytes;
-                    const float2* es = reinterpret_cast<const float2*>(st + kABytes + kBBytes);
+                    const float4* es = reinterpret_cast<const float4*>(st + kABytes + kBBytes);  // [pair][token] {E_l, E_h, S_l, S_h}
                     const uint4 hdr = reinterpret_cast<const uint4*>(st + kABytes + kBBytes + kEsBytes)[o];
-                    const u32 tbase = tmem + lane_addr + buf * (kStageGroups * kGN) + 32u * w;
+                    const u32 tbase = tmem + lane_addr + buf * (kStageGroups * kGN) + kTPT * w;
 #pragma unroll
                     for (int pp = 0; pp < 2; ++pp) {
                         const Factors f = q4k_factors(hdr, 2 * hf + pp);
+                        const float2 D = make_float2(f.Dl, f.Dh), DMn = make_float2(-f.DMl, -f.DMh);
 #pragma unroll
-                        for (int tq = 0; tq < 2; ++tq) {
-                            if (32u * w + 16u * tq >= t.nt) continue;  // no valid token in these 16 columns (warp-uniform)
-                            u32 dl[16], dh[16];
-                            tmem_ld16(tbase + (2 * pp) * kGN + 16 * tq, dl);
-                            tmem_ld16(tbase + (2 * pp + 1) * kGN + 16 * tq, dh);
+                        for (int tq = 0; tq < (int)kTPT / 8; ++tq) {
+                            if (kTPT * w + 8u * tq >= t.nt) continue;  // no valid token in these 8 columns (warp-uniform)
+                            u32 dl[8], dh[8];
+                            tmem_ld8(tbase + (2 * pp) * kGN + 8 * tq, dl);
+                            tmem_ld8(tbase + (2 * pp + 1) * kGN + 8 * tq, dh);
                             tmem_wait_ld();
-                            const float2* el = es + (2 * pp) * kGN + 32u * w + 16 * tq;
-                            const float2* eh = el + kGN;
+                            tie8(dl); tie8(dh);
+                            const float4* e4 = es + pp * kGN + kTPT * w + 8 * tq;
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                const float2 l = el[i], h = eh[i];
-                                const float xl = __fmul_rn(l.x, __fsub_rn(__fmul_rn(f.Dl, small_int_to_float(static_cast<int>(dl[i]))), __fmul_rn(f.DMl, l.y)));
-                                const float xh = __fmul_rn(h.x, __fsub_rn(__fmul_rn(f.Dh, small_int_to_float(static_cast<int>(dh[i]))), __fmul_rn(f.DMh, h.y)));
-                                acc[16 * tq + i][2 * hf + pp] = __fadd_rn(acc[16 * tq + i][2 * hf + pp], __fadd_rn(xl, xh));
+                            for (int i = 0; i < 8; ++i) {
+                                const float4 e = e4[i];
+                                const float2 fd = make_float2(__int2float_rn(static_cast<int>(dl[i])), __int2float_rn(static_cast<int>(dh[i])));
+                                // x = E * ((D * float(dot)) - (DM * S)) for the pair's two groups; (-DM) * S = -(DM * S) exactly
+                                const float2 pa = mul2(D, fd), pb = mul2(DMn, make_float2(e.z, e.w));
+                                const float2 x = mul2(make_float2(e.x, e.y), make_float2(__fadd_rn(pa.x, pb.x), __fadd_rn(pa.y, pb.y)));
+                                acc[8 * tq + i][2 * hf + pp] = __fadd_rn(acc[8 * tq + i][2 * hf + pp], __fadd_rn(x.x, x.y));
                             }
                         }
                     }
@@ -323,8 +351,8 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
             if (kDown) {
                 if (ok) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const u32 tok = 32u * w + i;
+                    for (int i = 0; i < (int)kTPT; ++i) {
+                        const u32 tok = kTPT * w + i;
                         if (tok < t.nt) {
                             const u32 slot = a.routes.slots[t.eb + tok];
                             a.raw[u64(slot) * H + kGM * t.c + o] = __fadd_rn(__fadd_rn(acc[i][0], acc[i][1]), __fadd_rn(acc[i][2], acc[i][3]));
@@ -334,8 +362,8 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
             } else {
                 asm volatile("bar.sync 3, %0;" ::"r"(kDrainWarps * 32) : "memory");  // the previous tile's epilogue has read s_out
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    s_out[(32u * w + i) * kGM + o] = __fadd_rn(__fadd_rn(acc[i][0], acc[i][1]), __fadd_rn(acc[i][2], acc[i][3]));
+                for (int i = 0; i < (int)kTPT; ++i)
+                    s_out[(kTPT * w + i) * kGM + o] = __fadd_rn(__fadd_rn(acc[i][0], acc[i][1]), __fadd_rn(acc[i][2], acc[i][3]));
                 asm volatile("bar.sync 3, %0;" ::"r"(kDrainWarps * 32) : "memory");
                 // SwiGLU + the A8 rule: one warp per (token, 32 outputs); the tile holds 2 groups of 32 per token
                 for (u32 task = warp; ok && task < 2 * t.nt; task += kDrainWarps) {
