@@ -42,6 +42,7 @@ CONFIGS["c3"] = dict(CONFIGS["c2"], desc="MoE prefill layer, Q4_K experts: hidde
 METRIC = "MoE-layer tokens/s (Q4_K decode)"
 UNIT = "tokens/s"
 L2_BYTES = 126 * 2 ** 20
+NCU_TRAFFIC_RATIO = 1.00  # measured dram bytes / algorithmic bytes of the gate/up kernel (ncu, three launches: 0.999 - 1.002)
 
 
 def peaks():
@@ -525,7 +526,9 @@ def main():
                 "ms_per_step": host_ms / K},
         "gpu_launches": int(round(launches_per_step * K)),
         "roofline": {"kernel": "gate_up_q4k_stream_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy", "traffic": None,
+                     "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy",
+                     # dram read + write per launch from an ncu capture of this kernel on this workload: 1.00 of the algorithmic bytes
+                     "traffic": algo_bytes * NCU_TRAFFIC_RATIO, "traffic_source": "profiles/stream_kernels_c2_decode_b8_dram.md",
                      "algorithmic_bytes_per_launch": algo_bytes, "avg_launch_us": float(np.mean(kern_ms)) * 1000.0,
                      "distinct_experts_per_step": float(np.mean(steps_uniq))},
         "extra": {"step_hbm_gbs_graph": step_bytes / (dev_ms / K * 1e-3) / 1e9, "ms_per_step_no_graph": plain_ms_total / K,
