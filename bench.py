@@ -39,6 +39,9 @@ CONFIGS = {
 }
 CONFIGS["c3"] = dict(CONFIGS["c2"], desc="MoE prefill layer, Q4_K experts: hidden 2048, 128 experts, top-8, inter 768, "
                                            "bf16-rounded activations, Zipf(1.1) expert load", prefill=True)
+CONFIGS["c4"] = dict(hidden=7168, experts=256, top_k=8, inter=2048, gate_type=12, down_type=12, large=True,
+                     desc="large routed MoE decode layer: hidden 7168, 256 Q4_K experts + 1 Q8_0 shared expert, inter 2048, "
+                          "sigmoid + bias router, 8 groups / best 4 / top-8, bf16-rounded activations")
 METRIC = "MoE-layer tokens/s (Q4_K decode)"
 UNIT = "tokens/s"
 L2_BYTES = 126 * 2 ** 20
@@ -259,6 +262,110 @@ def prefill_arm(args, cfg, rank, world, dev):
         dist.destroy_process_group()
 
 
+def large_arm(args, cfg, rank, world, dev):
+    """Config 4: 256 routed Q4_K experts (group-limited sigmoid router) + a replicated Q8_0 shared expert, `--batch` tokens
+    per rank (default 64). One GPU holds every expert; N GPUs run expert parallelism with experts / N per rank
+    (b200moe.ep). A step = shared expert + routed experts + the rank-ordered fold y = ((shared + S_0) + S_1) ...;
+    one set of weights (6.3 GB of routed experts: far beyond L2)."""
+    import torch
+    import torch.distributed as dist
+    import b200moe
+    from b200moe import ep, ops, synth
+
+    K, W = args.steps if args.steps != 2000 else 100, max(min(args.warmup, 20), 3)
+    B = args.batch if args.batch != 8 else 64
+    H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
+    PARTS = 8                                                # the fold always has 8 expert ranges: 1 and 8 GPUs give the same bits
+    per = E // world
+    shape = ops.make_shape(H, I, E, TK, 12, 12)
+    sh_shape = ops.make_shape(H, I, 1, 1, 8, 8)
+    policy = ops.sigmoid_group_policy(E, TK, 8, 4)
+    rng0 = np.random.default_rng(400)
+    rw = torch.from_numpy(synth.router_weight(rng0, E, H)).to(dev)
+    bias = torch.from_numpy((rng0.standard_normal(E) * 0.1).astype(np.float32)).to(dev)
+    sg, su, sd = (torch.from_numpy(a).to(dev) for a in synth.expert_tensors(rng0, 1, H, I, 8, 8))
+    parts = []
+    for r in range(world if world > 1 else PARTS):           # experts are generated in 8 (or world) seeded slices
+        if world > 1 and r != rank:
+            continue
+        n_e = per if world > 1 else E // PARTS
+        parts.append(synth.expert_tensors(np.random.default_rng(500 + r), n_e, H, I, 12, 12))
+    gate, up, down = (torch.from_numpy(np.concatenate([p[i] for p in parts])).to(dev) for i in range(3))
+    del parts
+    rng = np.random.default_rng(7 + rank)
+    NX = 4
+    xs_host = [torch.from_numpy(synth.bf16_round(synth.activations(rng, B, H))).pin_memory() for _ in range(NX)]
+    xs = [x.to(dev) for x in xs_host]
+    ys_host = torch.empty((B, H), dtype=torch.float32).pin_memory()
+    if world > 1:
+        kern = ep.DeviceKernels(shape, policy, rw, gate, up, down, world * B, b200moe.COMBINE_PARTS, world, rank, select_bias=bias)
+        routed = ep.EpMoeFfn(kern, B, TK, H, b200moe.COMBINE_PARTS)
+        fn = lambda x, shared: routed(x, shared)
+    else:
+        ffn = ops.MoeFfn(shape, policy, gate, up, down, rw, capacity=B, combine_form=b200moe.COMBINE_PARTS, parts=PARTS, select_bias=bias)
+        fn = lambda x, shared: ffn(x, shared=shared)
+
+    def step(x):
+        shared = ops.enqueue_dense_ffn(sh_shape, sg, su, sd, ops.enqueue_quantize_a8(x))
+        return fn(x, shared)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for s in range(W):
+        step(xs[s % NX])
+    barrier()
+    launches0 = b200moe.launch_count()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for s in range(K):
+        step(xs[s % NX])
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    launches = b200moe.launch_count() - launches0
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(K):
+        ys_host.copy_(step(xs_host[s % NX].to(dev, non_blocking=True)), non_blocking=True)
+    barrier()
+    host_ms = 1000.0 * (time.perf_counter() - t0)
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    t = torch.tensor([dev_ms, host_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, host_ms = (float(v) for v in t.cpu())
+    tokens = B * K * world
+    peak, peak_kind = peaks()
+    gate_up_bytes, down_bytes = expert_bytes(cfg)
+    rank_bytes = (E // world) * (gate_up_bytes + down_bytes)   # upper bound: every local expert hit in the step
+    achieved = rank_bytes / (dev_ms / K * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": tokens / (dev_ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {B} per rank",
+                   "parallelism": f"ep x{world} ({per} experts per rank)" if world > 1 else "1 gpu (all 256 experts)",
+                   "l2": "6.3 GB of routed expert weights per layer (far beyond L2)", "launch": "per-step launches" + (" + NCCL" if world > 1 else "")},
+        "clocks": sampler.summary(),
+        "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
+                "ms_per_step": host_ms / K},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "whole step (upper bound: all local routed expert bytes / step time)", "bound": "hbm", "achieved": achieved,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy", "traffic": None},
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def ep_arm(args, cfg, rank, world, dev):
     """Expert parallelism: every rank holds experts / world experts of each layer and `batch` local token rows; a step is
     one EpMoeFfn call (route, all-gather, local experts over the global window, all-to-all, combine). Timed on the device,
@@ -381,6 +488,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     if cfg.get("prefill"):
         return prefill_arm(args, cfg, rank, world, dev)
+    if cfg.get("large"):
+        return large_arm(args, cfg, rank, world, dev)
     if world > 1 and args.parallelism == "ep":
         return ep_arm(args, cfg, rank, world, dev)
     K, W, B, L = args.steps, max(args.warmup, 3), args.batch, args.layers

@@ -87,20 +87,13 @@ __device__ __forceinline__ void mma_i8(u32 d_tmem, u64 a_desc, u64 b_desc) {
 __device__ __forceinline__ void mma_commit(u64* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(u32 taddr, u32* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
-}
 __device__ __forceinline__ void tmem_ld8(u32 taddr, u32* v) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                  : "r"(taddr)
                  : "memory");
 }
+// Ties registers to the point after tcgen05.wait::ld, so that no use of a loaded value is scheduled before the wait.
 __device__ __forceinline__ void tie8(u32* v) {
     asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]));
 }
@@ -108,11 +101,6 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ float small_int_to_float(int v) { return __fsub_rn(__int_as_float(0x4b400000 + v), 12582912.0f); }
-// Tie registers to the point after tcgen05.wait::ld, so that no use of a loaded value is scheduled before the wait.
-__device__ __forceinline__ void tie16(u32* v) {
-    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]));
-    asm volatile("" : "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]));
-}
 // Two FP32 lanes per instruction (Blackwell packed FP32): each lane is one IEEE round-to-nearest multiplication, the
 // same result as two scalar instructions at half the issue slots. Only the multiplications are packed: a packed add
 // fed by a packed multiply did not reproduce the scalar bits on B200 (it behaves as contracted), so the adds stay scalar.
