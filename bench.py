@@ -37,6 +37,8 @@ CONFIGS = {
     "c2": dict(hidden=2048, experts=128, top_k=8, inter=768, gate_type=12, down_type=12,
                desc="MoE decode layer, Q4_K experts: hidden 2048, 128 experts, top-8, inter 768"),
 }
+CONFIGS["c1"] = dict(hidden=2048, experts=64, top_k=4, inter=1024, gate_type=8, down_type=8, batch=1, parts_form=True,
+                     desc="MoE decode layer, Q8_0 experts (the reference's CPU-backend case): hidden 2048, 64 experts, top-4, inter 1024")
 CONFIGS["c3"] = dict(CONFIGS["c2"], desc="MoE prefill layer, Q4_K experts: hidden 2048, 128 experts, top-8, inter 768, "
                                            "bf16-rounded activations, Zipf(1.1) expert load", prefill=True)
 CONFIGS["c4"] = dict(hidden=7168, experts=256, top_k=8, inter=2048, gate_type=12, down_type=12, large=True,
@@ -90,6 +92,8 @@ def make_layer(cfg, seed):
 
 
 def expert_bytes(cfg):
+    if cfg["gate_type"] == 8:
+        return 2 * cfg["inter"] * (cfg["hidden"] // 32 * 34), cfg["hidden"] * (cfg["inter"] // 32 * 34)
     gate_row = cfg["hidden"] // 256 * 144
     down_row = cfg["inter"] // 256 * 144
     return 2 * cfg["inter"] * gate_row, cfg["hidden"] * down_row
@@ -103,6 +107,30 @@ def cpu_arm(cfg, batch, target_s, threads=None):
     g, u, d, rw = make_layer(cfg, 1000)
     x = synth.activations(np.random.default_rng(7), batch, cfg["hidden"])
     threads = threads or os.cpu_count() or 1
+    if cfg["gate_type"] == 8:  # the reference's Q8_0 path is scalar and single-threaded (reference_window; no SIMD / threaded table)
+        pol = O.softmax_policy(cfg["experts"], cfg["top_k"])
+        orc = O.Oracle()
+        _, _, ids, wts = orc.router(pol, x=x, w=rw)
+        if O.Ref.available():
+            ref = O.Ref()
+            call = lambda: ref.window_q8_0(g, u, d, cfg["experts"], cfg["hidden"], cfg["inter"], float("inf"), x, ids, wts, None, cfg["experts"] // 2)
+            kind = "reference"
+        else:
+            sh = O.Shape(cfg["hidden"], cfg["inter"], cfg["experts"], cfg["top_k"], 8, 8, float("inf"))
+            call = lambda: orc.ffn(sh, pol, g, u, d, rw, x, O.COMBINE_PARTS)
+            kind = "port"
+        t0 = time.perf_counter()
+        call()
+        one = time.perf_counter() - t0
+        reps = max(1, int(target_s / max(one, 1e-6)))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            call()
+        sec = time.perf_counter() - t0
+        value = batch * reps / sec
+        return value, {"value": value, "unit": UNIT, "cores": 1, "kind": kind,
+                       "sample": f"{reps} reference_window calls of batch {batch} on one layer's weights ({sec:.1f} s, scalar single thread: "
+                                 "the reference has no SIMD or threaded Q8_0 kernel; router ids precomputed)"}
     if O.Ref.available():
         ref = O.Ref()
         args = (g, u, d, cfg["experts"], cfg["hidden"], cfg["inter"], cfg["top_k"], rw, x, threads)
@@ -131,10 +159,10 @@ def cpu_arm(cfg, batch, target_s, threads=None):
 def reference_arm(args, cfg, rank, world):
     if rank != 0:
         return
-    batch = args.batch
+    batch = cfg.get("batch", args.batch) if args.batch == 8 else args.batch
     total = max(1, args.steps + args.warmup)
     value, base = cpu_arm(cfg, batch, target_s=min(60.0, 0.02 * total + 15.0))
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+    line = {"impl": "reference", "metric": METRIC if cfg["gate_type"] == 12 else "MoE-layer tokens/s (Q8_0 decode)", "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1000.0 * batch / value, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {batch}", "l2": "host arm"},
@@ -492,15 +520,16 @@ def main():
         return large_arm(args, cfg, rank, world, dev)
     if world > 1 and args.parallelism == "ep":
         return ep_arm(args, cfg, rank, world, dev)
-    K, W, B, L = args.steps, max(args.warmup, 3), args.batch, args.layers
+    K, W, L = args.steps, max(args.warmup, 3), args.layers
+    B = cfg.get("batch", args.batch) if args.batch == 8 else args.batch
     H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
     shape = ops.make_shape(H, I, E, TK, cfg["gate_type"], cfg["down_type"])
     policy = ops.softmax_policy(E, TK)
+    form = b200moe.COMBINE_PARTS if cfg.get("parts_form") else b200moe.COMBINE_FMA_SLOTS
     layers = []
     for li in range(L):
         g, u, d, rw = make_layer(cfg, 1000 + li + 100 * rank)
-        layers.append(ops.MoeFfn(shape, policy, *(torch.from_numpy(a).to(dev) for a in (g, u, d, rw)), capacity=B,
-                                 combine_form=b200moe.COMBINE_FMA_SLOTS))
+        layers.append(ops.MoeFfn(shape, policy, *(torch.from_numpy(a).to(dev) for a in (g, u, d, rw)), capacity=B, combine_form=form))
     rng = np.random.default_rng(7 + rank)
     NX = 16
     xs_host = [torch.from_numpy(synth.activations(rng, B, H)).pin_memory() for _ in range(NX)]
@@ -624,9 +653,9 @@ def main():
     achieved = algo_bytes / (float(np.mean(kern_ms)) * 1e-3) / 1e9
     step_bytes = float(np.mean(steps_uniq)) * (gate_up_bytes + down_bytes) + E * H * 4
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "metric": METRIC if cfg["gate_type"] == 12 else "MoE-layer tokens/s (Q8_0 decode)", "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
+        "dtype": "int8xint4->int32, fp32 chains" if cfg["gate_type"] == 12 else "int8xint8->int32, fp32 lane classes", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {B}", "parallelism": f"replicas x{world}" if world > 1 else "1 gpu",
                    "l2": f"rotating {L} layers of distinct expert weights ({L * E * (gate_up_bytes + down_bytes) / 2**20:.0f} MiB) > 2 x {L2_BYTES // 2**20} MiB L2",
                    "launch": "CUDA graph replay of the per-step kernel sequence"},
@@ -634,10 +663,11 @@ def main():
         "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
                 "ms_per_step": host_ms / K},
         "gpu_launches": int(round(launches_per_step * K)),
-        "roofline": {"kernel": "gate_up_q4k_stream_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "roofline": {"kernel": "gate_up_q4k_stream_kernel" if cfg["gate_type"] == 12 else "gate_up_q8_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy",
                      # dram read + write per launch from an ncu capture of this kernel on this workload: 1.00 of the algorithmic bytes
-                     "traffic": algo_bytes * NCU_TRAFFIC_RATIO, "traffic_source": "profiles/stream_kernels_c2_decode_b8_dram.md",
+                     "traffic": algo_bytes * NCU_TRAFFIC_RATIO if cfg["gate_type"] == 12 else None,
+                     "traffic_source": "profiles/stream_kernels_c2_decode_b8_dram.md" if cfg["gate_type"] == 12 else None,
                      "algorithmic_bytes_per_launch": algo_bytes, "avg_launch_us": float(np.mean(kern_ms)) * 1000.0,
                      "distinct_experts_per_step": float(np.mean(steps_uniq))},
         "extra": {"step_hbm_gbs_graph": step_bytes / (dev_ms / K * 1e-3) / 1e9, "ms_per_step_no_graph": plain_ms_total / K,

@@ -19,6 +19,9 @@ namespace {
 
 constexpr int kR = 8;
 constexpr u32 kStageBytes = 1088 + 16;
+// Warps per CTA. The kernels are latency bound, not instruction bound: what counts is how many weight rows are in flight,
+// so the routed kernels give every row of a 32-output group its own warp.
+constexpr u32 kRoutedWarps = 32, kDenseWarps = 16;
 
 struct A8View {
     const i8* codes;      // row r at codes + r * stride
@@ -26,21 +29,50 @@ struct A8View {
     u32 stride;
 };
 
+// A run of up to 32 blocks (1088 B = 68 x 16 B) held in registers between its global load and its store to the
+// warp's stage: the load of the NEXT run (of this row or of the warp's next row) is issued before the current run is
+// computed, so a warp always has a run in flight.
+struct RunRegs { uint4 v[3]; };
+__device__ __forceinline__ bool run_is_fast(u32 align, u32 nb) { return align >= 16 && (nb & 7u) == 0; }
+__device__ __forceinline__ void run_load(const u8* src, u32 nb, u32 lane, RunRegs& r) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    const u32 n16 = nb * kQ8Block / 16;
+#pragma unroll
+    for (int k = 0; k < 3; ++k) if (lane + 32u * k < n16) r.v[k] = __ldg(s4 + lane + 32u * k);
+}
+__device__ __forceinline__ void run_store(u32* stage, u32 nb, u32 lane, const RunRegs& r) {
+    uint4* d4 = reinterpret_cast<uint4*>(stage);
+    const u32 n16 = nb * kQ8Block / 16;
+#pragma unroll
+    for (int k = 0; k < 3; ++k) if (lane + 32u * k < n16) d4[lane + 32u * k] = r.v[k];
+}
+
 // One Q8_0 weight row against nr <= kR A8 rows; lane = lane class. `stage` is this warp's 1104-byte scratch.
+// `pre` carries the row's first run when `have_pre` (loaded by the previous call); `next_row` (nullable) is the row the
+// warp takes next: its first run is loaded into `pre` during this row's last run. Returns whether `pre` holds it.
 // Every lane returns the products in out[].
-__device__ __forceinline__ void q8_row(const u8* __restrict__ wrow, u32 groups, u32 align, u32* stage, const A8View& x, int nr,
-                                       u32 lane, float* out) {
+__device__ __forceinline__ bool q8_row(const u8* __restrict__ wrow, u32 groups, u32 align, u32* stage, const A8View& x, int nr,
+                                       u32 lane, float* out, RunRegs& pre, bool have_pre, const u8* next_row) {
     float cls[kR];
 #pragma unroll
     for (int r = 0; r < kR; ++r) cls[r] = 0.0f;
+    bool next_loaded = false;
     for (u32 g0 = 0; g0 < groups; g0 += 32) {
         const u32 nb = min(32u, groups - g0);
         const u8* src = wrow + u64(g0) * kQ8Block;
         __syncwarp();
-        if (align >= 16 && (nb & 7u) == 0) {
-            const uint4* s4 = reinterpret_cast<const uint4*>(src);
-            uint4* d4 = reinterpret_cast<uint4*>(stage);
-            for (u32 i = lane; i < nb * kQ8Block / 16; i += 32) d4[i] = __ldg(s4 + i);
+        if (run_is_fast(align, nb)) {
+            if (!have_pre) run_load(src, nb, lane, pre);
+            run_store(stage, nb, lane, pre);
+            have_pre = false;
+            const u32 g1 = g0 + 32;
+            if (g1 < groups) {  // this row's next run
+                const u32 nb1 = min(32u, groups - g1);
+                if (run_is_fast(align, nb1)) { run_load(wrow + u64(g1) * kQ8Block, nb1, lane, pre); have_pre = true; }
+            } else if (next_row && run_is_fast(align, min(32u, groups))) {  // the next row's first run
+                run_load(next_row, min(32u, groups), lane, pre);
+                next_loaded = true;
+            }
         } else if (align >= 2) {
             const u16* s2 = reinterpret_cast<const u16*>(src);
             u16* d2 = reinterpret_cast<u16*>(stage);
@@ -86,6 +118,7 @@ __device__ __forceinline__ void q8_row(const u8* __restrict__ wrow, u32 groups, 
     }
 #pragma unroll
     for (int r = 0; r < kR; ++r) out[r] = butterfly32(cls[r]);
+    return next_loaded;
 }
 
 __device__ __forceinline__ void stage_rows(const b200moe_a8_rows& src, const u32* idx, u32 first_row, int nr, u32 width, i8* s_codes,
@@ -101,9 +134,9 @@ __device__ __forceinline__ void stage_rows(const b200moe_a8_rows& src, const u32
 }
 
 // Dense site: out[r][o] for o in [first, first + count). grid (ceil(count / 32)); 256 threads; rows in passes of 8.
-__global__ void __launch_bounds__(256) q8_0_a8_kernel(b200moe_q8a8_view v, u32 align) {
+__global__ void __launch_bounds__(1024) q8_0_a8_kernel(b200moe_q8a8_view v, u32 align) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const u32 K = v.width, groups = K / 32;
+    const u32 K = v.width, groups = K / 32, nw = blockDim.x >> 5;
     i8* s_codes = reinterpret_cast<i8*>(smem_raw);
     float* s_deltas = reinterpret_cast<float*>(smem_raw + u64(kR) * K);
     u32* s_stage = reinterpret_cast<u32*>(s_deltas + kR * groups);
@@ -116,11 +149,15 @@ __global__ void __launch_bounds__(256) q8_0_a8_kernel(b200moe_q8a8_view v, u32 a
         __syncthreads();
         stage_rows(v.x, nullptr, r0, nr, K, s_codes, s_deltas);
         __syncthreads();
-        for (u32 t = warp; t < 32; t += 8) {
+        RunRegs pre;
+        bool have_pre = false;
+        for (u32 t = warp; t < 32; t += nw) {
             const u32 o = 32u * blockIdx.x + t;
             if (o >= v.count) break;
             float val[kR];
-            q8_row(v.weight + u64(v.first + o) * v.row_bytes, groups, align, stage, xs, nr, lane, val);
+            const bool more = t + nw < 32 && o + nw < v.count;
+            have_pre = q8_row(v.weight + u64(v.first + o) * v.row_bytes, groups, align, stage, xs, nr, lane, val, pre, have_pre,
+                              more ? v.weight + u64(v.first + o + nw) * v.row_bytes : nullptr);
             if (lane == 0) {
 #pragma unroll
                 for (int r = 0; r < kR; ++r)
@@ -134,9 +171,9 @@ __global__ void __launch_bounds__(256) q8_0_a8_kernel(b200moe_q8a8_view v, u32 a
 }
 
 // Routed gate/up: grid (inter / 32, max_union); 256 threads; one CTA = one expert x one 32-output group.
-__global__ void __launch_bounds__(256) gate_up_q8_kernel(b200moe_gate_up_view v, u32 align) {
+__global__ void __launch_bounds__(1024) gate_up_q8_kernel(b200moe_gate_up_view v, u32 align) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const u32 j = blockIdx.y;
+    const u32 j = blockIdx.y, nw = blockDim.x >> 5;
     if (j >= v.routes.counts[0]) return;
     const u32 H = v.shape.hidden, I = v.shape.inter, groups = H / 32;
     i8* s_codes = reinterpret_cast<i8*>(smem_raw);
@@ -153,6 +190,13 @@ __global__ void __launch_bounds__(256) gate_up_q8_kernel(b200moe_gate_up_view v,
     const u8* up = v.weights.up + (u64(expert) * I + 32u * blockIdx.x) * row_bytes;
     const A8View xs{s_codes, s_deltas, H};
     const u32 act_stride = v.act.stride ? v.act.stride : v.act.width;
+    // the warp's first weight run is requested before the activations are staged: its latency hides behind the staging
+    RunRegs pre;
+    bool have_pre = false;
+    if (warp < 64 && run_is_fast(align, min(32u, groups))) {
+        run_load((warp < 32 ? gate : up) + u64(warp & 31u) * row_bytes, min(32u, groups), lane, pre);
+        have_pre = true;
+    }
     for (u32 p0 = eb; p0 < ee; p0 += kR) {
         const int nr = static_cast<int>(min(u32(kR), ee - p0));
         __syncthreads();
@@ -160,10 +204,12 @@ __global__ void __launch_bounds__(256) gate_up_q8_kernel(b200moe_gate_up_view v,
         __syncthreads();
         stage_rows(v.x, s_rows, 0, nr, H, s_codes, s_deltas);
         __syncthreads();
-        for (u32 t = warp; t < 64; t += 8) {
+        for (u32 t = warp; t < 64; t += nw) {
             const u8* wrow = (t < 32 ? gate : up) + u64(t & 31u) * row_bytes;
+            const u32 tn = t + nw;
             float val[kR];
-            q8_row(wrow, groups, align, stage, xs, nr, lane, val);
+            have_pre = q8_row(wrow, groups, align, stage, xs, nr, lane, val, pre, have_pre,
+                              tn < 64 ? (tn < 32 ? gate : up) + u64(tn & 31u) * row_bytes : nullptr);
             if (lane == 0) {
                 float* dst = t < 32 ? s_g : s_u;
 #pragma unroll
@@ -171,7 +217,7 @@ __global__ void __launch_bounds__(256) gate_up_q8_kernel(b200moe_gate_up_view v,
             }
         }
         __syncthreads();
-        for (int r = warp; r < nr; r += 8) {
+        for (int r = warp; r < nr; r += nw) {
             const float g = s_g[r * 32 + lane], u = s_u[r * 32 + lane];
             const u32 slot = s_slots[r], o = 32u * blockIdx.x + lane;
             if (v.gate_out) { v.gate_out[u64(slot) * I + o] = g; v.up_out[u64(slot) * I + o] = u; }
@@ -189,10 +235,10 @@ __global__ void __launch_bounds__(256) gate_up_q8_kernel(b200moe_gate_up_view v,
 }
 
 // Routed down: grid (hidden / 32, max_union); 256 threads.
-__global__ void __launch_bounds__(256) down_q8_kernel(b200moe_down_view v, u32 align) {
+__global__ void __launch_bounds__(1024) down_q8_kernel(b200moe_down_view v, u32 align) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     if (v.summary && *v.summary) return;
-    const u32 j = blockIdx.y;
+    const u32 j = blockIdx.y, nw = blockDim.x >> 5;
     if (j >= v.routes.counts[0]) return;
     const u32 H = v.shape.hidden, I = v.shape.inter, groups = I / 32;
     i8* s_codes = reinterpret_cast<i8*>(smem_raw);
@@ -206,6 +252,12 @@ __global__ void __launch_bounds__(256) down_q8_kernel(b200moe_down_view v, u32 a
     const u32 o0 = 32u * blockIdx.x;
     const u8* down = v.weights.down + (u64(expert) * H + o0) * row_bytes;
     const A8View xs{s_codes, s_deltas, I};
+    RunRegs pre;  // the first weight run is requested before the activations are staged
+    bool have_pre = false;
+    if (warp < 32 && run_is_fast(align, min(32u, groups))) {
+        run_load(down + u64(warp) * row_bytes, min(32u, groups), lane, pre);
+        have_pre = true;
+    }
     for (u32 p0 = eb; p0 < ee; p0 += kR) {
         const int nr = static_cast<int>(min(u32(kR), ee - p0));
         __syncthreads();
@@ -213,9 +265,10 @@ __global__ void __launch_bounds__(256) down_q8_kernel(b200moe_down_view v, u32 a
         __syncthreads();
         stage_rows(v.act, s_slots, 0, nr, I, s_codes, s_deltas);
         __syncthreads();
-        for (u32 t = warp; t < 32; t += 8) {
+        for (u32 t = warp; t < 32; t += nw) {
             float val[kR];
-            q8_row(down + u64(t) * row_bytes, groups, align, stage, xs, nr, lane, val);
+            have_pre = q8_row(down + u64(t) * row_bytes, groups, align, stage, xs, nr, lane, val, pre, have_pre,
+                              t + nw < 32 ? down + u64(t + nw) * row_bytes : nullptr);
             if (lane == 0) {
 #pragma unroll
                 for (int r = 0; r < kR; ++r) if (r < nr) v.raw[u64(s_slots[r]) * H + o0 + t] = val[r];
@@ -235,9 +288,10 @@ int launch_q8_0_a8(const b200moe_q8a8_view& v, cudaStream_t stream) {
     if (v.count == 0 || v.x.rows == 0) return B200MOE_OK;
     const u32 K = v.width;
     const u32 align = (aligned(v.weight, 16) && v.row_bytes % 16 == 0) ? 16u : ((aligned(v.weight, 2) && v.row_bytes % 2 == 0) ? 2u : 1u);
-    const u32 smem = kR * (K + K / 32 * 4) + 8 * kStageBytes;
+    const u32 nw = kDenseWarps;
+    const u32 smem = kR * (K + K / 32 * 4) + nw * kStageBytes;
     if (int rc = set_smem(q8_0_a8_kernel, smem)) return rc;
-    q8_0_a8_kernel<<<(v.count + 31) / 32, 256, smem, stream>>>(v, align);
+    q8_0_a8_kernel<<<(v.count + 31) / 32, nw * 32, smem, stream>>>(v, align);
     return after_launch("q8_0_a8");
 }
 
@@ -245,9 +299,10 @@ int launch_gate_up_q8(const b200moe_gate_up_view& v, cudaStream_t stream) {
     if (v.max_union == 0) return B200MOE_OK;
     const u32 H = v.shape.hidden, I = v.shape.inter;
     const u32 align = (aligned(v.weights.gate, 16) && aligned(v.weights.up, 16) && (H / 32 * kQ8Block) % 16 == 0) ? 16u : 2u;
-    const u32 smem = kR * (H + H / 32 * 4) + 2 * kR * 32 * 4 + 8 * kStageBytes;
+    const u32 nw = kRoutedWarps;   // 64 weight rows per CTA: two per warp, the second one prefetched
+    const u32 smem = kR * (H + H / 32 * 4) + 2 * kR * 32 * 4 + nw * kStageBytes;
     if (int rc = set_smem(gate_up_q8_kernel, smem)) return rc;
-    gate_up_q8_kernel<<<dim3(I / 32, v.max_union), 256, smem, stream>>>(v, align);
+    gate_up_q8_kernel<<<dim3(I / 32, v.max_union), nw * 32, smem, stream>>>(v, align);
     return after_launch("gate_up_q8");
 }
 
@@ -255,9 +310,10 @@ int launch_down_q8(const b200moe_down_view& v, cudaStream_t stream) {
     if (v.max_union == 0) return B200MOE_OK;
     const u32 H = v.shape.hidden, I = v.shape.inter;
     const u32 align = (aligned(v.weights.down, 16) && (I / 32 * kQ8Block) % 16 == 0) ? 16u : 2u;
-    const u32 smem = kR * (I + I / 32 * 4) + 8 * kStageBytes;
+    const u32 nw = kRoutedWarps;   // 32 weight rows per CTA: one per warp, every row of the expert in flight at once
+    const u32 smem = kR * (I + I / 32 * 4) + nw * kStageBytes;
     if (int rc = set_smem(down_q8_kernel, smem)) return rc;
-    down_q8_kernel<<<dim3(H / 32, v.max_union), 256, smem, stream>>>(v, align);
+    down_q8_kernel<<<dim3(H / 32, v.max_union), nw * 32, smem, stream>>>(v, align);
     return after_launch("down_q8");
 }
 

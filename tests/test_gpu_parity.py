@@ -424,6 +424,36 @@ def test_experts_q4k_grouped_tensor_core_form(gpu, oracle):
     print("grouped form bit-exact on every case:", exact_all)
 
 
+def test_experts_q4k_collisions_and_empty_experts(gpu, oracle):
+    """Every row routed to the same two experts (64 entries per expert: many passes of the decode form; 200 entries:
+    several token tiles of the grouped form), all other experts empty; and the opposite, one entry per expert."""
+    import b200moe
+    from b200moe import synth
+    rng = np.random.default_rng(33)
+    E, H, I, K = 12, 512, 256, 2
+    gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
+    sh, osh = shape_pair(H, I, E, K, 12, 12)
+    for rows in (64, 200):
+        x = rng.standard_normal((rows, H), dtype=np.float32)
+        ids = np.tile(np.array([[7, 2]], np.uint32), (rows, 1))
+        wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
+        run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, exact=False)
+    x = rng.standard_normal((6, H), dtype=np.float32)
+    ids = np.arange(12, dtype=np.uint32).reshape(6, 2)
+    run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, rng.uniform(0.05, 0.6, size=(6, K)).astype(np.float32),
+               b200moe.COMBINE_FMA_SLOTS, exact=False)
+
+
+def test_routes_maximum_sizes(gpu, oracle):
+    """1024 experts and top-32 (the ABI's limits), one-block and chunked windows, with an owned expert range."""
+    from b200moe import ops
+    rng = np.random.default_rng(34)
+    for rows, first, end in ((8, 0, 0), (70, 0, 0), (70, 256, 768)):
+        ids = np.stack([rng.permutation(1024)[:32] for _ in range(rows)]).astype(np.uint32)
+        want = oracle.routes(ids, 1024, 512, first, end, first)
+        check_routes(ops.enqueue_moe_routes(dv(ids.view(np.int32), gpu), 1024, 512, first, end, first), want)
+
+
 def test_experts_fail_closed(gpu, oracle):
     """A non-finite projection sets status bit 8 on its row, the summary word, and the down stage writes nothing
     (src/cpu/core/routed_expert.hpp:17-19; host-side injection as tests/cpu/routed_expert_host_tests.cpp:393-399)."""
