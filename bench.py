@@ -327,7 +327,7 @@ def large_arm(args, cfg, rank, world, dev):
     ys_host = torch.empty((B, H), dtype=torch.float32).pin_memory()
     if world > 1:
         kern = ep.DeviceKernels(shape, policy, rw, gate, up, down, world * B, b200moe.COMBINE_PARTS, world, rank, select_bias=bias)
-        routed = ep.EpMoeFfn(kern, B, TK, H, b200moe.COMBINE_PARTS)
+        routed = ep.EpMoeFfn(kern, B, TK, H, b200moe.COMBINE_PARTS, peer_return=not args.no_peer_return, device=dev)
         fn = lambda x, shared: routed(x, shared)
     else:
         ffn = ops.MoeFfn(shape, policy, gate, up, down, rw, capacity=B, combine_form=b200moe.COMBINE_PARTS, parts=PARTS, select_bias=bias)
@@ -380,7 +380,7 @@ def large_arm(args, cfg, rank, world, dev):
         "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {B} per rank",
                    "parallelism": f"ep x{world} ({per} experts per rank)" if world > 1 else "1 gpu (all 256 experts)",
-                   "l2": "6.3 GB of routed expert weights per layer (far beyond L2)", "launch": "per-step launches" + (" + NCCL" if world > 1 else "")},
+                   "l2": "6.3 GB of routed expert weights per layer (far beyond L2)", "launch": "per-step launches" + ((" + NCCL all-gather dispatch, " + ("all-to-all return" if args.no_peer_return else "peer-store return (CUDA IPC) + 1-word all-reduce")) if world > 1 else "")},
         "clocks": sampler.summary(),
         "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
                 "ms_per_step": host_ms / K},
@@ -495,6 +495,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=4, help="distinct layers of weights rotated between steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-peer-return", action="store_true",
+                    help="expert parallelism, PARTS form: return the partial sums with an NCCL all-to-all instead of the combine kernel's peer stores")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
                     help="N > 1: independent replicas (rows sharded, weights replicated, no collective) or expert parallelism "
                          "(experts / N per rank, all-gather dispatch + all-to-all return over NCCL)")

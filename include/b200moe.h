@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 1
+#define B200MOE_ABI_VERSION 2
 
 /* Status codes (values follow strix::weight::Error's role, include/strix/weight/types.hpp:35-40). */
 enum {
@@ -266,6 +266,12 @@ typedef struct b200moe_combine_view {
     float* y;                  /* [rows][hidden] */
     uint16_t* y_bf16;          /* optional */
     const uint32_t* row_status; /* optional: a row with status != 0 is not written (fail closed) */
+    /* Optional scatter of y by row blocks (expert parallelism: each block of y_block_rows rows belongs to another home
+     * rank and is written straight into that rank's memory by this kernel - plain peer stores over NVLink, no
+     * collective in between): a DEVICE array of ceil(rows / y_block_rows) pointers; row r goes to
+     * y_blocks[r / y_block_rows] + (r % y_block_rows) * hidden. When set, y may be NULL and y_bf16 must be NULL. */
+    float* const* y_blocks;
+    uint32_t y_block_rows;
 } b200moe_combine_view;
 int b200moe_combine(const b200moe_combine_view* view, void* stream);
 
@@ -284,6 +290,14 @@ int b200moe_canonical_sum(const float* a, const float* b, const float* c, uint64
  * select_owner_slots: raw[s] = blocks[owner(s)][s] with owner(s) = min(ids[s] / experts_per_block, n_blocks - 1): every
  *   peer returned a [slots][hidden] block of raw slot vectors of which only its own experts' slots are meaningful
  *   (include/strix/ds41_moe.hpp:5-8); the result feeds b200moe_combine (the Qwen form's chain cannot be split by rank). */
+/* Buffers other ranks of the node write into (CUDA IPC; set-up time, these calls allocate / map memory and
+ * synchronise). create: cudaMalloc + the 64-byte IPC handle to send to the peers; open: map a peer's buffer from its
+ * handle (peer access is enabled on first use); close / destroy undo them. The reference's counterpart is the
+ * DirectTransport's registered windows (docs/engine/transport/communicator.md: "registered windows, submit, repost"). */
+int b200moe_peer_buffer_create(uint64_t bytes, void** dev_ptr, void* ipc_handle_64);
+int b200moe_peer_buffer_open(const void* ipc_handle_64, void** dev_ptr);
+int b200moe_peer_buffer_close(void* dev_ptr);
+int b200moe_peer_buffer_destroy(void* dev_ptr);
 int b200moe_fold_parts(const float* parts, uint32_t n_parts, uint64_t part_stride, const float* shared, uint64_t count, float* y,
                        uint16_t* y_bf16, void* stream);
 int b200moe_select_owner_slots(const float* blocks, uint64_t block_stride, uint32_t n_blocks, uint32_t experts_per_block,
@@ -316,6 +330,8 @@ typedef struct b200moe_layer_view {
      * cudaEvent_t handles recorded on the stream before / after the stages routes, gate/up, down, combine
      * ([2 * stage], [2 * stage + 1]). NULL: nothing is recorded. */
     void* const* stage_events;
+    float* const* y_blocks;     /* optional, with y_block_rows: see b200moe_combine_view */
+    uint32_t y_block_rows;
 } b200moe_layer_view;
 uint64_t b200moe_layer_workspace_bytes(const b200moe_shape* shape, uint32_t capacity);
 int b200moe_layer(const b200moe_layer_view* view, void* stream);

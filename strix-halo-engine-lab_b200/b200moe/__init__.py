@@ -87,14 +87,15 @@ class DownView(C.Structure):
 class CombineView(C.Structure):
     _fields_ = [("raw", vp), ("shared", vp), ("weights", vp), ("ids", vp), ("order", vp), ("rows", u32), ("top_k", u32),
                 ("hidden", u32), ("form", u32), ("parts", u32), ("part_experts", u32), ("only_part", i32), ("y", vp),
-                ("y_bf16", vp), ("row_status", vp)]
+                ("y_bf16", vp), ("row_status", vp), ("y_blocks", vp), ("y_block_rows", u32)]
 
 
 class LayerView(C.Structure):
     _fields_ = [("shape", Shape), ("weights", ExpertWeights), ("rows", u32), ("x", A8Rows), ("ids", vp), ("route_weights", vp),
                 ("shared", vp), ("first", u32), ("end", u32), ("base", u32), ("combine_form", u32), ("parts", u32),
                 ("part_experts", u32), ("only_part", i32), ("raw", vp), ("y", vp), ("y_bf16", vp), ("row_status", vp),
-                ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32), ("stage_events", vp)]
+                ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32), ("stage_events", vp),
+                ("y_blocks", vp), ("y_block_rows", u32)]
 
 
 class FfnView(C.Structure):
@@ -115,7 +116,8 @@ EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", 
            "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_routes_static_max_words",
            "b200moe_build_routes_static", "b200moe_gate_row_bytes",
            "b200moe_down_row_bytes", "b200moe_expert_bytes", "b200moe_gate_up", "b200moe_down", "b200moe_combine",
-           "b200moe_canonical_sum", "b200moe_fold_parts", "b200moe_select_owner_slots", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
+           "b200moe_canonical_sum", "b200moe_fold_parts", "b200moe_select_owner_slots", "b200moe_peer_buffer_create",
+           "b200moe_peer_buffer_open", "b200moe_peer_buffer_close", "b200moe_peer_buffer_destroy", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
            "b200moe_ffn", "b200moe_ffn_host", "b200moe_dense_ffn"]
 
 _lib = None
@@ -149,6 +151,13 @@ def lib():
             getattr(L, n).argtypes = [C.POINTER(t), vp]
         L.b200moe_ffn_host.restype = C.c_int
         L.b200moe_ffn_host.argtypes = [C.POINTER(FfnView), vp, vp, vp]
+        L.b200moe_peer_buffer_create.restype = C.c_int
+        L.b200moe_peer_buffer_create.argtypes = [u64, C.POINTER(vp), vp]
+        L.b200moe_peer_buffer_open.restype = C.c_int
+        L.b200moe_peer_buffer_open.argtypes = [vp, C.POINTER(vp)]
+        for n in ("b200moe_peer_buffer_close", "b200moe_peer_buffer_destroy"):
+            getattr(L, n).restype = C.c_int
+            getattr(L, n).argtypes = [vp]
         L.b200moe_fold_parts.restype = C.c_int
         L.b200moe_fold_parts.argtypes = [vp, u32, u64, vp, u64, vp, vp, vp]
         L.b200moe_select_owner_slots.restype = C.c_int

@@ -11,7 +11,9 @@ One step, every rank alike:
                (Every rank sees every row; at decode sizes the volume is a few hundred KB and the step is latency bound.)
   3. experts:  b200moe_layer over the global window restricted to the rank's expert range, on its local tensors.
                PARTS form: the rank's partial sum S_r per row (only_part = r).  FMA_SLOTS form: raw slot vectors.
-  4. return:   all-to-all, the block of home rank h goes to h.
+  4. return:   all-to-all, the block of home rank h goes to h - or, with peer_return (PARTS form, one node), no
+               collective at all: the combine kernel stores each home rank's rows straight into that rank's buffer
+               (CUDA IPC peer memory over NVLink), then a one-word all-reduce as the barrier.
   5. combine:  PARTS: y = ((shared + S_0) + S_1) ... in rank order (b200moe_fold_parts).
                FMA_SLOTS: slot s is taken from the block of the rank that owns ids[s] (b200moe_select_owner_slots), then
                the ordinary slot-order chain (b200moe_combine).
@@ -49,16 +51,23 @@ class DeviceKernels:
         _, _, ids, wts = ops.enqueue_router(self.policy, x=x, weight=self.router_weight, logit_bias=self.logit_bias, bias=self.select_bias)
         return codes, deltas, sums, ids, wts
 
-    def experts(self, a8, ids, wts):
+    def experts(self, a8, ids, wts, y_blocks=None, y_block_rows=0):
         first = self.rank * self.per
         if self.combine_form == COMBINE_PARTS:
-            return self.layer(a8, ids, wts, first=first, end=first + self.per, base=first, only_part=self.rank)
+            return self.layer(a8, ids, wts, first=first, end=first + self.per, base=first, only_part=self.rank,
+                              y_blocks=y_blocks, y_block_rows=y_block_rows)
         return self.layer(a8, ids, wts, first=first, end=first + self.per, base=first, want_raw=True, combine=False)[1]
 
     def fold(self, parts, shared):
         world, rows, hidden = parts.shape
         y = torch.empty((rows, hidden), dtype=torch.float32, device=parts.device)
         check(lib().b200moe_fold_parts(ptr(parts), world, rows * hidden, ptr(shared), rows * hidden, ptr(y), None, stream_ptr()))
+        return y
+
+    def fold_at(self, parts_ptr, world, rows, hidden, shared, device):
+        """fold over a raw device pointer (a peer buffer of this rank)."""
+        y = torch.empty((rows, hidden), dtype=torch.float32, device=device)
+        check(lib().b200moe_fold_parts(parts_ptr, world, rows * hidden, ptr(shared), rows * hidden, ptr(y), None, stream_ptr()))
         return y
 
     def combine_slots(self, blocks, ids, wts, shared):
@@ -69,14 +78,72 @@ class DeviceKernels:
         return ops.enqueue_moe_combine(COMBINE_FMA_SLOTS, raw, wts, ids, shared=shared)
 
 
-class EpMoeFfn:
-    """One MoE FFN layer under expert parallelism. Every rank calls it with the same number of local rows."""
+class PeerBuffers:
+    """Receive buffers of the PARTS return step that the peers write DIRECTLY (CUDA IPC, one node): two buffers per rank
+    ([world][rows][hidden] FP32, alternating by step), every rank maps every other rank's. The combine kernel of rank r
+    stores the partial sums of home rank h's rows straight into block r of h's buffer - peer stores over NVLink from
+    the kernel that computes them, no all-to-all. A stream-ordered NCCL all-reduce of one word is the barrier between
+    "everyone has written" and the home rank's fold; alternating buffers keep step s + 1's stores away from a fold of
+    step s that may still be running."""
 
-    def __init__(self, kernels, rows, top_k, hidden, combine_form, group=None):
+    def __init__(self, rows, hidden, group, device):
+        self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        self.rows, self.hidden, self.device = rows, hidden, device
+        L = lib()
+        nbytes = self.world * rows * hidden * 4
+        self.mine, handles = [], []
+        for _ in range(2):
+            p, h = C.c_void_p(), C.create_string_buffer(64)
+            check(L.b200moe_peer_buffer_create(nbytes, C.byref(p), h))
+            self.mine.append(p.value)
+            handles.append(h.raw)
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, handles, group=group)
+        self.opened = []
+        self.tables = []                       # per parity: device array of world pointers (block `rank` of each home's buffer)
+        block = rows * hidden * 4
+        for parity in range(2):
+            ptrs = []
+            for h in range(self.world):
+                if h == self.rank:
+                    base = self.mine[parity]
+                else:
+                    p = C.c_void_p()
+                    check(L.b200moe_peer_buffer_open(everyone[h][parity], C.byref(p)))
+                    self.opened.append(p.value)
+                    base = p.value
+                ptrs.append(base + self.rank * block)
+            self.tables.append(torch.tensor(ptrs, dtype=torch.int64, device=device))
+        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.step = 0
+        dist.barrier(group=group)
+
+    def barrier(self):
+        dist.all_reduce(self.flag, group=self.group)   # stream-ordered: runs after this rank's stores, before its fold
+
+    def close(self):
+        L = lib()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for p in self.opened:
+            L.b200moe_peer_buffer_close(p)
+        dist.barrier(group=self.group)
+        for p in self.mine:
+            L.b200moe_peer_buffer_destroy(p)
+        self.opened, self.mine = [], []
+
+
+class EpMoeFfn:
+    """One MoE FFN layer under expert parallelism. Every rank calls it with the same number of local rows.
+    peer_return=True (PARTS form, CUDA ranks of one node): the return step is the combine kernel's own peer stores
+    (PeerBuffers) instead of an all-to-all."""
+
+    def __init__(self, kernels, rows, top_k, hidden, combine_form, group=None, peer_return=False, device=None):
         self.k, self.rows, self.top_k, self.hidden, self.form = kernels, rows, top_k, hidden, combine_form
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
+        self.peers = PeerBuffers(rows, hidden, group, device) if peer_return and combine_form == COMBINE_PARTS else None
 
     def _all_gather(self, t):
         out = torch.empty((self.world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
@@ -94,6 +161,13 @@ class EpMoeFfn:
             raise ValueError(f"every rank passes {self.rows} rows, got {x.shape[0]}")
         codes, deltas, sums, ids, wts = self.k.route(x)
         g = [self._all_gather(t) for t in (codes, deltas, sums, ids, wts)]
+        if self.peers is not None:
+            pb = self.peers
+            parity = pb.step & 1
+            pb.step += 1
+            self.k.experts((g[0], g[1], g[2]), g[3], g[4], y_blocks=pb.tables[parity], y_block_rows=self.rows)
+            pb.barrier()
+            return self.k.fold_at(pb.mine[parity], self.world, self.rows, self.hidden, shared, x.device)
         out = self.k.experts((g[0], g[1], g[2]), g[3], g[4])
         if self.form == COMBINE_PARTS:      # out [world * rows][hidden]: the rank's partial sums of every row
             parts = self._return_home(out.view(self.world, self.rows, self.hidden))

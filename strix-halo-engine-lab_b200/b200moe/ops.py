@@ -144,15 +144,18 @@ class MoeLayer:
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=gate.device)
 
     def __call__(self, x_a8, ids, route_weights, shared=None, first=0, end=0, base=0, only_part=-1, want_raw=False, bf16=False,
-                 row_status=None, combine=True):
+                 row_status=None, combine=True, y_blocks=None, y_block_rows=0):
+        """y_blocks: int64 device tensor of destination pointers (one per block of y_block_rows rows): the combine writes
+        there (peer buffers under expert parallelism) and no y is returned."""
         rows = ids.shape[0]
         dev = self.gate.device
-        y = torch.zeros((rows, self.shape.hidden), dtype=torch.float32, device=dev) if combine else None
+        y = torch.zeros((rows, self.shape.hidden), dtype=torch.float32, device=dev) if combine and y_blocks is None else None
         yb = torch.zeros((rows, self.shape.hidden), dtype=torch.bfloat16, device=dev) if bf16 else None
         raw = torch.zeros((rows * self.shape.top_k, self.shape.hidden), dtype=torch.float32, device=dev) if want_raw else None
         v = LayerView(self.shape, ExpertWeights(ptr(self.gate), ptr(self.up), ptr(self.down)), rows, a8_rows(*x_a8), ptr(ids),
                       ptr(route_weights), ptr(shared), first, end, base, self.combine_form, self.parts, self.part_experts, only_part,
-                      ptr(raw), ptr(y), ptr(yb), ptr(row_status), ptr(self.ws), self.ws_bytes, self.capacity, self.grouped_min_rows, None)
+                      ptr(raw), ptr(y), ptr(yb), ptr(row_status), ptr(self.ws), self.ws_bytes, self.capacity, self.grouped_min_rows, None,
+                      ptr(y_blocks), y_block_rows)
         check(lib().b200moe_layer(C.byref(v), stream_ptr()))
         out = [y]
         if want_raw:

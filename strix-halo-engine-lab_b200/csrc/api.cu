@@ -298,7 +298,8 @@ int b200moe_down(const b200moe_down_view* v, void* stream) {
 
 int b200moe_combine(const b200moe_combine_view* v, void* stream) {
     B200_REQUIRE(v, "null view");
-    B200_REQUIRE(v->raw && v->weights && v->y, "combine: raw / weights / y are null");
+    B200_REQUIRE(v->raw && v->weights && (v->y || v->y_blocks), "combine: raw / weights / y are null");
+    B200_REQUIRE(!v->y_blocks || (v->y_block_rows && !v->y_bf16), "combine: y_blocks needs y_block_rows > 0 and no y_bf16");
     B200_REQUIRE(v->top_k && v->top_k <= kMaxTopK && v->hidden, "combine: need 0 < top_k <= 32 and hidden > 0");
     B200_REQUIRE(v->form <= B200MOE_COMBINE_FMA_SLOTS, "combine: unknown form %u", v->form);
     if (v->form == B200MOE_COMBINE_PARTS) {
@@ -384,12 +385,13 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
     if (int rc = enqueue_down(dn, v->rows, st, v->grouped_min_rows)) return rc;
     tap(5);
 
-    if (!v->y) return B200MOE_OK;
+    if (!v->y && !v->y_blocks) return B200MOE_OK;
+    B200_REQUIRE(!v->y_blocks || (v->y_block_rows && !v->y_bf16), "layer: y_blocks needs y_block_rows > 0 and no y_bf16");
     b200moe_combine_view cv{};
     cv.raw = raw; cv.shared = v->shared; cv.weights = v->route_weights; cv.ids = v->ids; cv.order = L.routes.order;
     cv.rows = v->rows; cv.top_k = s.top_k; cv.hidden = s.hidden; cv.form = v->combine_form;
     cv.parts = v->parts; cv.part_experts = v->part_experts; cv.only_part = v->only_part;
-    cv.y = v->y; cv.y_bf16 = v->y_bf16;
+    cv.y = v->y; cv.y_bf16 = v->y_bf16; cv.y_blocks = v->y_blocks; cv.y_block_rows = v->y_block_rows;
     cv.row_status = s.gate_type == B200MOE_TYPE_Q4_K ? row_status : nullptr;
     tap(6);
     const int rc = launch_combine(cv, st);

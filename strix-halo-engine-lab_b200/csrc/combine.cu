@@ -53,6 +53,11 @@ __global__ void __launch_bounds__(256) combine_kernel(b200moe_combine_view v) {
         }
         out = v.only_part >= 0 ? single : total;
     }
+    if (v.y_blocks) {  // the row's home rank's buffer: a peer store
+        const u32 blk = row / v.y_block_rows;
+        v.y_blocks[blk][u64(row - blk * v.y_block_rows) * v.hidden + o] = out;
+        return;
+    }
     v.y[u64(row) * v.hidden + o] = out;
     if (v.y_bf16) v.y_bf16[u64(row) * v.hidden + o] = bf16_rne_bits(out);
 }

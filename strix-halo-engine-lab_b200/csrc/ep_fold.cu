@@ -9,6 +9,8 @@
 //    produces the same raw vectors"). Every peer returns a full [slots][hidden] block of which only the slots of its
 //    own experts are meaningful; this picks slot s from the block of the rank that owns expert ids[s].
 // Pure data movement and FP32 adds: HBM-bound, tiny at decode sizes.
+#include <cstring>
+
 #include "kernels.cuh"
 
 namespace b200moe {
@@ -38,6 +40,49 @@ __global__ void __launch_bounds__(256) select_owner_slots_kernel(const float* __
 }  // namespace b200moe
 
 extern "C" {
+
+int b200moe_peer_buffer_create(uint64_t bytes, void** dev_ptr, void* ipc_handle_64) {
+    using namespace b200moe;
+    B200_REQUIRE(bytes && dev_ptr && ipc_handle_64, "peer_buffer_create: bytes / dev_ptr / ipc_handle are null");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the IPC handle is sent as 64 bytes");
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h{};
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        if (p) cudaFree(p);
+        return fail(B200MOE_ERR_CUDA, "peer_buffer_create: %s", cudaGetErrorString(e));
+    }
+    std::memcpy(ipc_handle_64, &h, 64);
+    *dev_ptr = p;
+    return B200MOE_OK;
+}
+int b200moe_peer_buffer_open(const void* ipc_handle_64, void** dev_ptr) {
+    using namespace b200moe;
+    B200_REQUIRE(ipc_handle_64 && dev_ptr, "peer_buffer_open: ipc_handle / dev_ptr are null");
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    cudaIpcMemHandle_t h{};
+    std::memcpy(&h, ipc_handle_64, 64);
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(B200MOE_ERR_COMM, "peer_buffer_open: %s", cudaGetErrorString(e));
+    *dev_ptr = p;
+    return B200MOE_OK;
+}
+int b200moe_peer_buffer_close(void* dev_ptr) {
+    using namespace b200moe;
+    B200_REQUIRE(dev_ptr, "peer_buffer_close: null pointer");
+    const cudaError_t e = cudaIpcCloseMemHandle(dev_ptr);
+    return e == cudaSuccess ? B200MOE_OK : fail(B200MOE_ERR_COMM, "peer_buffer_close: %s", cudaGetErrorString(e));
+}
+int b200moe_peer_buffer_destroy(void* dev_ptr) {
+    using namespace b200moe;
+    B200_REQUIRE(dev_ptr, "peer_buffer_destroy: null pointer");
+    const cudaError_t e = cudaFree(dev_ptr);
+    return e == cudaSuccess ? B200MOE_OK : fail(B200MOE_ERR_CUDA, "peer_buffer_destroy: %s", cudaGetErrorString(e));
+}
 
 int b200moe_fold_parts(const float* parts, uint32_t n_parts, uint64_t part_stride, const float* shared, uint64_t count, float* y,
                        uint16_t* y_bf16, void* stream) {

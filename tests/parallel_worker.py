@@ -110,7 +110,7 @@ class OracleDenseKernels:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["ep_parts", "ep_fma", "tp", "tp_allreduce"])
+    ap.add_argument("--case", required=True, choices=["ep_parts", "ep_parts_peer", "ep_fma", "tp", "tp_allreduce"])
     ap.add_argument("--backend", default="gloo")
     ap.add_argument("--out", required=True)
     a = ap.parse_args()
@@ -128,7 +128,7 @@ def main():
     put = lambda arr: torch.from_numpy(np.ascontiguousarray(arr)).to(dev)
 
     if a.case.startswith("ep"):
-        form = b200moe.COMBINE_PARTS if a.case == "ep_parts" else b200moe.COMBINE_FMA_SLOTS
+        form = b200moe.COMBINE_PARTS if a.case.startswith("ep_parts") else b200moe.COMBINE_FMA_SLOTS
         gate, up, down, rw, x, shared = ep_inputs(world)
         per = E // world
         x_l, sh_l = x[rank * ROWS:(rank + 1) * ROWS], shared[rank * ROWS:(rank + 1) * ROWS]
@@ -140,7 +140,13 @@ def main():
                                  world, rank)
         else:
             k = OracleEpKernels(orc, O.Shape(H, I, E, K, 12, 12, float("inf")), O.softmax_policy(E, K), rw, gate, up, down, form, world, rank)
-        y = ep.EpMoeFfn(k, ROWS, K, H, form)(put(x_l), put(sh_l))
+        layer = ep.EpMoeFfn(k, ROWS, K, H, form, peer_return=a.case == "ep_parts_peer", device=dev)
+        y = layer(put(x_l), put(sh_l))
+        if layer.peers is not None:       # a second and third step: the alternating buffers
+            y = layer(put(x_l), put(sh_l))
+            y = layer(put(x_l), put(sh_l))
+            torch.cuda.synchronize()
+            layer.peers.close()
     else:
         gate, up, down, x = tp_inputs()
         start, size = tp.tp_shares(DI, world)[rank]

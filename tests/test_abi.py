@@ -30,7 +30,7 @@ def test_exports_match_header(lib):
     assert declared == set(b200moe.EXPORTS), declared ^ set(b200moe.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.b200moe_abi_version() == 1
+    assert lib.b200moe_abi_version() == 2
 
 
 def test_struct_layouts(tmp_path):

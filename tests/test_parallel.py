@@ -107,7 +107,7 @@ def _two_gpus():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("case,form", [("ep_parts", 0), ("ep_fma", 1)])
+@pytest.mark.parametrize("case,form", [("ep_parts", 0), ("ep_parts_peer", 0), ("ep_fma", 1)])
 def test_expert_parallel_two_gpus_nccl(oracle, case, form):
     if not _two_gpus():
         pytest.skip("needs 2 CUDA devices")
