@@ -383,6 +383,36 @@ typedef struct b200moe_dense_view {
 } b200moe_dense_view;
 int b200moe_dense_ffn(const b200moe_dense_view* view, void* stream);
 
+/* ------------------------------------------------------------------------------------------------ GGUF container
+ * Reader for the files the expert tensors come in, with the reference reader's admission rules (strix::gguf::read_file,
+ * include/strix/gguf_reader.hpp:104-111; src/gguf_reader.cpp:23-99, :330-373): GGUF v3 little-endian, bounded counts,
+ * no duplicate keys or names, zero padding, aligned / in-file / non-overlapping tensor ranges, sizes from the block
+ * geometry. Host-only calls (no CUDA); the handle owns the strings the infos point to. */
+typedef struct b200moe_gguf_tensor_info {
+    const char* name;
+    uint32_t n_dims;
+    uint64_t dims[4];     /* GGUF order: dims[0] is the innermost (row length in elements) */
+    uint32_t ggml_type;
+    uint64_t offset;      /* absolute file offset of the data */
+    uint64_t bytes;
+} b200moe_gguf_tensor_info;
+/* The expert tensors and the router of layer L under their conventional names blk.<L>.ffn_{gate,up,down}_exps.weight and
+ * blk.<L>.ffn_gate_inp.weight (roles expert_gate / expert_up / expert_down / router of include/strix/weight/types.hpp:30-34),
+ * cross-checked ([hidden, inter, experts] / [inter, hidden, experts] / F32 [hidden, experts]); shape.top_k is left 0
+ * (routing metadata is not tensor geometry). The byte ranges are the kernels' layout as they lie in the file. */
+typedef struct b200moe_gguf_moe_layer {
+    b200moe_gguf_tensor_info gate, up, down, router;
+    b200moe_shape shape;
+} b200moe_gguf_moe_layer;
+int b200moe_gguf_open(const char* path, void** file);
+void b200moe_gguf_close(void* file);
+uint64_t b200moe_gguf_tensor_count(const void* file);
+uint64_t b200moe_gguf_data_offset(const void* file);
+uint64_t b200moe_gguf_alignment(const void* file);
+int b200moe_gguf_tensor_at(const void* file, uint64_t index, b200moe_gguf_tensor_info* out);
+int b200moe_gguf_find(const void* file, const char* name, b200moe_gguf_tensor_info* out);
+int b200moe_gguf_find_moe_layer(const void* file, uint32_t layer, b200moe_gguf_moe_layer* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -111,6 +111,14 @@ class DenseView(C.Structure):
                 ("workspace", vp), ("workspace_bytes", u64)]
 
 
+class GgufTensorInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("n_dims", u32), ("dims", u64 * 4), ("ggml_type", u32), ("offset", u64), ("bytes", u64)]
+
+
+class GgufMoeLayer(C.Structure):
+    _fields_ = [("gate", GgufTensorInfo), ("up", GgufTensorInfo), ("down", GgufTensorInfo), ("router", GgufTensorInfo), ("shape", Shape)]
+
+
 # every symbol include/b200moe.h declares (tests check that the library exports each of them)
 EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_quantize_a8", "b200moe_q8_0_a8",
            "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_routes_static_max_words",
@@ -118,7 +126,9 @@ EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", 
            "b200moe_down_row_bytes", "b200moe_expert_bytes", "b200moe_gate_up", "b200moe_down", "b200moe_combine",
            "b200moe_canonical_sum", "b200moe_fold_parts", "b200moe_select_owner_slots", "b200moe_peer_buffer_create",
            "b200moe_peer_buffer_open", "b200moe_peer_buffer_close", "b200moe_peer_buffer_destroy", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
-           "b200moe_ffn", "b200moe_ffn_host", "b200moe_dense_ffn"]
+           "b200moe_ffn", "b200moe_ffn_host", "b200moe_dense_ffn", "b200moe_gguf_open", "b200moe_gguf_close",
+           "b200moe_gguf_tensor_count", "b200moe_gguf_data_offset", "b200moe_gguf_alignment", "b200moe_gguf_tensor_at", "b200moe_gguf_find",
+           "b200moe_gguf_find_moe_layer"]
 
 _lib = None
 
@@ -151,6 +161,19 @@ def lib():
             getattr(L, n).argtypes = [C.POINTER(t), vp]
         L.b200moe_ffn_host.restype = C.c_int
         L.b200moe_ffn_host.argtypes = [C.POINTER(FfnView), vp, vp, vp]
+        L.b200moe_gguf_open.restype = C.c_int
+        L.b200moe_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+        L.b200moe_gguf_close.restype = None
+        L.b200moe_gguf_close.argtypes = [vp]
+        for n in ("b200moe_gguf_tensor_count", "b200moe_gguf_data_offset", "b200moe_gguf_alignment"):
+            getattr(L, n).restype = u64
+            getattr(L, n).argtypes = [vp]
+        L.b200moe_gguf_tensor_at.restype = C.c_int
+        L.b200moe_gguf_tensor_at.argtypes = [vp, u64, C.POINTER(GgufTensorInfo)]
+        L.b200moe_gguf_find.restype = C.c_int
+        L.b200moe_gguf_find.argtypes = [vp, C.c_char_p, C.POINTER(GgufTensorInfo)]
+        L.b200moe_gguf_find_moe_layer.restype = C.c_int
+        L.b200moe_gguf_find_moe_layer.argtypes = [vp, u32, C.POINTER(GgufMoeLayer)]
         L.b200moe_peer_buffer_create.restype = C.c_int
         L.b200moe_peer_buffer_create.argtypes = [u64, C.POINTER(vp), vp]
         L.b200moe_peer_buffer_open.restype = C.c_int
