@@ -180,6 +180,14 @@ FfnScratch carve_ffn(void* ws, const b200moe_shape& s, u32 capacity) {
     return F;
 }
 
+// Zeroes the job summary (4 words) and, when it lives in the workspace, the per-row status behind it. The two sections
+// are neighbours in the workspace (carve_layer), so one memset node covers both and the padding between them.
+cudaError_t clear_status(const LayerScratch& L, bool with_row_status, u32 rows, cudaStream_t st) {
+    const unsigned char* b = reinterpret_cast<const unsigned char*>(L.summary);
+    const unsigned char* e = with_row_status ? reinterpret_cast<const unsigned char*>(L.row_status + rows) : b + 16;
+    return cudaMemsetAsync(L.summary, 0, static_cast<size_t>(e - b), st);
+}
+
 // Plan by window size, chosen on the host from the row count (no environment reads inside numerical code): decode
 // windows of Q4_K experts take the persistent bulk-copy form, everything else the plain per-block form.
 // grouped_min_rows: 0 = the default threshold; windows of at least that many rows take the tensor-core form.
@@ -350,8 +358,7 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
 
     u32* row_status = v->row_status ? v->row_status : L.row_status;
     if (!routes_ready) {
-        cudaError_t ce = cudaMemsetAsync(L.summary, 0, 16, st);
-        if (ce == cudaSuccess && !v->row_status) ce = cudaMemsetAsync(L.row_status, 0, sizeof(u32) * v->rows, st);
+        const cudaError_t ce = clear_status(L, !v->row_status, v->rows, st);
         if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "layer: cudaMemsetAsync: %s", cudaGetErrorString(ce));
     }
 
@@ -437,8 +444,7 @@ int b200moe_ffn(const b200moe_ffn_view* v, void* stream) {
     b200moe_routes_view rv{};
     if (fused) {
         u32* row_status = v->row_status ? v->row_status : L.row_status;
-        cudaError_t ce = cudaMemsetAsync(L.summary, 0, 16, st);  // summary word, prologue ticket
-        if (ce == cudaSuccess && !v->row_status) ce = cudaMemsetAsync(L.row_status, 0, sizeof(u32) * v->rows, st);
+        const cudaError_t ce = clear_status(L, !v->row_status, v->rows, st);  // summary word, prologue ticket, row status
         if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "ffn: cudaMemsetAsync: %s", cudaGetErrorString(ce));
         rv.ids = r.ids; rv.rows = v->rows; rv.top_k = s.top_k; rv.experts = s.experts;
         rv.split = v->part_experts ? v->part_experts : s.experts / 2;
