@@ -82,9 +82,8 @@ def test_tp_shares():
     assert tp.tp_shares(1792, 2) == [(0, 1024), (1024, 768)]
 
 
-@pytest.mark.parametrize("case,form", [("ep_parts", 0), ("ep_fma", 1)])
-def test_expert_parallel_two_ranks_gloo(oracle, case, form):
-    world = 2
+@pytest.mark.parametrize("case,form,world", [("ep_parts", 0, 2), ("ep_fma", 1, 2), ("ep_parts", 0, 4)])
+def test_expert_parallel_ranks_gloo(oracle, case, form, world):
     ys = run_ranks(case, "gloo", world)
     want = ep_expected(oracle, form, world)
     got = np.concatenate(ys)
