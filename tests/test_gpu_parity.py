@@ -533,6 +533,59 @@ def test_ffn_config2_q4k(gpu, oracle):
     assert same(yh.numpy(), host(y))
 
 
+def test_ffn_config3_prefill_zipf(gpu, oracle):
+    """Config 3 at reduced size: a token block with bf16-rounded activations and a Zipf(1.1) logit bias (skewed expert
+    load, some experts empty) through the whole call: tiled router logits, chunked routes, grouped tensor-core experts,
+    slot-order merge. Ids bit-exact, outputs within tolerance (reported exact when they are)."""
+    import b200moe
+    from b200moe import ops, synth
+    rng = np.random.default_rng(3)
+    E, H, I, K, rows = 32, 512, 256, 4, 700
+    gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
+    rw = synth.router_weight(rng, E, H)
+    bias = synth.zipf_logit_bias(rng, E)
+    sh, osh = shape_pair(H, I, E, K, 12, 12)
+    ffn = ops.MoeFfn(sh, ops.softmax_policy(E, K), dv(gate, gpu), dv(up, gpu), dv(down, gpu), dv(rw, gpu), capacity=rows,
+                     combine_form=b200moe.COMBINE_FMA_SLOTS, logit_bias=dv(bias, gpu))
+    x = synth.bf16_round(synth.activations(rng, rows, H))
+    want = oracle.ffn(osh, O.softmax_policy(E, K), gate, up, down, rw, x, O.COMBINE_FMA_SLOTS, logit_bias=bias)
+    y, ids, wts = ffn(dv(x, gpu), want_routes=True)
+    assert np.array_equal(u32(ids), want["ids"]) and same(host(wts), want["weights"])
+    counts = np.bincount(want["ids"].reshape(-1), minlength=E)
+    assert max_rel(host(y), want["y"]) <= REL_TOL
+    print(f"config3-like: rows/expert max {counts.max()} min {counts.min()}; bit-exact={same(host(y), want['y'])}")
+
+
+def test_ffn_config4_group_limited_shared_expert(gpu, oracle):
+    """Config 4 at reduced size: sigmoid scores + selection bias, group-limited top-k (8 groups, best 4), Q4_K routed
+    experts folded in 8 expert ranges onto a dense Q8_0 shared expert: y = ((shared + S_0) + ...) + S_7. A decode window
+    and a token block. The group step is this build's extension: the oracle restates it (parity unpinned for it)."""
+    import b200moe
+    from b200moe import ops, synth
+    rng = np.random.default_rng(4)
+    E, H, I, K = 64, 512, 256, 8
+    gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
+    sg, su, sd = synth.expert_tensors(rng, 1, H, I, 8, 8)
+    rw = synth.router_weight(rng, E, H)
+    sbias = (rng.standard_normal(E) * 0.1).astype(np.float32)
+    sh, osh = shape_pair(H, I, E, K, 12, 12)
+    ssh, sosh = shape_pair(H, I, 1, 1, 8, 8)
+    pol, opol = ops.sigmoid_group_policy(E, K, 8, 4), O.sigmoid_group_policy(E, K, 8, 4)
+    for rows in (64, 200):
+        ffn = ops.MoeFfn(sh, pol, dv(gate, gpu), dv(up, gpu), dv(down, gpu), dv(rw, gpu), capacity=rows, combine_form=b200moe.COMBINE_PARTS,
+                         parts=8, select_bias=dv(sbias, gpu))
+        x = synth.bf16_round(synth.activations(rng, rows, H))
+        codes, deltas, sums = oracle.quantize_a8(x)
+        shared_want = oracle.experts(sosh, sg, su, sd, np.zeros((rows, 1), np.uint32), codes, deltas, sums)["raw"]
+        shared = ops.enqueue_dense_ffn(ssh, dv(sg, gpu), dv(su, gpu), dv(sd, gpu), ops.enqueue_quantize_a8(dv(x, gpu)))
+        assert same(host(shared), shared_want)   # the Q8_0 family is bit-exact
+        want = oracle.ffn(osh, opol, gate, up, down, rw, x, O.COMBINE_PARTS, parts=8, part_experts=E // 8, shared=shared_want, select_bias=sbias)
+        y, ids, wts = ffn(dv(x, gpu), shared=shared, want_routes=True)
+        assert np.array_equal(u32(ids), want["ids"]) and same(host(wts), want["weights"])
+        assert max_rel(host(y), want["y"]) <= REL_TOL
+        print(f"config4-like rows {rows}: bit-exact={same(host(y), want['y'])}")
+
+
 def test_layer_expert_parallel_fold(gpu, oracle):
     """Expert-parallel split on one device: each of `parts` virtual ranks owns a contiguous expert range, produces its
     partial sum (only_part), and the fixed-order fold equals the unsplit layer bit for bit (the reference's 2-rank
