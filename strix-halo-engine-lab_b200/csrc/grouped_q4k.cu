@@ -10,11 +10,15 @@
 //
 // Tile = (expert, 128 weight rows, 64 of the expert's tokens). gate/up: rows 0..63 are gate rows [64c, 64c + 64), rows
 // 64..127 the up rows of the same outputs, so SwiGLU + the A8 rule of h finish inside the tile. down: 128 rows of H.
-// A persistent CTA per SM walks tiles round-robin; three roles:
-//   * loader warps (4): per stage = half a super-block (4 groups): unpack the rows' nibbles to bytes into the MMA's
-//     canonical K-major layout (8-row x 16-byte core matrices), gather the tokens' A8 codes into the same layout, and
-//     stage the tokens' {E_g, S_g} and the rows' 16-byte block headers. Its first thread then issues the 4 MMAs
-//     (M 128, N 64, K 32, s8 x s8 -> s32) into one half of tensor memory and commits them to an mbarrier.
+// A persistent CTA per SM walks tiles round-robin; four roles:
+//   * issuer (1 warp, one thread): drives both asynchronous engines. The weight rows of a super-block arrive by two tiled
+//     TMA copies (cp.async.bulk.tensor.2d: 144 bytes x 64 rows, the tile's gate rows and up rows, or two halves of its
+//     down rows) into a raw ring, four super-blocks ahead of their use; the 4 MMAs of a stage (M 128, N 64, K 32,
+//     s8 x s8 -> s32) go into one half of tensor memory as soon as the stage's operands are published, and are
+//     committed to an mbarrier.
+//   * unpacker warps (4): per stage = half a super-block (4 groups): unpack the rows' nibbles (from the raw ring) to
+//     bytes into the MMA's canonical K-major layout (8-row x 16-byte core matrices), gather the tokens' A8 codes into
+//     the same layout (ordinary loads, one stage ahead), stage the tokens' {E_g, S_g} and the rows' 16-byte block headers.
 //   * drain warps (8): thread = (weight row = TMEM lane, 32 of the 64 tokens). tcgen05.ld brings 8 dots at a time;
 //     x_g = E_g * ((d * sc_g) * float(dot_g) - (dmin * m_g) * float(S_g)), pair sums, the four chains acc_p over
 //     ascending super-blocks, (a0 + a1) + (a2 + a3) at the end - exactly the decode kernels' order.
@@ -24,6 +28,8 @@
 //
 // Roofline: CUDA-core FP32 issue, not the tensor pipe and not HBM - about 8 instructions per (row, token, group),
 // against 1/32 of a tensor instruction. Weights are re-read from L2 once per token tile.
+#include <cuda.h>
+
 #include "declared_math.cuh"
 #include "kernels.cuh"
 
@@ -31,7 +37,8 @@ namespace b200moe {
 namespace {
 
 constexpr u32 kGM = 128, kGN = 64;           // tile: weight rows x tokens
-constexpr u32 kDrainWarps = 8, kLoadWarps = 4, kGThreads = (kDrainWarps + kLoadWarps) * 32;
+constexpr u32 kDrainWarps = 8, kLoadWarps = 4, kIssueWarps = 4;  // of the last group only warp 0 works (whole warp groups trade registers)
+constexpr u32 kGThreads = (kDrainWarps + kLoadWarps + kIssueWarps) * 32;
 constexpr u32 kStageGroups = 4;              // half a super-block per stage
 constexpr u32 kTPT = kGN / (kDrainWarps / 4);   // tokens per drain thread (16)
 constexpr u32 kTmemCols = 512;
@@ -39,7 +46,11 @@ constexpr u32 kABytes = kStageGroups * kGM * 32, kBBytes = kStageGroups * kGN * 
 constexpr u32 kStageBytes = kABytes + kBBytes + kEsBytes + kHdrBytes;  // 28672
 constexpr u32 kOutBytes = kGN * kGM * 4;     // epilogue tile (gate/up)
 constexpr u32 kMaxUnion = 1024;
-constexpr u32 kGroupedSmem = 120u * 1024u;   // above half an SM's shared memory: never two CTAs (and two TMEM allocations) per SM
+constexpr u32 kRawDepth = 4, kRawBlock = kGM * kQ4KBlock;  // ring of raw super-blocks (128 rows x 144 B) fed by bulk copies
+constexpr u32 kBarBytes = (6 + 2 * kRawDepth) * 8 + 16;  // full[2], empty[2], ready[2], raw_full[], raw_free[]
+// above half an SM's shared memory: never two CTAs (and two TMEM allocations) per SM
+constexpr u32 kGroupedSmem = 2 * kStageBytes + kOutBytes + (kMaxUnion + 2) * 4 + kBarBytes + kRawDepth * kRawBlock + 256;
+static_assert(kGroupedSmem > 114u * 1024u && kGroupedSmem <= 227u * 1024u, "one CTA per SM, within the shared memory of an SM");
 constexpr u32 kWaitLimit = 1u << 22;
 constexpr u32 kAbortBit = 1u << 30;
 // instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N = 64, M = 128
@@ -51,6 +62,16 @@ __device__ __forceinline__ void mbar_init(u64* bar, u32 count) {
 }
 __device__ __forceinline__ void mbar_arrive(u64* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(u64* bar, u32 bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
+}
+// One tiled TMA copy: a box of 144 bytes x 64 rows of a [rows][row_bytes] byte tensor into shared memory (rows end up
+// contiguous, 144 bytes each). x is a multiple of 16 bytes (a super-block boundary).
+__device__ __forceinline__ void tma_2d(void* dst, const CUtensorMap* map, u32 x, u32 y, u64* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(saddr(dst)),
+                 "l"(reinterpret_cast<u64>(map)), "r"(x), "r"(y), "r"(saddr(bar))
+                 : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(u64* bar, u32 parity) {
     u32 ok;
@@ -163,14 +184,16 @@ __device__ __forceinline__ Tile find_tile(const GroupedArgs& a, const u32* cum, 
 }
 
 template <bool kDown>
-__global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a) {
+__global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1,
+                                                                   GroupedArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* stage0 = smem;                                       // 2 x kStageBytes
     float* s_out = reinterpret_cast<float*>(smem + 2 * kStageBytes);    // [kGN][kGM]
     u32* cum = reinterpret_cast<u32*>(smem + 2 * kStageBytes + kOutBytes);  // [kMaxUnion + 1]
-    u64* bars = reinterpret_cast<u64*>(cum + kMaxUnion + 2);            // full[2], empty[2]
-    u32* s_tmem = reinterpret_cast<u32*>(bars + 4);
+    u64* bars = reinterpret_cast<u64*>(cum + kMaxUnion + 2);            // full[2], empty[2], ready[2], raw_full[], raw_free[]
+    u32* s_tmem = reinterpret_cast<u32*>(bars + 6 + 2 * kRawDepth);
     volatile u32* s_abort = s_tmem + 1;
+    unsigned char* raw = smem + ((2 * kStageBytes + kOutBytes + (kMaxUnion + 2) * 4 + kBarBytes + 127u) & ~127u);  // [kRawDepth][kRawBlock]
 
     if (kDown && a.summary && (*a.summary & ~kAbortBit)) return;  // a failed projection skips the stage (routed_expert.hpp:17-19)
 
@@ -181,6 +204,8 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
         cum[0] = 0;
         mbar_init(&bars[0], 1); mbar_init(&bars[1], 1);
         mbar_init(&bars[2], kDrainWarps * 32); mbar_init(&bars[3], kDrainWarps * 32);
+        mbar_init(&bars[4], kLoadWarps * 32); mbar_init(&bars[5], kLoadWarps * 32);
+        for (u32 i = 0; i < kRawDepth; ++i) { mbar_init(&bars[6 + i], 1); mbar_init(&bars[6 + kRawDepth + i], kLoadWarps * 32); }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -203,89 +228,151 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
     const u32 tmem = *s_tmem;
     const u32 n_tiles = cum[n_union] * a.n_row_tiles;
     const u32 K = a.K, I = a.shape.inter, H = a.shape.hidden;
-    const u32 nblocks = K / 256, row_bytes = nblocks * kQ4KBlock;
+    const u32 nblocks = K / 256;
     const u32 in_stride = a.in.stride ? a.in.stride : a.in.width, in_gs = in_stride / 32;
     u64* full = bars;
     u64* empty = bars + 2;
+    u64* ready = bars + 4;
+    u64* raw_full = bars + 6;
+    u64* raw_free = bars + 6 + kRawDepth;
     bool ok = true;
-    u32 n = 0;  // stage counter of this role (both roles count alike)
+    u32 n = 0;  // stage counter of this role (all roles count alike)
+    const u32 my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+    const u32 total_sb = my_tiles * nblocks;
+    // Register split between whole warp groups (the CTA holds 512 x 128): the drain threads - 128 accumulators each - take
+    // what the unpackers and the issuer group give up: 256 x 192 + 128 x 96 + 128 x 24 <= 512 x 128.
+    static_assert(kDrainWarps * 32 * 192 + kLoadWarps * 32 * 96 + kIssueWarps * 32 * 24 <= kGThreads * 128, "setmaxnreg split exceeds the register file share");
 
-    if (warp >= kDrainWarps) {
-        // ===================================================================================== loader + MMA issue
-        // Register split (the CTA holds 384 x 168): the loaders give registers up, the drain threads - 128 accumulators
-        // each - take them: 128 x 72 + 256 x 216 = 384 x 168.
-        static_assert(kLoadWarps * 32 * 72 + kDrainWarps * 32 * 216 <= kGThreads * 168, "setmaxnreg split exceeds the register file share");
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-        const u32 lt = tid - kDrainWarps * 32;            // 0..127 = weight row of the tile
-        for (u32 id = blockIdx.x; id < n_tiles; id += gridDim.x) {
-            const Tile t = find_tile(a, cum, n_union, id);
-            const u8* wrow;
-            if (kDown) wrow = a.w0 + (u64(t.expert) * H + kGM * t.c + lt) * row_bytes;
-            else wrow = (lt < 64 ? a.w0 : a.w1) + (u64(t.expert) * I + 64u * t.c + (lt & 63u)) * row_bytes;
-            // the token this thread gathers codes for (two threads per token), and the one it stages {E, S} for
-            const u32 tok_b = lt >> 1, half = lt & 1u, tok_e = lt & 63u, ge = lt >> 6;
-            const u32 ent_b = t.eb + min(tok_b, t.nt - 1), ent_e = t.eb + min(tok_e, t.nt - 1);
-            const u32 src_b = kDown ? a.routes.slots[ent_b] : a.routes.rows[ent_b];
-            const u32 src_e = kDown ? a.routes.slots[ent_e] : a.routes.rows[ent_e];
-            const i8* codes = a.in.codes + u64(src_b) * in_stride;
-            const float* deltas = a.in.deltas + u64(src_e) * in_gs;
-            const i32* sums = a.in.sums + u64(src_e) * in_gs;
-            for (u32 s = 0; s < 2 * nblocks; ++s, ++n) {
-                const u32 buf = n & 1u, use = n >> 1, b = s >> 1, hf = s & 1u;
-                // global loads first: they do not depend on the buffer
-                const uint4* wq = reinterpret_cast<const uint4*>(wrow + u64(b) * kQ4KBlock);
-                const uint4 hdr = __ldg(wq);
-                uint4 q[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) q[c] = __ldg(wq + 1 + 4 * hf + c);
-                const uint4* cq = reinterpret_cast<const uint4*>(codes + 32u * (8u * b + 4u * hf)) + 4 * half;
-                uint4 cc[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) cc[c] = __ldg(cq + c);
-                const u32 g0 = 8u * b + 4u * hf + 2u * ge;   // this thread stages pair ge of the stage for token tok_e
-                const float e0 = __ldg(deltas + g0), e1 = __ldg(deltas + g0 + 1);
-                const i32 s0 = __ldg(sums + g0), s1 = __ldg(sums + g0 + 1);
-                if (ok) ok = mbar_wait(&empty[buf], (use & 1u) ^ 1u, s_abort);  // the drain is done with this buffer
-                unsigned char* st = stage0 + buf * kStageBytes;
-                if (ok) {
-                    // A: row lt, chunk c = (pair pp, 16-byte half kc): low nibbles -> group 2pp, high nibbles -> group 2pp + 1
-                    const u32 core = (lt >> 3) * 256u + (lt & 7u) * 16u;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const u32 pp = c >> 1, kc = c & 1;
-                        uint4 lo, hi;
-                        lo.x = q[c].x & 0x0f0f0f0fu; lo.y = q[c].y & 0x0f0f0f0fu; lo.z = q[c].z & 0x0f0f0f0fu; lo.w = q[c].w & 0x0f0f0f0fu;
-                        hi.x = (q[c].x >> 4) & 0x0f0f0f0fu; hi.y = (q[c].y >> 4) & 0x0f0f0f0fu; hi.z = (q[c].z >> 4) & 0x0f0f0f0fu; hi.w = (q[c].w >> 4) & 0x0f0f0f0fu;
-                        *reinterpret_cast<uint4*>(st + (2 * pp) * (kGM * 32) + core + kc * 128u) = lo;
-                        *reinterpret_cast<uint4*>(st + (2 * pp + 1) * (kGM * 32) + core + kc * 128u) = hi;
-                    }
-                    // B: token tok_b, chunks 4 * half .. + 3 of the stage's 128 code bytes: chunk = (group gi, half kc)
-                    unsigned char* sb = st + kABytes + (tok_b >> 3) * 256u + (tok_b & 7u) * 16u;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const u32 ch = 4 * half + c, gi = ch >> 1, kc = ch & 1u;
-                        *reinterpret_cast<uint4*>(sb + gi * (kGN * 32) + kc * 128u) = cc[c];
-                    }
-                    reinterpret_cast<float4*>(st + kABytes + kBBytes)[ge * kGN + tok_e] =
-                        make_float4(e0, e1, static_cast<float>(s0), static_cast<float>(s1));
-                    reinterpret_cast<uint4*>(st + kABytes + kBBytes + kEsBytes)[lt] = hdr;
+    if (warp >= kDrainWarps + kLoadWarps) {
+        // ============================================================================ issuer: TMA copies + MMA issue
+        // One thread drives both asynchronous engines. The weight rows of super-block m of the CTA's sequence (tiles in
+        // order, blocks in order) arrive by two tiled TMA copies (144 bytes x 64 rows each: the gate rows and the up rows
+        // of the tile, or two halves of the down rows) into ring slot m % kRawDepth, kRawDepth super-blocks ahead of
+        // their use; the four MMAs of a stage are issued as soon as the unpackers have published its operands.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
+        if (warp == kDrainWarps + kLoadWarps) {
+            u32 ck = 0xffffffffu, cy = 0;
+            auto tma_block = [&](u32 mm) {  // lane 0 only
+                const u32 k = mm / nblocks, b = mm - k * nblocks;
+                if (k != ck) {
+                    ck = k;
+                    const Tile t = find_tile(a, cum, n_union, blockIdx.x + k * gridDim.x);
+                    cy = kDown ? t.expert * H + kGM * t.c : t.expert * I + 64u * t.c;
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> the tensor core's reads
-                asm volatile("bar.sync 2, %0;" ::"r"(kLoadWarps * 32) : "memory");
-                if (lt == 0 && ok && !*s_abort) {
-                    tc_fence_after();
-                    const u32 abase = saddr(st), bbase = abase + kABytes;
+                const u32 slot = mm % kRawDepth;
+                unsigned char* dst = raw + slot * kRawBlock;
+                mbar_expect_tx(&raw_full[slot], kRawBlock);
+                tma_2d(dst, &tm0, b * kQ4KBlock, cy, &raw_full[slot]);
+                tma_2d(dst + 64u * kQ4KBlock, kDown ? &tm0 : &tm1, b * kQ4KBlock, kDown ? cy + 64u : cy, &raw_full[slot]);
+            };
+            if (lane == 0) for (u32 mm = 0; mm < min(kRawDepth, total_sb); ++mm) tma_block(mm);
+            u32 m = 0;
+            for (u32 k = 0; k < my_tiles; ++k) {
+                for (u32 s = 0; s < 2 * nblocks; ++s, ++n) {
+                    const u32 buf = n & 1u, use = n >> 1, hf = s & 1u;
+                    if (ok) ok = mbar_wait(&ready[buf], use & 1u, s_abort);  // the stage's operands are in shared memory
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (ok && lane == 0) {
+                        tc_fence_after();
+                        const u32 abase = saddr(stage0 + buf * kStageBytes), bbase = abase + kABytes;
 #pragma unroll
-                    for (u32 gi = 0; gi < kStageGroups; ++gi)
-                        mma_i8(tmem + buf * (kStageGroups * kGN) + gi * kGN, smem_desc(abase + gi * (kGM * 32), 128, 256),
-                               smem_desc(bbase + gi * (kGN * 32), 128, 256));
-                    mma_commit(&full[buf]);
+                        for (u32 gi = 0; gi < kStageGroups; ++gi)
+                            mma_i8(tmem + buf * (kStageGroups * kGN) + gi * kGN, smem_desc(abase + gi * (kGM * 32), 128, 256),
+                                   smem_desc(bbase + gi * (kGN * 32), 128, 256));
+                        mma_commit(&full[buf]);
+                    }
+                    if (hf == 1) {
+                        if (m + kRawDepth < total_sb) {  // the slot has been read out: the block kRawDepth ahead takes it
+                            if (ok) ok = mbar_wait(&raw_free[m % kRawDepth], (m / kRawDepth) & 1u, s_abort);
+                            ok = __all_sync(0xffffffffu, ok);
+                            if (ok && lane == 0) tma_block(m + kRawDepth);
+                        }
+                        ++m;
+                    }
                 }
             }
+            if (!ok) for (u32 i = 0; i < 400; ++i) __nanosleep(100);  // an aborted launch: let the copies in flight land before the CTA retires
+        }
+    } else if (warp >= kDrainWarps) {
+        // ================================================================================================= unpackers
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        const u32 lt = tid - kDrainWarps * 32;            // 0..127 = weight row of the tile
+        // The tokens' bytes (A8 codes, deltas, sums) come by ordinary loads - L2 hits - one stage AHEAD: the registers
+        // filled here are stored in the next iteration, so their latency hides behind this stage's work.
+        const u32 tok_b = lt >> 1, half = lt & 1u, tok_e = lt & 63u, ge = lt >> 6;
+        struct Tok { uint4 cc[4]; float e0, e1; i32 s0, s1; };
+        u32 tk = 0xffffffffu;
+        const i8* t_codes = nullptr;
+        const float* t_deltas = nullptr;
+        const i32* t_sums = nullptr;
+        const u32 stages_per_tile = 2 * nblocks, total_stages = my_tiles * stages_per_tile;
+        auto load_tok = [&](u32 sn, Tok& r) {  // stage sn of the CTA's sequence
+            const u32 k = sn / stages_per_tile, s = sn - k * stages_per_tile, b = s >> 1, hf = s & 1u;
+            if (k != tk) {
+                tk = k;
+                const Tile t = find_tile(a, cum, n_union, blockIdx.x + k * gridDim.x);
+                // the token this thread gathers codes for (two threads per token), and the one it stages {E, S} for
+                const u32 ent_b = t.eb + min(tok_b, t.nt - 1), ent_e = t.eb + min(tok_e, t.nt - 1);
+                const u32 src_b = kDown ? a.routes.slots[ent_b] : a.routes.rows[ent_b];
+                const u32 src_e = kDown ? a.routes.slots[ent_e] : a.routes.rows[ent_e];
+                t_codes = a.in.codes + u64(src_b) * in_stride;
+                t_deltas = a.in.deltas + u64(src_e) * in_gs;
+                t_sums = a.in.sums + u64(src_e) * in_gs;
+            }
+            const uint4* cq = reinterpret_cast<const uint4*>(t_codes + 32u * (8u * b + 4u * hf)) + 4 * half;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) r.cc[c] = __ldg(cq + c);
+            const u32 g0 = 8u * b + 4u * hf + 2u * ge;   // this thread stages pair ge of the stage for token tok_e
+            r.e0 = __ldg(t_deltas + g0); r.e1 = __ldg(t_deltas + g0 + 1);
+            r.s0 = __ldg(t_sums + g0); r.s1 = __ldg(t_sums + g0 + 1);
+        };
+        Tok tok{};
+        if (total_stages) load_tok(0, tok);
+        u32 m = 0;  // super-block counter of the sequence
+        for (; n < total_stages; ++n) {
+            const u32 buf = n & 1u, use = n >> 1, hf = n & 1u;  // a tile has an even number of stages
+            const u32 rslot = m % kRawDepth;
+            const Tok cur = tok;
+            if (n + 1 < total_stages) load_tok(n + 1, tok);
+            if (ok && hf == 0) ok = mbar_wait(&raw_full[rslot], (m / kRawDepth) & 1u, s_abort);  // the super-block's rows have landed
+            if (ok) ok = mbar_wait(&empty[buf], (use & 1u) ^ 1u, s_abort);  // the drain is done with this buffer
+            unsigned char* st = stage0 + buf * kStageBytes;
+            if (ok) {
+                const uint4* wq = reinterpret_cast<const uint4*>(raw + rslot * kRawBlock + lt * kQ4KBlock);
+                const uint4 hdr = wq[0];
+                // A: row lt, chunk c = (pair pp, 16-byte half kc): low nibbles -> group 2pp, high nibbles -> group 2pp + 1
+                const u32 core = (lt >> 3) * 256u + (lt & 7u) * 16u;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const u32 pp = c >> 1, kc = c & 1;
+                    const uint4 q = wq[1 + 4 * hf + c];
+                    uint4 lo, hi;
+                    lo.x = q.x & 0x0f0f0f0fu; lo.y = q.y & 0x0f0f0f0fu; lo.z = q.z & 0x0f0f0f0fu; lo.w = q.w & 0x0f0f0f0fu;
+                    hi.x = (q.x >> 4) & 0x0f0f0f0fu; hi.y = (q.y >> 4) & 0x0f0f0f0fu; hi.z = (q.z >> 4) & 0x0f0f0f0fu; hi.w = (q.w >> 4) & 0x0f0f0f0fu;
+                    *reinterpret_cast<uint4*>(st + (2 * pp) * (kGM * 32) + core + kc * 128u) = lo;
+                    *reinterpret_cast<uint4*>(st + (2 * pp + 1) * (kGM * 32) + core + kc * 128u) = hi;
+                }
+                // B: token tok_b, chunks 4 * half .. + 3 of the stage's 128 code bytes: chunk = (group gi, half kc)
+                unsigned char* sb = st + kABytes + (tok_b >> 3) * 256u + (tok_b & 7u) * 16u;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const u32 ch = 4 * half + c, gi = ch >> 1, kc = ch & 1u;
+                    *reinterpret_cast<uint4*>(sb + gi * (kGN * 32) + kc * 128u) = cur.cc[c];
+                }
+                reinterpret_cast<float4*>(st + kABytes + kBBytes)[ge * kGN + tok_e] =
+                    make_float4(cur.e0, cur.e1, static_cast<float>(cur.s0), static_cast<float>(cur.s1));
+                reinterpret_cast<uint4*>(st + kABytes + kBBytes + kEsBytes)[lt] = hdr;
+                // generic-proxy accesses (the stores above, the reads of the raw slot) before the async proxy's:
+                // the tensor core reading the operands, the next TMA copy overwriting the slot
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&ready[buf]);
+                if (hf == 1) mbar_arrive(&raw_free[rslot]);
+            }
+            if (hf == 1) ++m;
         }
     } else {
         // ================================================================================================ drain
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
         const u32 quarter = warp & 3u, w = warp >> 2;   // TMEM lane quarter, token half
         const u32 o = 32u * quarter + lane;             // weight row of the tile = TMEM lane
         const u32 lane_addr = (32u * quarter) << 16;
@@ -389,6 +476,28 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(GroupedArgs a
     }
 }
 
+// Tensor map of a [rows][row_bytes] byte tensor with boxes of 144 bytes x 64 rows (no swizzle, no interleave). The
+// encoder is the driver's cuTensorMapEncodeTiled, looked up through the runtime (no link against the driver library).
+int encode_rows_map(const u8* base, u64 row_bytes, u64 rows, CUtensorMap* out) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q{};
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    if (!fn) return fail(B200MOE_ERR_CUDA, "grouped: cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};       // bytes between rows: a multiple of 16 (144 per super-block)
+    const cuuint32_t box[2] = {kQ4KBlock, 64};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<u8*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200MOE_ERR_CUDA, "grouped: cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+    return B200MOE_OK;
+}
+
 bool grouped_shape_ok(const b200moe_shape& s) {
     return s.gate_type == B200MOE_TYPE_Q4_K && s.down_type == B200MOE_TYPE_Q4_K && s.hidden % 256 == 0 && s.inter % 256 == 0 &&
            s.hidden % kGM == 0 && s.inter % 64 == 0 && s.experts <= kMaxUnion;
@@ -410,8 +519,12 @@ int launch_gate_up_q4k_grouped(const b200moe_gate_up_view& v, cudaStream_t strea
     a.shape = v.shape; a.routes = v.routes; a.w0 = v.weights.gate; a.w1 = v.weights.up; a.in = v.x; a.act = v.act;
     a.gate_out = v.gate_out; a.up_out = v.up_out; a.row_status = v.row_status; a.summary = v.summary;
     a.n_row_tiles = v.shape.inter / 64; a.K = v.shape.hidden;
+    CUtensorMap tm0, tm1;
+    const u64 rb = u64(v.shape.hidden / 256) * kQ4KBlock, rows = u64(v.shape.experts) * v.shape.inter;
+    if (int rc = encode_rows_map(v.weights.gate, rb, rows, &tm0)) return rc;
+    if (int rc = encode_rows_map(v.weights.up, rb, rows, &tm1)) return rc;
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_q4k_kernel<false>), kGroupedSmem)) return rc;
-    grouped_q4k_kernel<false><<<grid_size(), kGThreads, kGroupedSmem, stream>>>(a);
+    grouped_q4k_kernel<false><<<grid_size(), kGThreads, kGroupedSmem, stream>>>(tm0, tm1, a);
     return after_launch("gate_up_q4k_grouped");
 }
 
@@ -421,8 +534,10 @@ int launch_down_q4k_grouped(const b200moe_down_view& v, cudaStream_t stream) {
     a.shape = v.shape; a.routes = v.routes; a.w0 = v.weights.down; a.in = v.act; a.raw = v.raw;
     a.summary = const_cast<u32*>(v.summary);
     a.n_row_tiles = v.shape.hidden / kGM; a.K = v.shape.inter;
+    CUtensorMap tm0;
+    if (int rc = encode_rows_map(v.weights.down, u64(v.shape.inter / 256) * kQ4KBlock, u64(v.shape.experts) * v.shape.hidden, &tm0)) return rc;
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_q4k_kernel<true>), kGroupedSmem)) return rc;
-    grouped_q4k_kernel<true><<<grid_size(), kGThreads, kGroupedSmem, stream>>>(a);
+    grouped_q4k_kernel<true><<<grid_size(), kGThreads, kGroupedSmem, stream>>>(tm0, tm0, a);
     return after_launch("down_q4k_grouped");
 }
 
