@@ -19,7 +19,8 @@
 //   * unpacker warps (4): per stage = half a super-block (4 groups): unpack the rows' nibbles (from the raw ring) to
 //     bytes into the MMA's canonical K-major layout (8-row x 16-byte core matrices), gather the tokens' A8 codes into
 //     the same layout (ordinary loads, one stage ahead), stage the tokens' {E_g, S_g} and the rows' 16-byte block headers.
-//   * drain warps (8): thread = (weight row = TMEM lane, 32 of the 64 tokens). tcgen05.ld brings 8 dots at a time;
+//   * drain warps (8): thread = (weight row = TMEM lane, 32 of the 64 tokens: the 8-token chunks alternate between the
+//     two warp groups, so a tile with few tokens still uses every warp). tcgen05.ld brings 8 dots at a time;
 //     x_g = E_g * ((d * sc_g) * float(dot_g) - (dmin * m_g) * float(S_g)), pair sums, the four chains acc_p over
 //     ascending super-blocks, (a0 + a1) + (a2 + a3) at the end - exactly the decode kernels' order.
 //   * tensor memory: 512 columns = 2 buffers x 4 groups x 64 tokens; smem stages follow the same two buffers.
@@ -40,7 +41,8 @@ constexpr u32 kGM = 128, kGN = 64;           // tile: weight rows x tokens
 constexpr u32 kDrainWarps = 8, kLoadWarps = 4, kIssueWarps = 4;  // of the last group only warp 0 works (whole warp groups trade registers)
 constexpr u32 kGThreads = (kDrainWarps + kLoadWarps + kIssueWarps) * 32;
 constexpr u32 kStageGroups = 4;              // half a super-block per stage
-constexpr u32 kTPT = kGN / (kDrainWarps / 4);   // tokens per drain thread (16)
+constexpr u32 kTPT = kGN / (kDrainWarps / 4);   // tokens per drain thread (32)
+constexpr u32 kDrainGroups = kDrainWarps / 4;    // warp groups sharing a tile's tokens: the 8-token chunks alternate between them
 constexpr u32 kTmemCols = 512;
 constexpr u32 kABytes = kStageGroups * kGM * 32, kBBytes = kStageGroups * kGN * 32, kEsBytes = kStageGroups * kGN * 8, kHdrBytes = kGM * 16;
 constexpr u32 kStageBytes = kABytes + kBBytes + kEsBytes + kHdrBytes;  // 28672
@@ -393,20 +395,20 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(const __grid_
                     const unsigned char* st = stage0 + buf * kStageBytes;
                     const float4* es = reinterpret_cast<const float4*>(st + kABytes + kBBytes);  // [pair][token] {E_l, E_h, S_l, S_h}
                     const uint4 hdr = reinterpret_cast<const uint4*>(st + kABytes + kBBytes + kEsBytes)[o];
-                    const u32 tbase = tmem + lane_addr + buf * (kStageGroups * kGN) + kTPT * w;
+                    const u32 tbase = tmem + lane_addr + buf * (kStageGroups * kGN) + 8u * w;
 #pragma unroll
                     for (int pp = 0; pp < 2; ++pp) {
                         const Factors f = q4k_factors(hdr, 2 * hf + pp);
                         const float2 D = make_float2(f.Dl, f.Dh), DMn = make_float2(-f.DMl, -f.DMh);
 #pragma unroll
-                        for (int tq = 0; tq < (int)kTPT / 8; ++tq) {
-                            if (kTPT * w + 8u * tq >= t.nt) continue;  // no valid token in these 8 columns (warp-uniform)
+                        for (int tq = 0; tq < (int)kTPT / 8; ++tq) {  // chunk 2 * tq + w of the tile: a short tile still uses every warp
+                            if (8u * (kDrainGroups * tq + w) >= t.nt) continue;  // no valid token in these 8 columns (warp-uniform)
                             u32 dl[8], dh[8];
-                            tmem_ld8(tbase + (2 * pp) * kGN + 8 * tq, dl);
-                            tmem_ld8(tbase + (2 * pp + 1) * kGN + 8 * tq, dh);
+                            tmem_ld8(tbase + (2 * pp) * kGN + 8 * kDrainGroups * tq, dl);
+                            tmem_ld8(tbase + (2 * pp + 1) * kGN + 8 * kDrainGroups * tq, dh);
                             tmem_wait_ld();
                             tie8(dl); tie8(dh);
-                            const float4* e4 = es + pp * kGN + kTPT * w + 8 * tq;
+                            const float4* e4 = es + pp * kGN + 8u * (kDrainGroups * tq + w);
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
                                 const float4 e = e4[i];
@@ -427,7 +429,7 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(const __grid_
                 if (ok) {
 #pragma unroll
                     for (int i = 0; i < (int)kTPT; ++i) {
-                        const u32 tok = kTPT * w + i;
+                        const u32 tok = 8u * (kDrainGroups * (i >> 3) + w) + (i & 7);
                         if (tok < t.nt) {
                             const u32 slot = a.routes.slots[t.eb + tok];
                             a.raw[u64(slot) * H + kGM * t.c + o] = __fadd_rn(__fadd_rn(acc[i][0], acc[i][1]), __fadd_rn(acc[i][2], acc[i][3]));
@@ -438,7 +440,7 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(const __grid_
                 asm volatile("bar.sync 3, %0;" ::"r"(kDrainWarps * 32) : "memory");  // the previous tile's epilogue has read s_out
 #pragma unroll
                 for (int i = 0; i < (int)kTPT; ++i)
-                    s_out[(kTPT * w + i) * kGM + o] = __fadd_rn(__fadd_rn(acc[i][0], acc[i][1]), __fadd_rn(acc[i][2], acc[i][3]));
+                    s_out[(8u * (kDrainGroups * (i >> 3) + w) + (i & 7)) * kGM + o] = __fadd_rn(__fadd_rn(acc[i][0], acc[i][1]), __fadd_rn(acc[i][2], acc[i][3]));
                 asm volatile("bar.sync 3, %0;" ::"r"(kDrainWarps * 32) : "memory");
                 // SwiGLU + the A8 rule: one warp per (token, 32 outputs); the tile holds 2 groups of 32 per token
                 for (u32 task = warp; ok && task < 2 * t.nt; task += kDrainWarps) {
