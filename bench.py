@@ -345,18 +345,42 @@ def large_arm(args, cfg, rank, world, dev):
     for s in range(W):
         step(xs[s % NX])
     barrier()
+    # NX consecutive steps captured into one CUDA graph (kernels, NCCL collectives and peer stores alike): the replay
+    # removes the per-launch host cost that otherwise dominates a step this short. Eager launches if the capture fails.
+    graph, mode = None, "per-step launches"
+    if not args.no_graph and world == 1:  # (with NCCL collectives inside, the capture of this step stalled on 2 GPUs: ranks stay eager)
+        try:
+            cap = torch.cuda.Stream()
+            cap.wait_stream(torch.cuda.current_stream())
+            g = torch.cuda.CUDAGraph()
+            launches_before = b200moe.launch_count()
+            with torch.cuda.graph(g, stream=cap):
+                kept = [step(xs[s]) for s in range(NX)]
+            per_graph = b200moe.launch_count() - launches_before
+            graph, mode = g, f"CUDA graph replay of {NX} steps"
+            for _ in range(2):
+                graph.replay()
+        except Exception as e:  # noqa: BLE001 - any capture problem: measure the eager path and say so
+            graph, mode = None, f"per-step launches (graph capture failed: {type(e).__name__})"
+    barrier()
     launches0 = b200moe.launch_count()
     sampler = ClockSampler(dev.index)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for s in range(K):
-        step(xs[s % NX])
+    if graph is not None:
+        for _ in range(K // NX):
+            graph.replay()
+        for s in range(K % NX):
+            step(xs[s])
+    else:
+        for s in range(K):
+            step(xs[s % NX])
     e1.record()
     barrier()
     dev_ms = e0.elapsed_time(e1)
-    launches = b200moe.launch_count() - launches0
+    launches = (b200moe.launch_count() - launches0) + (per_graph * (K // NX) if graph is not None else 0)
     barrier()
     t0 = time.perf_counter()
     for s in range(K):
@@ -380,7 +404,7 @@ def large_arm(args, cfg, rank, world, dev):
         "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {B} per rank",
                    "parallelism": f"ep x{world} ({per} experts per rank)" if world > 1 else "1 gpu (all 256 experts)",
-                   "l2": "6.3 GB of routed expert weights per layer (far beyond L2)", "launch": "per-step launches" + ((" + NCCL all-gather dispatch, " + ("all-to-all return" if args.no_peer_return else "peer-store return (CUDA IPC) + 1-word all-reduce")) if world > 1 else "")},
+                   "l2": "6.3 GB of routed expert weights per layer (far beyond L2)", "launch": mode + ((" + NCCL all-gather dispatch, " + ("all-to-all return" if args.no_peer_return else "peer-store return (CUDA IPC) + 1-word all-reduce")) if world > 1 else "")},
         "clocks": sampler.summary(),
         "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
                 "ms_per_step": host_ms / K},
@@ -495,6 +519,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=4, help="distinct layers of weights rotated between steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="config 4 arm: launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-peer-return", action="store_true",
                     help="expert parallelism, PARTS form: return the partial sums with an NCCL all-to-all instead of the combine kernel's peer stores")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
