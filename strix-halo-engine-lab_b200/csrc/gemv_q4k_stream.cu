@@ -5,16 +5,18 @@
 //
 //  * One persistent CTA per SM walks a contiguous run of work items (expert, 32-output group | 64 hidden outputs); the
 //    runs are cut by estimated cost (entries per expert), not by count, so the CTAs finish together.
-//  * A producer warp streams weight rows - contiguous, 16-byte aligned GGUF bytes - into a ring of shared-memory stages
-//    with cp.async.bulk (global -> shared, completion counted on an mbarrier). A stage holds one OCTET = 8 weight rows;
-//    rows are laid down with a stride whose 16-byte count is odd, which makes the consumers' 128-bit reads conflict free.
+//  * Four producer warps stream weight rows - contiguous, 16-byte aligned GGUF bytes - into a ring of shared-memory
+//    stages with cp.async.bulk (global -> shared, completion counted on an mbarrier; eight lanes of a producer issue the
+//    eight row copies of its octet). A stage holds one OCTET = 8 weight rows, laid down with a stride whose 16-byte count
+//    is odd, which makes the consumers' 128-bit reads conflict free. The A8 rows the consumers read (x for gate/up, h of
+//    the run's entries for down) are staged in shared memory with cp.async.
 //  * Each consumer warp owns whole octets (octet n goes to warp n mod W): lane = (row of the octet, pair p). A lane walks
 //    its row's super-blocks in ascending order, so the serial chain acc_p += pair_p needs no shuffle at all; the final
 //    (a0 + a1) + (a2 + a3) is two xor-shuffles. Integer -> float conversions use the exact 2^23 magic-number form.
 //  * gate/up: the last warp to finish an item's eight octets (a shared-memory counter) runs SwiGLU + the A8 rule.
 //
 // Every wait on an mbarrier is bounded: after kWaitLimit polls the waiter raises an abort flag, all roles stop waiting
-// (they still walk their loops, doing no work), the producer drains the copies it has in flight (bounded), bit 30 of the
+// (they still walk their loops, doing no work), the producers drain the copies they have in flight (bounded), bit 30 of the
 // job summary is set and the kernel returns: the host reads a status, the GPU never hangs.
 //
 // Roofline: HBM. Algorithmic bytes per item = 64 rows x K / 256 x 144.
