@@ -305,7 +305,7 @@ __device__ __forceinline__ float tree4(float a) {
 // chunk-swapped and {E, E, S, S} packs in shared memory). acc[r] is the lane's chain acc_p of row r.
 template <int NR>
 __device__ __forceinline__ void row_gate_up(const uint4* blk, u32 nblocks, u32 p, u32 swz, u32 H, const unsigned char* const* xr, float* acc) {
-#pragma unroll(NR <= 2 ? 2 : 1)
+#pragma unroll(NR == 1 ? 4 : (NR == 2 ? 2 : 1))
     for (u32 b = 0; b < nblocks; ++b, blk += kQ4KBlock / 16) {
         const uint4 hdr = blk[0], q0 = blk[1 + 2 * p], q1 = blk[2 + 2 * p];
         const Factors f = q4k_factors(hdr, p);
