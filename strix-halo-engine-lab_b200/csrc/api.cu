@@ -65,6 +65,23 @@ int ensure_dynamic_smem(const void* kernel, u32 bytes) {
     return B200MOE_OK;
 }
 
+// The decode step alternates kernels that need almost all of an SM's shared memory with kernels that need little. Asking
+// for the largest shared-memory carve-out on the small ones too keeps the SMs' L1 / shared split the same from one
+// kernel of the step to the next (a change of the split has to wait for the SM to drain). Once per kernel and device.
+int prefer_max_shared(const void* kernel) {
+    static std::mutex m;
+    static std::map<std::pair<int, const void*>, bool> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(m);
+    bool& set = done[{dev, kernel}];
+    if (set) return B200MOE_OK;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, static_cast<int>(cudaSharedmemCarveoutMaxShared));
+    if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "cudaFuncSetAttribute(carve-out): %s", cudaGetErrorString(e));
+    set = true;
+    return B200MOE_OK;
+}
+
 namespace {
 
 constexpr u32 kMaxExperts = 1024, kMaxTopK = 32;

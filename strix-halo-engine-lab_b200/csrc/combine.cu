@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(256) row_order_kernel(const u32* ids, u32 rows
 
 int launch_combine(const b200moe_combine_view& v, cudaStream_t stream) {
     if (v.rows == 0) return B200MOE_OK;
+    if (int rc = prefer_max_shared(reinterpret_cast<const void*>(combine_kernel))) return rc;
     combine_kernel<<<dim3((v.hidden + 255) / 256, v.rows), 256, 0, stream>>>(v);
     return after_launch("combine");
 }

@@ -35,6 +35,8 @@ int after_launch(const char* what);
 bool device_ready();
 // Raises a kernel's dynamic shared memory limit when `bytes` needs more than it has been given so far (per device).
 int ensure_dynamic_smem(const void* kernel, u32 bytes);
+// Asks for the largest shared-memory carve-out for a kernel that itself needs little (see api.cu).
+int prefer_max_shared(const void* kernel);
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 inline bool aligned(const void* p, std::size_t a) { return (reinterpret_cast<std::uintptr_t>(p) % a) == 0; }

@@ -145,6 +145,7 @@ int launch_prologue(const b200moe_router_view& r, const b200moe_quantize_a8_view
 #define B200_PRO(RT)                                                                                            \
     {                                                                                                           \
         if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(prologue_decode_kernel<RT>), smem)) return rc; \
+        if (int rc = prefer_max_shared(reinterpret_cast<const void*>(prologue_decode_kernel<RT>))) return rc;       \
         prologue_decode_kernel<RT><<<grid, kWarps * 32, smem, stream>>>(a);                                     \
     }
     if (r.rows <= 2) B200_PRO(2)
