@@ -20,6 +20,7 @@ One JSON line on stdout (rank 0):
 import argparse
 import ctypes as C
 import json
+import math
 import os
 import sys
 import threading
@@ -44,10 +45,18 @@ CONFIGS["c3"] = dict(CONFIGS["c2"], desc="MoE prefill layer, Q4_K experts: hidde
 CONFIGS["c4"] = dict(hidden=7168, experts=256, top_k=8, inter=2048, gate_type=12, down_type=12, large=True,
                      desc="large routed MoE decode layer: hidden 7168, 256 Q4_K experts + 1 Q8_0 shared expert, inter 2048, "
                           "sigmoid + bias router, 8 groups / best 4 / top-8, bf16-rounded activations")
+CONFIGS["c5"] = dict(hidden=5120, experts=1, top_k=1, inter=17408, gate_type=12, down_type=12, dense=True,
+                     desc="dense SwiGLU FFN block, Q4_K: hidden 5120, inter 17408")
 METRIC = "MoE-layer tokens/s (Q4_K decode)"
 UNIT = "tokens/s"
 L2_BYTES = 126 * 2 ** 20
 NCU_TRAFFIC_RATIO = 1.00  # measured dram bytes / algorithmic bytes of the gate/up kernel (ncu, three launches: 0.999 - 1.002)
+
+
+def metric_of(cfg):
+    if cfg.get("dense"):
+        return "dense FFN block tokens/s (Q4_K decode)"
+    return METRIC if cfg["gate_type"] == 12 else "MoE-layer tokens/s (Q8_0 decode)"
 
 
 def peaks():
@@ -162,7 +171,7 @@ def reference_arm(args, cfg, rank, world):
     batch = cfg.get("batch", args.batch) if args.batch == 8 else args.batch
     total = max(1, args.steps + args.warmup)
     value, base = cpu_arm(cfg, batch, target_s=min(60.0, 0.02 * total + 15.0))
-    line = {"impl": "reference", "metric": METRIC if cfg["gate_type"] == 12 else "MoE-layer tokens/s (Q8_0 decode)", "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+    line = {"impl": "reference", "metric": metric_of(cfg), "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1000.0 * batch / value, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {batch}", "l2": "host arm"},
@@ -284,6 +293,122 @@ def prefill_arm(args, cfg, rank, world, dev):
         if world == 1 and not args.no_cpu_baseline:
             _, base = cpu_arm(cfg, 256, target_s=12.0)
             base["sample"] = "256 of the step's tokens: " + base["sample"]
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def dense_arm(args, cfg, rank, world, dev):
+    """Config 5: the dense Q4_K FFN block (hidden 5120, inter 17408), `--batch` rows (1..8). One GPU holds the whole
+    block; N GPUs run tensor parallelism (b200moe.tp): whole-super-block shares of inter per rank, every rank sees the
+    same rows, the partial sums are all-gathered and folded in rank order. A step = A8 of x + gate/up + SwiGLU + A8 of h +
+    down (+ all-gather + fold). Enough distinct layers are rotated that one rotation exceeds twice the L2."""
+    import torch
+    import torch.distributed as dist
+    import b200moe
+    from b200moe import ops, synth, tp
+
+    K, W = args.steps if args.steps != 2000 else 400, max(min(args.warmup, 50), 3)
+    B = args.batch
+    H, I = cfg["hidden"], cfg["inter"]
+    start, size = tp.tp_shares(I, world)[rank]
+    shape = ops.make_shape(H, size, 1, 1, 12, 12)
+    rank_bytes = 3 * (size // 256) * 144 * H                     # gate + up rows of the share, down K-share of every row
+    layers = max(2, min(32, -(-2 * L2_BYTES // rank_bytes) + 1))
+    kernels = []
+    for layer in range(layers):
+        gate, up, down = synth.expert_tensors(np.random.default_rng(900 + layer), 1, H, I, 12, 12)
+        g2, u2, d3 = gate.reshape(I, -1), up.reshape(I, -1), down.reshape(H, I // 256, 144)
+        share = (np.ascontiguousarray(g2[start:start + size]).reshape(-1), np.ascontiguousarray(u2[start:start + size]).reshape(-1),
+                 np.ascontiguousarray(d3[:, start // 256:(start + size) // 256]).reshape(-1))
+        kernels.append(tp.DeviceDenseKernels(shape, *(torch.from_numpy(a).to(dev) for a in share)))
+        del gate, up, down, share
+    ffns = [tp.TpDenseFfn(k) for k in kernels] if world > 1 else None
+    rng = np.random.default_rng(7)                            # the same rows on every rank (x is replicated under TP)
+    NX = 4
+    xs_host = [torch.from_numpy(synth.activations(rng, B, H)).pin_memory() for _ in range(NX)]
+    xs = [x.to(dev) for x in xs_host]
+    ys_host = torch.empty((B, H), dtype=torch.float32).pin_memory()
+
+    def step(s, x):
+        return ffns[s % layers](x) if world > 1 else kernels[s % layers].partial(x)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for s in range(W):
+        step(s, xs[s % NX])
+    barrier()
+    graph, mode, G = None, "per-step launches", layers * NX // math.gcd(layers, NX)
+    if not args.no_graph and world == 1:
+        try:
+            cap = torch.cuda.Stream()
+            cap.wait_stream(torch.cuda.current_stream())
+            g = torch.cuda.CUDAGraph()
+            launches_before = b200moe.launch_count()
+            with torch.cuda.graph(g, stream=cap):
+                kept = [step(s, xs[s % NX]) for s in range(G)]
+            per_graph = b200moe.launch_count() - launches_before
+            graph, mode = g, f"CUDA graph replay of {G} steps"
+            for _ in range(2):
+                graph.replay()
+        except Exception as e:  # noqa: BLE001 - any capture problem: measure the eager path and say so
+            graph, mode = None, f"per-step launches (graph capture failed: {type(e).__name__})"
+    barrier()
+    launches0 = b200moe.launch_count()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    if graph is not None:
+        for _ in range(K // G):
+            graph.replay()
+        for s in range(K % G):
+            step(s, xs[s % NX])
+    else:
+        for s in range(K):
+            step(s, xs[s % NX])
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    launches = (b200moe.launch_count() - launches0) + (per_graph * (K // G) if graph is not None else 0)
+    t0 = time.perf_counter()
+    for s in range(K):
+        ys_host.copy_(step(s, xs_host[s % NX].to(dev, non_blocking=True)), non_blocking=True)
+    barrier()
+    host_ms = 1000.0 * (time.perf_counter() - t0)
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    t = torch.tensor([dev_ms, host_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, host_ms = (float(v) for v in t.cpu())
+    tokens = B * K                                            # TP: every rank works on the same rows (strong scaling)
+    peak, peak_kind = peaks()
+    achieved = rank_bytes / (dev_ms / K * 1e-3) / 1e9
+    line = {
+        "metric": metric_of(cfg), "value": tokens / (dev_ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {B}",
+                   "parallelism": f"tp x{world} (inter share {size} of {I} on rank 0)" if world > 1 else "1 gpu",
+                   "l2": f"{layers} distinct layers rotated ({layers * rank_bytes / 2 ** 20:.0f} MB per rank per rotation, L2 is 126 MB)",
+                   "launch": mode + (" + NCCL all-gather of the partial sums + rank-ordered fold" if world > 1 else "")},
+        "clocks": sampler.summary(),
+        "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
+                "ms_per_step": host_ms / K},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "whole step (the rank's gate + up + down bytes / step time)", "bound": "hbm", "achieved": achieved,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy", "traffic": None,
+                     "algorithmic_bytes_per_step": rank_bytes},
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            _, base = cpu_arm(cfg, B, target_s=10.0)
             line["cpu_baseline"] = base
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -543,6 +668,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     if cfg.get("prefill"):
         return prefill_arm(args, cfg, rank, world, dev)
+    if cfg.get("dense"):
+        return dense_arm(args, cfg, rank, world, dev)
     if cfg.get("large"):
         return large_arm(args, cfg, rank, world, dev)
     if world > 1 and args.parallelism == "ep":

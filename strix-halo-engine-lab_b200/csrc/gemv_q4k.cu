@@ -194,9 +194,10 @@ __global__ void __launch_bounds__(256) gate_up_q4k_kernel(b200moe_gate_up_view v
     }
 }
 
-// grid (hidden / 64, max_union); 256 threads: 64 down rows per CTA, Q4_K rows over K = inter.
+// grid (hidden / rows_per_cta, max_union); 256 threads: rows_per_cta (64, or fewer when that grid would leave SMs idle:
+// the dense block has one "expert") down rows per CTA, Q4_K rows over K = inter.
 template <int LPR>
-__global__ void __launch_bounds__(256) down_q4k_kernel(b200moe_down_view v) {
+__global__ void __launch_bounds__(256) down_q4k_kernel(b200moe_down_view v, u32 rows_per_cta) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     if (v.summary && *v.summary) return;  // a failed projection skips the whole down stage (routed_expert.hpp:17-19)
     const u32 j = blockIdx.y;
@@ -211,7 +212,7 @@ __global__ void __launch_bounds__(256) down_q4k_kernel(b200moe_down_view v) {
     constexpr u32 RPW = 32 / LPR;
     const u32 sub = lane / LPR, li = lane % LPR, base = sub * LPR;
     const u64 row_bytes = u64(nblocks) * kQ4KBlock;
-    const u32 o0 = 64u * blockIdx.x;
+    const u32 o0 = rows_per_cta * blockIdx.x;
     const u8* down = v.weights.down + (u64(expert) * H + o0) * row_bytes;
     const A8Smem xs{s_codes, s_deltas, s_sums, I};
 
@@ -222,7 +223,7 @@ __global__ void __launch_bounds__(256) down_q4k_kernel(b200moe_down_view v) {
         __syncthreads();
         stage_a8(v.act, s_slots, nr, I, s_codes, s_deltas, s_sums);
         __syncthreads();
-        for (u32 t0 = warp * RPW; t0 < 64; t0 += 8 * RPW) {
+        for (u32 t0 = warp * RPW; t0 < rows_per_cta; t0 += 8 * RPW) {
             const u32 t = t0 + sub;
             float val[kR];
             q4k_row<LPR>(down + u64(t) * row_bytes, nblocks, xs, nr, li, base, val);
@@ -341,11 +342,13 @@ int launch_down_q4k(const b200moe_down_view& v, cudaStream_t stream) {
     const u32 H = v.shape.hidden, I = v.shape.inter;
     if (v.max_union == 0) return B200MOE_OK;
     const u32 smem = kR * (I + I / 32 * 8);
-    const dim3 grid(H / 64, v.max_union);
+    u32 rpc = 64;  // rows per CTA: halved while the grid would not give every SM two CTAs (H is a multiple of 256)
+    while (rpc > 8 && u64(H / rpc) * v.max_union < 2u * 148u) rpc /= 2;
+    const dim3 grid(H / rpc, v.max_union);
 #define B200_DN(L)                                                     \
     {                                                                  \
         if (int rc = set_smem(down_q4k_kernel<L>, smem)) return rc;    \
-        down_q4k_kernel<L><<<grid, 256, smem, stream>>>(v);            \
+        down_q4k_kernel<L><<<grid, 256, smem, stream>>>(v, rpc);       \
     }
     switch (lanes_per_row(I / 256)) {
         case 32: B200_DN(32) break;
