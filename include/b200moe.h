@@ -83,6 +83,26 @@ typedef struct b200moe_quantize_a8_view {
 } b200moe_quantize_a8_view;
 int b200moe_quantize_a8(const b200moe_quantize_a8_view* view, void* stream);
 
+/* ------------------------------------------------------------------------------------------- RMSNorm (+ A8) before the FFN
+ * The step in front of the FFN in a layer, fused with the A8 quantiser the router / experts read:
+ *   y[r][i] = (x[r][i] * s_r) * weight[i]   (weight NULL: x * s_r),   s_r = 1 / sqrt(sumsq_r / n + eps),
+ * sumsq_r in the host rule's order: L = 256 lanes (128 when n < 512), lane l = fma(x[i], x[i], .) over i = l, l + L, ...
+ * from +0, then the halving tree lane[l] += lane[l + h], h = L/2 .. 1. Bitwise strix::cpu::Kernels::rmsnorm_f32
+ * (src/cpu/core/backend.hpp:71-72; src/cpu/core/reference.cpp:86-103), which it replaces together with the norm + A8
+ * outputs of strix::ds41::cuda::enqueue_norm(NormView) (include/strix/cuda/ds41_core.hpp:86-100).
+ * out (optional, may alias x) gets y; a8 (optional: a8.codes NULL = none) gets quantize_a8(y). n a multiple of 32. */
+typedef struct b200moe_rmsnorm_view {
+    const float* x;
+    uint32_t rows, n, x_stride; /* x_stride in elements, 0 = n */
+    const float* weight;        /* [n] or NULL */
+    float eps;
+    float* out;                 /* optional [rows][out_stride] */
+    uint32_t out_stride;        /* 0 = n */
+    b200moe_a8_rows a8;         /* optional */
+    uint32_t* status;           /* optional [rows]: |= NONFINITE_ACTIVATION for a row whose y holds a NaN / Inf */
+} b200moe_rmsnorm_view;
+int b200moe_rmsnorm_a8(const b200moe_rmsnorm_view* view, void* stream);
+
 /* ------------------------------------------------------------------------------------------------ Q8_0 x A8 GEMV
  * out[r * out_stride + o] = product_q8_0(weight row (first + o), A8 row r) for o in [0, count): per 32-weight group
  * float(int32 dot) * (scale * delta); group g into lane class g % 32, classes accumulated ascending from +0, combined

@@ -105,6 +105,14 @@ class Oracle:
             raise ValueError("A8 width must be a multiple of 32")
         return codes, deltas, sums
 
+    def rmsnorm(self, x, w=None, eps=1e-6):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, n = x.shape
+        y = np.zeros_like(x)
+        wp = _p(np.ascontiguousarray(w, dtype=np.float32), f32p) if w is not None else None
+        self.lib.orc_rmsnorm_f32(_p(x, f32p), wp, n, C.c_float(eps), _p(y, f32p), rows)
+        return y
+
     def gemv_q8_0_a8(self, weight, width, codes, deltas, out=None, accumulate=False):
         weight = np.ascontiguousarray(weight, dtype=np.uint8)
         count, row_bytes = weight.shape
@@ -256,6 +264,14 @@ class Ref:
         L.ref_cpu_isa.restype = C.c_char_p
         L.ref_expert_isa.restype = C.c_char_p
         L.ref_time_layer_q4k.restype = C.c_double
+
+    def rmsnorm(self, x, w=None, eps=1e-6):
+        x = np.ascontiguousarray(x, np.float32)
+        rows, n = x.shape
+        y = np.zeros_like(x)
+        wp = _p(np.ascontiguousarray(w, np.float32), f32p) if w is not None else None
+        self.lib.ref_rmsnorm_f32(_p(x, f32p), wp, n, C.c_float(eps), _p(y, f32p), rows)
+        return y
 
     def quantize_a8(self, x, ds41=False):
         x = np.ascontiguousarray(x, np.float32)

@@ -281,6 +281,28 @@ int orc_quantize_a8(const float* x, u32 rows, u32 width, u32 x_stride, i8* codes
     return 0;
 }
 
+// RMSNorm of the CPU backend (src/cpu/core/reference.cpp:86-103; lane count src/cpu/core/backend.hpp:91): L = 256 lanes
+// (128 below n = 512), lane l = fma(x[i], x[i], .) over i = l, l + L, ..., halving tree, r = 1 / sqrt(sum / n + eps),
+// y = (x * r) * w or x * r. y may alias x.
+int orc_rmsnorm_f32(const float* x, const float* w, u32 n, float eps, float* y, u32 rows) {
+    const u32 lanes = n >= 512 ? 256u : 128u;
+    float partial[256];
+    for (u32 row = 0; row < rows; ++row) {
+        const float* xr = x + (size_t)row * n;
+        float* yr = y + (size_t)row * n;
+        for (u32 lane = 0; lane < lanes; ++lane) {
+            float a = 0.0f;
+            for (u32 i = lane; i < n; i += lanes) a = std::fma(xr[i], xr[i], a);
+            partial[lane] = a;
+        }
+        for (u32 h = lanes / 2; h > 0; h >>= 1)
+            for (u32 lane = 0; lane < h; ++lane) partial[lane] = partial[lane] + partial[lane + h];
+        const float r = 1.0f / std::sqrt(partial[0] / (float)n + eps);
+        for (u32 i = 0; i < n; ++i) yr[i] = w ? (xr[i] * r) * w[i] : xr[i] * r;
+    }
+    return 0;
+}
+
 // Q8_0 x A8 GEMV (src/cpu/core/reference.cpp:57-84).
 int orc_gemv_q8_0_a8(const u8* weight, u32 row_bytes, u32 width, u32 count, u32 rows, const i8* codes, const float* deltas,
                      u32 x_stride, float* out, u32 out_stride, u32 accumulate) {

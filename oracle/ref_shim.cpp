@@ -110,6 +110,10 @@ int ref_gemv_q8_0_a8(const u8* weight, u32 row_bytes, u32 in, u32 count, u32 row
     return 0;
 }
 // strix::ds41 host references (src/ds41_formats.cpp).
+void ref_rmsnorm_f32(const float* x, const float* w, u32 n, float eps, float* y, u32 rows) {
+    strix::cpu::reference_kernels().rmsnorm_f32(x, w, n, eps, y, rows, strix::cpu::Stream{});
+}
+
 void ref_ds41_quantize_a8(const float* x, std::size_t width, i8* codes, float* deltas, i32* sums) {
     const auto a = strix::ds41::quantize_a8(std::span<const float>(x, width));
     std::memcpy(codes, a.codes.data(), width);

@@ -40,6 +40,11 @@ class QuantizeA8View(C.Structure):
     _fields_ = [("x", vp), ("rows", u32), ("width", u32), ("x_stride", u32), ("x_is_bf16", u32), ("out", A8Rows), ("status", vp)]
 
 
+class RmsnormView(C.Structure):
+    _fields_ = [("x", vp), ("rows", u32), ("n", u32), ("x_stride", u32), ("weight", vp), ("eps", C.c_float), ("out", vp),
+                ("out_stride", u32), ("a8", A8Rows), ("status", vp)]
+
+
 class Q8A8View(C.Structure):
     _fields_ = [("weight", vp), ("row_bytes", u32), ("width", u32), ("first", u32), ("count", u32), ("x", A8Rows), ("out", vp),
                 ("out_stride", u32), ("accumulate", u32)]
@@ -120,7 +125,7 @@ class GgufMoeLayer(C.Structure):
 
 
 # every symbol include/b200moe.h declares (tests check that the library exports each of them)
-EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_quantize_a8", "b200moe_q8_0_a8",
+EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_quantize_a8", "b200moe_rmsnorm_a8", "b200moe_q8_0_a8",
            "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_routes_static_max_words",
            "b200moe_build_routes_static", "b200moe_gate_row_bytes",
            "b200moe_down_row_bytes", "b200moe_expert_bytes", "b200moe_gate_up", "b200moe_down", "b200moe_combine",
@@ -152,7 +157,7 @@ def lib():
         for n in ("b200moe_layer_workspace_bytes", "b200moe_ffn_workspace_bytes"):
             getattr(L, n).restype = u64
             getattr(L, n).argtypes = [C.POINTER(Shape), u32]
-        for n, t in (("b200moe_quantize_a8", QuantizeA8View), ("b200moe_q8_0_a8", Q8A8View), ("b200moe_router", RouterView),
+        for n, t in (("b200moe_quantize_a8", QuantizeA8View), ("b200moe_rmsnorm_a8", RmsnormView), ("b200moe_q8_0_a8", Q8A8View), ("b200moe_router", RouterView),
                      ("b200moe_build_routes", RoutesView), ("b200moe_build_routes_static", RoutesView),
                      ("b200moe_gate_up", GateUpView), ("b200moe_down", DownView),
                      ("b200moe_combine", CombineView), ("b200moe_layer", LayerView), ("b200moe_ffn", FfnView),

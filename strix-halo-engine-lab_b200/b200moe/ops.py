@@ -31,6 +31,22 @@ def enqueue_quantize_a8(x, status=None, stride=0):
     return codes, deltas, sums
 
 
+def enqueue_rmsnorm_a8(x, weight=None, eps=1e-6, want_out=True, want_a8=True, status=None):
+    """x [rows][n] float32 -> (y float32 or None, (codes, deltas, sums) or None): RMSNorm and the A8 of its output in one launch."""
+    from . import RmsnormView
+    rows, n = x.shape
+    y = torch.empty((rows, n), dtype=torch.float32, device=x.device) if want_out else None
+    a8, rows_view = None, A8Rows()
+    if want_a8:
+        codes = torch.empty((rows, n), dtype=torch.int8, device=x.device)
+        deltas = torch.empty((rows, max(n // 32, 1)), dtype=torch.float32, device=x.device)
+        sums = torch.empty_like(deltas, dtype=torch.int32)
+        a8, rows_view = (codes, deltas, sums), A8Rows(ptr(codes), ptr(deltas), ptr(sums), rows, n, n)
+    v = RmsnormView(ptr(x), rows, n, x.stride(0), ptr(weight), eps, ptr(y), 0, rows_view, ptr(status))
+    check(lib().b200moe_rmsnorm_a8(C.byref(v), stream_ptr()))
+    return y, a8
+
+
 def enqueue_q8_0_a8(weight, width, codes, deltas, out=None, accumulate=False, first=0, count=None):
     """weight uint8 [n][row_bytes] Q8_0 rows; A8 rows (codes, deltas) -> out [rows][count]."""
     n, row_bytes = weight.shape

@@ -255,6 +255,23 @@ int b200moe_quantize_a8(const b200moe_quantize_a8_view* v, void* stream) {
     return launch_quantize_a8(*v, as_stream(stream));
 }
 
+int b200moe_rmsnorm_a8(const b200moe_rmsnorm_view* v, void* stream) {
+    B200_REQUIRE(v, "null view");
+    B200_REQUIRE(v->n % 32 == 0, "rmsnorm: n must be a multiple of 32 (got %u)", v->n);
+    if (v->rows == 0 || v->n == 0) return B200MOE_OK;
+    B200_REQUIRE(v->x, "rmsnorm: x is null");
+    B200_REQUIRE(v->out || v->a8.codes, "rmsnorm: neither out nor a8 is given");
+    const u32 xs = v->x_stride ? v->x_stride : v->n, os = v->out_stride ? v->out_stride : v->n;
+    B200_REQUIRE(xs >= v->n && os >= v->n, "rmsnorm: a stride is below n = %u", v->n);
+    if (v->a8.codes) {
+        const u32 stride = v->a8.stride ? v->a8.stride : v->a8.width;
+        B200_REQUIRE(v->a8.deltas, "rmsnorm: a8.deltas is null");
+        B200_REQUIRE(v->a8.width == v->n && stride >= v->n && stride % 32 == 0 && v->a8.rows >= v->rows, "rmsnorm: a8 view does not fit rows %u x n %u", v->rows, v->n);
+    }
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    return launch_rmsnorm_a8(*v, as_stream(stream));
+}
+
 int b200moe_q8_0_a8(const b200moe_q8a8_view* v, void* stream) {
     B200_REQUIRE(v, "null view");
     B200_REQUIRE(v->width % 32 == 0, "Q8_0 product width must be a multiple of 32 (got %u)", v->width);

@@ -7,6 +7,7 @@ namespace b200moe {
 
 // a8.cu
 int launch_quantize_a8(const b200moe_quantize_a8_view& v, cudaStream_t stream);
+int launch_rmsnorm_a8(const b200moe_rmsnorm_view& v, cudaStream_t stream);
 
 // router.cu
 // fused_quantize (optional): the A8 quantiser of the same activations is enqueued first

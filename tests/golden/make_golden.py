@@ -3,6 +3,7 @@ the reference checkout by oracle/Makefile). Run where the reference checkout exi
 
     make -C oracle && python tests/golden/make_golden.py
 
+norm_golden.npz (the RMSNorm in front of the FFN) is written by the same run; `--norm-only` writes just that file.
 The vectors are small seeded cases of every contract on the path; tests/test_oracle_pins.py::test_golden_vectors
 replays them against the restated oracle wherever the reference itself is absent (e.g. on the GPU box).
 """
@@ -79,5 +80,23 @@ def main():
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def norm_vectors():
+    """tests/golden/norm_golden.npz: RMSNorm of the CPU backend (rmsnorm_f32) on small seeded rows, both lane counts."""
+    ref = Ref()
+    rng = np.random.default_rng(20251)
+    out = {}
+    for n in (96, 512, 2048):
+        x = (rng.standard_normal((3, n)) * 3.0).astype(np.float32)
+        w = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        out[f"x_{n}"], out[f"w_{n}"] = x, w
+        out[f"y_{n}"] = ref.rmsnorm(x, w, 1e-6)
+        out[f"y_unscaled_{n}"] = ref.rmsnorm(x, None, 1e-6)
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "norm_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
-    main()
+    if "--norm-only" not in sys.argv:
+        main()
+    norm_vectors()

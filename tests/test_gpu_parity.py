@@ -106,6 +106,40 @@ def test_quantize_a8_padding_and_rejection(gpu, oracle):
         assert np.array_equal(host(codes), before)
 
 
+def test_rmsnorm_a8(gpu, oracle):
+    """RMSNorm + the A8 of its output in one launch, bit for bit the host rule (both lane counts, with / without the
+    weight, in place, A8 only); a partial group is rejected; a non-finite row is flagged."""
+    import b200moe
+    from b200moe import ops
+    rng = np.random.default_rng(12)
+    for rows, n in ((1, 32), (3, 480), (8, 2048), (5, 7168)):
+        x = (rng.standard_normal((rows, n)) * 3.0).astype(np.float32)
+        w = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        for ww in (w, None):
+            want = oracle.rmsnorm(x, ww, 1e-6)
+            wc, wd, ws = oracle.quantize_a8(want)
+            y, (c, d, sm) = ops.enqueue_rmsnorm_a8(dv(x, gpu), dv(ww, gpu) if ww is not None else None, 1e-6)
+            assert same(host(y), want)
+            assert np.array_equal(host(c), wc) and same(host(d), wd) and np.array_equal(host(sm), ws)
+            y2, a8 = ops.enqueue_rmsnorm_a8(dv(x, gpu), dv(ww, gpu) if ww is not None else None, 1e-6, want_out=False)
+            assert y2 is None and np.array_equal(host(a8[0]), wc)
+    # in place
+    xs = dv(x, gpu)
+    v = b200moe.RmsnormView(xs.data_ptr(), rows, n, n, None, 1e-6, xs.data_ptr(), 0, b200moe.A8Rows(), None)
+    b200moe.check(b200moe.lib().b200moe_rmsnorm_a8(v, b200moe.stream_ptr()))
+    assert same(host(xs), oracle.rmsnorm(x, None, 1e-6))
+    # rejection and status
+    v = b200moe.RmsnormView(xs.data_ptr(), 1, 33, 64, None, 1e-6, xs.data_ptr(), 0, b200moe.A8Rows(), None)
+    with pytest.raises(b200moe.InvalidArgument):
+        b200moe.check(b200moe.lib().b200moe_rmsnorm_a8(v, b200moe.stream_ptr()))
+    bad = x.copy()
+    bad[1, 7] = np.inf
+    status = torch.zeros(rows, dtype=torch.int32, device=gpu)
+    ops.enqueue_rmsnorm_a8(dv(bad, gpu), None, 1e-6, status=status)
+    st = host(status)
+    assert st[1] == 2 and st[0] == 0
+
+
 # ---------------------------------------------------------------------------------------------------------- Q8_0 GEMV
 def test_q8_0_a8_dense(gpu, oracle):
     from b200moe import ops, synth

@@ -388,3 +388,22 @@ def test_golden_vectors(oracle):
     codes, deltas, sums = oracle.quantize_a8(g["qw_x"])
     ex = oracle.experts(sh, g["qw_gate"], g["qw_up"], g["qw_down"], g["qw_ids"], codes, deltas, sums)
     assert same(ex["raw"], g["qw_raw"])
+
+
+# ---- RMSNorm in front of the FFN (src/cpu/core/reference.cpp:86-103) ---------------------------------------------
+def test_rmsnorm_golden_vectors(oracle):
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "norm_golden.npz"))
+    for n in (96, 512, 2048):
+        assert same(oracle.rmsnorm(g[f"x_{n}"], g[f"w_{n}"], 1e-6), g[f"y_{n}"])
+        assert same(oracle.rmsnorm(g[f"x_{n}"], None, 1e-6), g[f"y_unscaled_{n}"])
+
+
+def test_rmsnorm_against_reference(oracle, ref):
+    """Both lane counts (128 below n = 512, 256 from there), with and without the weight, as the reference's own
+    test_norm does (tests/cpu_backend_host_tests.cpp:220-239)."""
+    rng = np.random.default_rng(77)
+    for n in (32, 480, 512, 1024, 7168):
+        x = (rng.standard_normal((4, n)) * 3.0).astype(np.float32)
+        w = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        for ww in (w, None):
+            assert same(oracle.rmsnorm(x, ww, 1e-6), ref.rmsnorm(x, ww, 1e-6))
