@@ -101,17 +101,29 @@ inline void q4k_factors(const u8* blk, unsigned j, unsigned* sc, unsigned* mn) {
 }
 
 // ---- Q4_K x A8 row, Qwen A8 contract (src/cpu/core/routed_expert.cpp:73-108; moe_q4k_a8_contract.cpp:126-141) ---
-float row_q4k(const u8* row, u32 blocks, const i8* codes, const float* deltas, const i32* sums) {
+inline size_t row_bytes(u32 type, u32 width) {
+    switch (type) {
+        case B200MOE_TYPE_Q8_0: return (size_t)width / 32 * 34;
+        case B200MOE_TYPE_Q5_1: return (size_t)width / 32 * 24;
+        case B200MOE_TYPE_Q5_K: return (size_t)width / 256 * 176;
+        default: return (size_t)width / 256 * 144;
+    }
+}
+// q5k: 176-byte super-blocks, 32 bytes of high bits at offset 16 (bit j of byte k = bit 4 of weight k of group j), the
+// nibbles from offset 48 (routed_expert.cpp:75, :88-95); everything else is the Q4_K rule.
+float row_kquant(const u8* row, u32 blocks, const i8* codes, const float* deltas, const i32* sums, bool q5k) {
+    const size_t wb = q5k ? 176 : 144, qs = q5k ? 48 : 16;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     for (u32 b = 0; b < blocks; ++b) {
-        const u8* blk = row + (size_t)b * 144;
+        const u8* blk = row + (size_t)b * wb;
         const float d = half_f(ld16(blk)), dm = half_f(ld16(blk + 2));
         float x[8];
         for (unsigned j = 0; j < 8; ++j) {
-            const u8* q = blk + 16 + 32 * (j >> 1);
+            const u8* q = blk + qs + 32 * (j >> 1);
             i32 dot = 0;
             for (int k = 0; k < 32; ++k) {
-                const int w = (j & 1) ? (q[k] >> 4) : (q[k] & 15);
+                int w = (j & 1) ? (q[k] >> 4) : (q[k] & 15);
+                if (q5k) w |= ((blk[16 + k] >> j) & 1) << 4;
                 dot += w * (i32)codes[256 * (size_t)b + 32 * j + k];
             }
             unsigned sc, mn;
@@ -123,6 +135,32 @@ float row_q4k(const u8* row, u32 blocks, const i8* codes, const float* deltas, c
             x[j] = deltas[8 * (size_t)b + j] * t;
         }
         for (int p = 0; p < 4; ++p) { const float pair = x[2 * p] + x[2 * p + 1]; acc[p] = acc[p] + pair; }
+    }
+    const float s01 = acc[0] + acc[1], s23 = acc[2] + acc[3];
+    return s01 + s23;
+}
+
+float row_q4k(const u8* row, u32 blocks, const i8* codes, const float* deltas, const i32* sums) {
+    return row_kquant(row, blocks, codes, deltas, sums, false);
+}
+
+// ---- Q5_1 down row, four chains (src/cpu/core/routed_expert.cpp:110-144): combined = d * float(dot) + m * float(S_g) ----
+float row_q5_1_chain4(const u8* row, u32 groups, const i8* codes, const float* deltas, const i32* sums) {
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (u32 g = 0; g < groups; ++g) {
+        const u8* blk = row + (size_t)g * 24;
+        const float d = half_f(ld16(blk)), m = half_f(ld16(blk + 2));
+        u32 qh;
+        std::memcpy(&qh, blk + 4, 4);
+        i32 dot = 0;
+        for (u32 k = 0; k < 32; ++k) {
+            const u8 byte = blk[8 + (k & 15)];
+            const int q = (k < 16 ? (byte & 15) : (byte >> 4)) | (int)(((qh >> k) & 1u) << 4);
+            dot += q * (i32)codes[32 * (size_t)g + k];
+        }
+        const float first = d * (float)dot;
+        const float combined = first + (m * (float)sums[g]);
+        acc[g % 4] = acc[g % 4] + (deltas[g] * combined);
     }
     const float s01 = acc[0] + acc[1], s23 = acc[2] + acc[3];
     return s01 + s23;
@@ -451,13 +489,13 @@ int orc_experts(const b200moe_shape* sh, const u8* gate, const u8* up, const u8*
                 float* gate_out, float* up_out, i8* act_codes, float* act_deltas, i32* act_sums, u32* status) {
     const u32 H = sh->hidden, I = sh->inter, K = sh->top_k;
     if (end == 0) end = sh->experts;
-    const bool q4k = sh->gate_type == B200MOE_TYPE_Q4_K;
+    const bool q5k = sh->gate_type == B200MOE_TYPE_Q5_K;
+    const bool q4k = sh->gate_type == B200MOE_TYPE_Q4_K || q5k;  // the K-quant (Qwen A8) family
     if (!q4k && sh->gate_type != B200MOE_TYPE_Q8_0) return 1;
-    if (sh->down_type != B200MOE_TYPE_Q4_K && sh->down_type != B200MOE_TYPE_Q8_0) return 1;
+    if (sh->down_type != B200MOE_TYPE_Q4_K && sh->down_type != B200MOE_TYPE_Q8_0 && sh->down_type != B200MOE_TYPE_Q5_1) return 1;
     if (!q4k && sh->down_type != B200MOE_TYPE_Q8_0) return 1;
     if (H % (q4k ? 256 : 32) || I % (sh->down_type == B200MOE_TYPE_Q4_K ? 256 : 32)) return 1;
-    const size_t grow = q4k ? (size_t)H / 256 * 144 : (size_t)H / 32 * 34;
-    const size_t drow = sh->down_type == B200MOE_TYPE_Q4_K ? (size_t)I / 256 * 144 : (size_t)I / 32 * 34;
+    const size_t grow = row_bytes(sh->gate_type, H), drow = row_bytes(sh->down_type, I);
     const u32 slots = rows * K;
     std::vector<i8> hc((size_t)slots * I);
     std::vector<float> hd((size_t)slots * (I / 32));
@@ -474,7 +512,7 @@ int orc_experts(const b200moe_shape* sh, const u8* gate, const u8* up, const u8*
             const u8* gr = gate + ((size_t)e * I + o) * grow;
             const u8* ur = up + ((size_t)e * I + o) * grow;
             float g, u;
-            if (q4k) { g = row_q4k(gr, H / 256, xc, xd, xs); u = row_q4k(ur, H / 256, xc, xd, xs); }
+            if (q4k) { g = row_kquant(gr, H / 256, xc, xd, xs, q5k); u = row_kquant(ur, H / 256, xc, xd, xs, q5k); }
             else { g = product_q8_0(gr, xc, xd, H); u = product_q8_0(ur, xc, xd, H); }
             if (gate_out) gate_out[(size_t)s * I + o] = g;
             if (up_out) up_out[(size_t)s * I + o] = u;
@@ -502,6 +540,7 @@ int orc_experts(const b200moe_shape* sh, const u8* gate, const u8* up, const u8*
             const u8* dr = down + ((size_t)e * H + o) * drow;
             float v;
             if (sh->down_type == B200MOE_TYPE_Q4_K) v = row_q4k(dr, I / 256, c, d, sm);
+            else if (sh->down_type == B200MOE_TYPE_Q5_1) v = row_q5_1_chain4(dr, I / 32, c, d, sm);
             else if (q4k) v = row_q8_chain4(dr, I / 32, c, d);
             else v = product_q8_0(dr, c, d, I);
             raw[(size_t)s * H + o] = v;
@@ -561,16 +600,30 @@ static double deq_dot(u32 type, const u8* row, const float* x, u32 width) {
             const double d = half_f(ld16(blk));
             for (int j = 0; j < 32; ++j) acc += d * (double)(i8)blk[2 + j] * (double)x[32 * g + j];
         }
+    } else if (type == B200MOE_TYPE_Q5_1) {
+        for (u32 g = 0; g < width / 32; ++g) {
+            const u8* blk = row + (size_t)g * 24;
+            const double d = half_f(ld16(blk)), m = half_f(ld16(blk + 2));
+            u32 qh;
+            std::memcpy(&qh, blk + 4, 4);
+            for (u32 k = 0; k < 32; ++k) {
+                const u8 byte = blk[8 + (k & 15)];
+                const int q = (k < 16 ? (byte & 15) : (byte >> 4)) | (int)(((qh >> k) & 1u) << 4);
+                acc += (d * q + m) * (double)x[32 * g + k];
+            }
+        }
     } else {
+        const bool q5k = type == B200MOE_TYPE_Q5_K;
         for (u32 b = 0; b < width / 256; ++b) {
-            const u8* blk = row + (size_t)b * 144;
+            const u8* blk = row + (size_t)b * (q5k ? 176 : 144);
             const double d = half_f(ld16(blk)), dm = half_f(ld16(blk + 2));
             for (unsigned j = 0; j < 8; ++j) {
                 unsigned sc, mn;
                 q4k_factors(blk, j, &sc, &mn);
-                const u8* q = blk + 16 + 32 * (j >> 1);
+                const u8* q = blk + (q5k ? 48 : 16) + 32 * (j >> 1);
                 for (int k = 0; k < 32; ++k) {
-                    const int w = (j & 1) ? (q[k] >> 4) : (q[k] & 15);
+                    int w = (j & 1) ? (q[k] >> 4) : (q[k] & 15);
+                    if (q5k) w |= ((blk[16 + k] >> j) & 1) << 4;
                     acc += (d * sc * w - dm * mn) * (double)x[256 * b + 32 * j + k];
                 }
             }
@@ -581,9 +634,8 @@ static double deq_dot(u32 type, const u8* row, const float* x, u32 width) {
 int orc_float_truth(const b200moe_shape* sh, const u8* gate, const u8* up, const u8* down, const u32* ids, const float* weights,
                     u32 rows, const float* x, float* y) {
     const u32 H = sh->hidden, I = sh->inter, K = sh->top_k;
-    const bool q4k = sh->gate_type == B200MOE_TYPE_Q4_K;
-    const size_t grow = q4k ? (size_t)H / 256 * 144 : (size_t)H / 32 * 34;
-    const size_t drow = sh->down_type == B200MOE_TYPE_Q4_K ? (size_t)I / 256 * 144 : (size_t)I / 32 * 34;
+    const bool q4k = sh->gate_type == B200MOE_TYPE_Q4_K || sh->gate_type == B200MOE_TYPE_Q5_K;
+    const size_t grow = row_bytes(sh->gate_type, H), drow = row_bytes(sh->down_type, I);
     parallel_for(rows, [&](size_t ri) {
         const u32 r = (u32)ri;
         std::vector<double> acc(H, 0.0);

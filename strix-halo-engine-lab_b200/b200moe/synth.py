@@ -5,11 +5,15 @@ every tensor here is drawn from a seeded numpy generator. Blocks are written in 
 consume:
   Q8_0 block (34 B):        fp16 d (little endian) | int8 q[32]
   Q4_K super-block (144 B): fp16 d | fp16 dmin | 12 B of packed 6-bit (scale, min) x 8 | 128 B of 4-bit quants
+  Q5_K super-block (176 B): as Q4_K with 32 B of high bits between the packed factors and the nibbles
+  Q5_1 block (24 B):        fp16 d | fp16 m | 32 high bits | 16 B of 4-bit quants
 """
 import numpy as np
 
 Q8_0_BLOCK = 34
 Q4_K_BLOCK = 144
+Q5_K_BLOCK = 176
+Q5_1_BLOCK = 24
 
 
 def q8_0_blocks(rng, nblocks, scale=0.01):
@@ -30,6 +34,24 @@ def q4_k_blocks(rng, nblocks, scale=0.01 / 32):
     return out
 
 
+def q5_k_blocks(rng, nblocks, scale=0.01 / 64):
+    """As q4_k_blocks with 5-bit quants: every byte but the two fp16 factors uniform."""
+    out = rng.integers(0, 256, size=(nblocks, Q5_K_BLOCK), dtype=np.uint8)
+    dd = (np.abs(rng.standard_normal((nblocks, 2), dtype=np.float32)) * scale).astype(np.float16)
+    out[:, 0:4] = dd.view(np.uint8).reshape(nblocks, 4)
+    return out
+
+
+def q5_1_blocks(rng, nblocks, scale=0.01 / 16):
+    """d = fp16(|N(0,1)| * scale), m = fp16(N(0,1) * scale * 8), 5-bit quants uniform in 0..31."""
+    out = rng.integers(0, 256, size=(nblocks, Q5_1_BLOCK), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal(nblocks, dtype=np.float32)) * scale).astype(np.float16)
+    m = (rng.standard_normal(nblocks, dtype=np.float32) * scale * 8).astype(np.float16)
+    out[:, 0:2] = d.view(np.uint8).reshape(nblocks, 2)
+    out[:, 2:4] = m.view(np.uint8).reshape(nblocks, 2)
+    return out
+
+
 def pack_q4k_factors(scales, mins):
     """Twelve bytes holding eight (scale, min) 6-bit pairs, the get_scale_min_k4 packing."""
     b = np.zeros(12, np.uint8)
@@ -46,7 +68,7 @@ def pack_q4k_factors(scales, mins):
 
 
 def row_bytes(ggml_type, width):
-    return width // 32 * Q8_0_BLOCK if ggml_type == 8 else width // 256 * Q4_K_BLOCK
+    return {7: width // 32 * Q5_1_BLOCK, 8: width // 32 * Q8_0_BLOCK, 13: width // 256 * Q5_K_BLOCK}.get(ggml_type, width // 256 * Q4_K_BLOCK)
 
 
 def expert_tensors(rng, experts, hidden, inter, gate_type, down_type):
@@ -54,6 +76,10 @@ def expert_tensors(rng, experts, hidden, inter, gate_type, down_type):
     def tensor(t, rows, width):
         if t == 8:
             return q8_0_blocks(rng, experts * rows * (width // 32)).reshape(-1)
+        if t == 7:
+            return q5_1_blocks(rng, experts * rows * (width // 32)).reshape(-1)
+        if t == 13:
+            return q5_k_blocks(rng, experts * rows * (width // 256)).reshape(-1)
         return q4_k_blocks(rng, experts * rows * (width // 256)).reshape(-1)
     return tensor(gate_type, inter, hidden), tensor(gate_type, inter, hidden), tensor(down_type, hidden, inter)
 

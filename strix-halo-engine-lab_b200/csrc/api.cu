@@ -100,12 +100,13 @@ struct Carver {  // caller-owned workspace, 256-byte aligned sections
 };
 
 int check_shape(const b200moe_shape& s) {
-    B200_REQUIRE(s.gate_type == B200MOE_TYPE_Q8_0 || s.gate_type == B200MOE_TYPE_Q4_K, "gate/up type %u is not bound (Q8_0 = 8, Q4_K = 12)", s.gate_type);
-    B200_REQUIRE(s.down_type == B200MOE_TYPE_Q8_0 || s.down_type == B200MOE_TYPE_Q4_K, "down type %u is not bound (Q8_0 = 8, Q4_K = 12)", s.down_type);
-    B200_REQUIRE(!(s.gate_type == B200MOE_TYPE_Q8_0 && s.down_type == B200MOE_TYPE_Q4_K), "Q8_0 gate/up with Q4_K down has no declared contract");
+    B200_REQUIRE(s.gate_type == B200MOE_TYPE_Q8_0 || is_kquant(s.gate_type), "gate/up type %u is not bound (Q8_0 = 8, Q4_K = 12, Q5_K = 13)", s.gate_type);
+    B200_REQUIRE(s.down_type == B200MOE_TYPE_Q8_0 || s.down_type == B200MOE_TYPE_Q4_K || s.down_type == B200MOE_TYPE_Q5_1,
+                 "down type %u is not bound (Q5_1 = 7, Q8_0 = 8, Q4_K = 12)", s.down_type);
+    B200_REQUIRE(!(s.gate_type == B200MOE_TYPE_Q8_0 && s.down_type != B200MOE_TYPE_Q8_0), "Q8_0 gate/up with a down type other than Q8_0 has no declared contract");
     B200_REQUIRE(s.hidden && s.inter && s.experts && s.top_k, "shape has a zero dimension");
     B200_REQUIRE(s.experts <= kMaxExperts && s.top_k <= kMaxTopK && s.top_k <= s.experts, "need top_k <= 32, top_k <= experts <= 1024");
-    B200_REQUIRE(s.hidden % (s.gate_type == B200MOE_TYPE_Q4_K ? 256u : 32u) == 0, "hidden %u is not a whole number of gate/up blocks", s.hidden);
+    B200_REQUIRE(s.hidden % (is_kquant(s.gate_type) ? 256u : 32u) == 0, "hidden %u is not a whole number of gate/up blocks", s.hidden);
     B200_REQUIRE(s.inter % (s.down_type == B200MOE_TYPE_Q4_K ? 256u : 32u) == 0, "inter %u is not a whole number of down blocks", s.inter);
     B200_REQUIRE(s.hidden % 64 == 0, "hidden %u must be a multiple of 64", s.hidden);
     return B200MOE_OK;
@@ -214,14 +215,15 @@ bool use_grouped(const b200moe_shape& s, u32 rows, u32 grouped_min_rows, bool ha
     return rows >= least && grouped_fits(s, have_sums);
 }
 int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
-    if (v.shape.gate_type != B200MOE_TYPE_Q4_K) return launch_gate_up_q8(v, st);
+    if (!is_kquant(v.shape.gate_type)) return launch_gate_up_q8(v, st);
+    if (v.shape.gate_type == B200MOE_TYPE_Q5_K) return launch_gate_up_q4k(v, st);  // the per-block form reads both K-quant layouts
     if (use_grouped(v.shape, rows, grouped_min_rows, v.x.sums != nullptr)) return launch_gate_up_q4k_grouped(v, st);
     return stream_gate_up_fits(v, rows) ? launch_gate_up_q4k_stream(v, rows, st) : launch_gate_up_q4k(v, st);
 }
 int enqueue_down(const b200moe_down_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
     if (v.shape.down_type == B200MOE_TYPE_Q4_K && use_grouped(v.shape, rows, grouped_min_rows, v.act.sums != nullptr)) return launch_down_q4k_grouped(v, st);
     if (v.shape.down_type == B200MOE_TYPE_Q4_K) return stream_down_fits(v, rows) ? launch_down_q4k_stream(v, rows, st) : launch_down_q4k(v, st);
-    return v.shape.gate_type == B200MOE_TYPE_Q4_K ? launch_down_q8_chain4(v, st) : launch_down_q8(v, st);
+    return is_kquant(v.shape.gate_type) ? launch_down_q8_chain4(v, st) : launch_down_q8(v, st);  // chain4: Q8_0 and Q5_1 blocks
 }
 
 }  // namespace
@@ -321,9 +323,9 @@ int b200moe_gate_up(const b200moe_gate_up_view* v, void* stream) {
     if (int rc = check_routes(v->routes)) return rc;
     B200_REQUIRE(v->weights.gate && v->weights.up && aligned(v->weights.gate, 16) && aligned(v->weights.up, 16), "gate_up: gate / up tensors must be non-null and 16-byte aligned");
     B200_REQUIRE((v->gate_out == nullptr) == (v->up_out == nullptr), "gate_up: gate_out and up_out come together");
-    const bool q4k = v->shape.gate_type == B200MOE_TYPE_Q4_K;
+    const bool q4k = is_kquant(v->shape.gate_type);
     if (int rc = check_a8(v->x, 0, v->shape.hidden, q4k, "gate_up x")) return rc;
-    if (int rc = check_a8(v->act, 0, v->shape.inter, v->shape.down_type == B200MOE_TYPE_Q4_K, "gate_up act")) return rc;
+    if (int rc = check_a8(v->act, 0, v->shape.inter, down_reads_sums(v->shape.down_type), "gate_up act")) return rc;
     if (!device_ready()) return B200MOE_ERR_CUDA;
     return enqueue_gate_up(*v, v->x.rows, as_stream(stream));
 }
@@ -333,7 +335,7 @@ int b200moe_down(const b200moe_down_view* v, void* stream) {
     if (int rc = check_shape(v->shape)) return rc;
     if (int rc = check_routes(v->routes)) return rc;
     B200_REQUIRE(v->weights.down && aligned(v->weights.down, 16) && v->raw, "down: the down tensor must be non-null and 16-byte aligned, raw non-null");
-    if (int rc = check_a8(v->act, 0, v->shape.inter, v->shape.down_type == B200MOE_TYPE_Q4_K, "down act")) return rc;
+    if (int rc = check_a8(v->act, 0, v->shape.inter, down_reads_sums(v->shape.down_type), "down act")) return rc;
     if (!device_ready()) return B200MOE_ERR_CUDA;
     return enqueue_down(*v, v->act.rows / v->shape.top_k, as_stream(stream));
 }
@@ -378,7 +380,7 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
     B200_REQUIRE(v->ids && v->route_weights, "layer: ids / route_weights are null");
     B200_REQUIRE(v->weights.gate && v->weights.up && v->weights.down, "layer: expert tensors are null");
     B200_REQUIRE(aligned(v->weights.gate, 16) && aligned(v->weights.up, 16) && aligned(v->weights.down, 16), "layer: expert tensors must be 16-byte aligned");
-    if (int rc = check_a8(v->x, v->rows, s.hidden, s.gate_type == B200MOE_TYPE_Q4_K, "layer x")) return rc;
+    if (int rc = check_a8(v->x, v->rows, s.hidden, is_kquant(s.gate_type), "layer x")) return rc;
     B200_REQUIRE(v->end <= s.experts && (v->end == 0 || v->first < v->end) && v->base <= v->first, "layer: expert range [%u, %u) base %u is inconsistent", v->first, v->end, v->base);
     B200_REQUIRE(v->combine_form <= B200MOE_COMBINE_FMA_SLOTS, "layer: unknown combine form %u", v->combine_form);
     if (v->y && v->combine_form == B200MOE_COMBINE_PARTS)
@@ -433,7 +435,7 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
     cv.rows = v->rows; cv.top_k = s.top_k; cv.hidden = s.hidden; cv.form = v->combine_form;
     cv.parts = v->parts; cv.part_experts = v->part_experts; cv.only_part = v->only_part;
     cv.y = v->y; cv.y_bf16 = v->y_bf16; cv.y_blocks = v->y_blocks; cv.y_block_rows = v->y_block_rows;
-    cv.row_status = s.gate_type == B200MOE_TYPE_Q4_K ? row_status : nullptr;
+    cv.row_status = is_kquant(s.gate_type) ? row_status : nullptr;
     tap(6);
     const int rc = launch_combine(cv, st);
     tap(7);
@@ -531,7 +533,7 @@ int b200moe_dense_ffn(const b200moe_dense_view* v, void* stream) {
     B200_REQUIRE(v->y, "dense_ffn: y is null");
     B200_REQUIRE(v->weights.gate && v->weights.up && v->weights.down, "dense_ffn: tensors are null");
     B200_REQUIRE(aligned(v->weights.gate, 16) && aligned(v->weights.up, 16) && aligned(v->weights.down, 16), "dense_ffn: tensors must be 16-byte aligned");
-    if (int rc = check_a8(v->x, v->rows, s.hidden, s.gate_type == B200MOE_TYPE_Q4_K, "dense_ffn x")) return rc;
+    if (int rc = check_a8(v->x, v->rows, s.hidden, is_kquant(s.gate_type), "dense_ffn x")) return rc;
     const LayerScratch L = carve_layer(v->workspace, s, v->rows);
     if (!v->workspace || v->workspace_bytes < L.bytes)
         return fail(B200MOE_ERR_WORKSPACE, "dense_ffn: workspace of %llu bytes needed, %llu given", (unsigned long long)L.bytes, (unsigned long long)v->workspace_bytes);

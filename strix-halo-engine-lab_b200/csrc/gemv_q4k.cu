@@ -6,6 +6,9 @@
 // h = (g / (1 + exp(-g))) * u and the A8 rule per 32 outputs. Q4_K down = the same row rule over K = inter
 // (src/moe_a8_down_contract.cpp:141-146); Q8_0 down = four chains by g % 4 (routed_expert.cpp:110-144).
 // Integer dots are exact (dp4a), every FP32 step is one IEEE operation, so results equal the host's bit for bit.
+// The same kernels read the executor's other stored formats (routed_expert.hpp:27-28): Q5_K gate / up (176-byte
+// super-blocks, the Q4_K rule with a fifth bit per weight) and Q5_1 down (24-byte blocks on the four chains,
+// d * float(dot) + m * float(S_g)).
 //
 // Mapping: 4 lanes per super-block (lane = pair p: 32 B of nibbles serve groups 2p (low) and 2p+1 (high)), LPR lanes
 // per weight row (8 / 16 / 32 by row length), so a warp streams 32 / LPR rows at once with 16-byte loads: per
@@ -38,23 +41,31 @@ __device__ __forceinline__ void q4k_factor(const uint4& hdr, u32 j, float d, flo
     *DM = __fmul_rn(dm, static_cast<float>(mn));
 }
 
-__device__ __forceinline__ int dot8(const uint4& wa, const uint4& wb, const uint4& ca, const uint4& cb, u32 shift) {
+// 32 weights of one group against 32 codes: nibbles at `shift` (0 = low, 4 = high) of the 32 bytes wa | wb. Q5_K adds
+// bit j of the 32 high-bit bytes ha | hb as bit 4 of each weight (routed_expert.cpp:88-95).
+template <bool Q5K>
+__device__ __forceinline__ int dot8(const uint4& wa, const uint4& wb, const uint4& ha, const uint4& hb, u32 j, const uint4& ca, const uint4& cb, u32 shift) {
+    auto w = [&](u32 q, u32 h) -> int {
+        u32 v = (q >> shift) & 0x0f0f0f0fu;
+        if (Q5K) v |= ((h >> j) & 0x01010101u) << 4;
+        return static_cast<int>(v);
+    };
     int s = 0;
-    s = __dp4a(static_cast<int>((wa.x >> shift) & 0x0f0f0f0fu), static_cast<int>(ca.x), s);
-    s = __dp4a(static_cast<int>((wa.y >> shift) & 0x0f0f0f0fu), static_cast<int>(ca.y), s);
-    s = __dp4a(static_cast<int>((wa.z >> shift) & 0x0f0f0f0fu), static_cast<int>(ca.z), s);
-    s = __dp4a(static_cast<int>((wa.w >> shift) & 0x0f0f0f0fu), static_cast<int>(ca.w), s);
-    s = __dp4a(static_cast<int>((wb.x >> shift) & 0x0f0f0f0fu), static_cast<int>(cb.x), s);
-    s = __dp4a(static_cast<int>((wb.y >> shift) & 0x0f0f0f0fu), static_cast<int>(cb.y), s);
-    s = __dp4a(static_cast<int>((wb.z >> shift) & 0x0f0f0f0fu), static_cast<int>(cb.z), s);
-    s = __dp4a(static_cast<int>((wb.w >> shift) & 0x0f0f0f0fu), static_cast<int>(cb.w), s);
+    s = __dp4a(w(wa.x, ha.x), static_cast<int>(ca.x), s);
+    s = __dp4a(w(wa.y, ha.y), static_cast<int>(ca.y), s);
+    s = __dp4a(w(wa.z, ha.z), static_cast<int>(ca.z), s);
+    s = __dp4a(w(wa.w, ha.w), static_cast<int>(ca.w), s);
+    s = __dp4a(w(wb.x, hb.x), static_cast<int>(cb.x), s);
+    s = __dp4a(w(wb.y, hb.y), static_cast<int>(cb.y), s);
+    s = __dp4a(w(wb.z, hb.z), static_cast<int>(cb.z), s);
+    s = __dp4a(w(wb.w, hb.w), static_cast<int>(cb.w), s);
     return s;
 }
 
 // One Q4_K weight row (nblocks super-blocks at wrow) against nr <= kR staged A8 rows. LPR lanes cooperate on the row
 // (lane-in-row li: super-block li / 4 of each step, pair li % 4); `base` is the first lane of the row's lane group.
 // Every lane of the group returns the row values in out[].
-template <int LPR>
+template <int LPR, bool Q5K = false>
 __device__ __forceinline__ void q4k_row(const u8* __restrict__ wrow, u32 nblocks, const A8Smem& x, int nr, u32 li, u32 base, float* out) {
     constexpr u32 BPI = LPR / 4;
     const u32 p = li & 3u, bsub = li >> 2;
@@ -64,12 +75,13 @@ __device__ __forceinline__ void q4k_row(const u8* __restrict__ wrow, u32 nblocks
     for (u32 b0 = 0; b0 < nblocks; b0 += BPI) {
         const u32 b = b0 + bsub;
         const bool valid = b < nblocks;
-        uint4 hdr = make_uint4(0, 0, 0, 0), q0 = hdr, q1 = hdr;
+        uint4 hdr = make_uint4(0, 0, 0, 0), q0 = hdr, q1 = hdr, h0 = hdr, h1 = hdr;
         if (valid) {
-            const uint4* blk = reinterpret_cast<const uint4*>(wrow + u64(b) * kQ4KBlock);
+            const uint4* blk = reinterpret_cast<const uint4*>(wrow + u64(b) * (Q5K ? kQ5KBlock : kQ4KBlock));
             hdr = __ldg(blk);
-            q0 = __ldg(blk + 1 + 2 * p);
-            q1 = __ldg(blk + 2 + 2 * p);
+            if (Q5K) { h0 = __ldg(blk + 1); h1 = __ldg(blk + 2); }  // Q5_K: 32 bytes of high bits between header and nibbles
+            q0 = __ldg(blk + (Q5K ? 3 : 1) + 2 * p);
+            q1 = __ldg(blk + (Q5K ? 4 : 2) + 2 * p);
         }
         const float d = half_bits_to_float(hdr.x & 0xffffu), dm = half_bits_to_float(hdr.x >> 16);
         float Dl, DMl, Dh, DMh;
@@ -83,7 +95,7 @@ __device__ __forceinline__ void q4k_row(const u8* __restrict__ wrow, u32 nblocks
                 if (valid) {
                     const uint4* c = reinterpret_cast<const uint4*>(x.codes + u64(r) * x.width + 256u * b + 64u * p);
                     const uint4 c0 = c[0], c1 = c[1], c2 = c[2], c3 = c[3];
-                    const int dl = dot8(q0, q1, c0, c1, 0), dh = dot8(q0, q1, c2, c3, 4);
+                    const int dl = dot8<Q5K>(q0, q1, h0, h1, 2 * p, c0, c1, 0), dh = dot8<Q5K>(q0, q1, h0, h1, 2 * p + 1, c2, c3, 4);
                     const u32 g = r * (x.width / 32) + 8u * b + 2u * p;
                     const float2 e = *reinterpret_cast<const float2*>(x.deltas + g);
                     const int2 s = *reinterpret_cast<const int2*>(x.sums + g);
@@ -124,7 +136,7 @@ __device__ __forceinline__ void stage_a8(const b200moe_a8_rows& src, const u32* 
 }
 
 // grid (inter / 32, max_union); 256 threads. One CTA = one expert x one 32-output group (= one A8 group of h).
-template <int LPR>
+template <int LPR, bool Q5K>
 __global__ void __launch_bounds__(256) gate_up_q4k_kernel(b200moe_gate_up_view v) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const u32 j = blockIdx.y;
@@ -141,7 +153,7 @@ __global__ void __launch_bounds__(256) gate_up_q4k_kernel(b200moe_gate_up_view v
     const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     constexpr u32 RPW = 32 / LPR;
     const u32 sub = lane / LPR, li = lane % LPR, base = sub * LPR;
-    const u64 row_bytes = u64(nblocks) * kQ4KBlock;
+    const u64 row_bytes = u64(nblocks) * (Q5K ? kQ5KBlock : kQ4KBlock);
     const u8* gate = v.weights.gate + (u64(expert) * I + 32u * blockIdx.x) * row_bytes;
     const u8* up = v.weights.up + (u64(expert) * I + 32u * blockIdx.x) * row_bytes;
     const A8Smem xs{s_codes, s_deltas, s_sums, H};
@@ -159,7 +171,7 @@ __global__ void __launch_bounds__(256) gate_up_q4k_kernel(b200moe_gate_up_view v
             const u32 t = t0 + sub;
             const u8* wrow = (t < 32 ? gate : up) + u64(t & 31u) * row_bytes;
             float val[kR];
-            q4k_row<LPR>(wrow, nblocks, xs, nr, li, base, val);
+            q4k_row<LPR, Q5K>(wrow, nblocks, xs, nr, li, base, val);
             if (li == 0) {
                 float* dst = t < 32 ? s_g : s_u;
 #pragma unroll
@@ -238,6 +250,7 @@ __global__ void __launch_bounds__(256) down_q4k_kernel(b200moe_down_view v, u32 
 // Q8_0 down in the four-chain rule (routed_expert.cpp:110-144): chain c = g % 4 adds E_g * (d * float(dot)) in
 // ascending g; value = (acc0 + acc1) + (acc2 + acc3). One warp per down row, lane = group within a run of 32.
 // grid (hidden / 32, max_union); 256 threads.
+template <bool Q51>
 __global__ void __launch_bounds__(256) down_q8_chain4_kernel(b200moe_down_view v) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     if (v.summary && *v.summary) return;
@@ -250,7 +263,7 @@ __global__ void __launch_bounds__(256) down_q8_chain4_kernel(b200moe_down_view v
     __shared__ u32 s_slots[kR];
     const u32 expert = v.routes.experts[j], eb = v.routes.begins[j], ee = v.routes.begins[j + 1];
     const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    const u64 row_bytes = u64(groups) * kQ8Block;
+    const u64 row_bytes = u64(groups) * (Q51 ? kQ51Block : kQ8Block);
     const u32 o0 = 32u * blockIdx.x;
     const u8* down = v.weights.down + (u64(expert) * H + o0) * row_bytes;
     const u32 chain = lane & 3u;
@@ -271,8 +284,22 @@ __global__ void __launch_bounds__(256) down_q8_chain4_kernel(b200moe_down_view v
                 const u32 g = g0 + lane;
                 const bool valid = g < groups;
                 u32 q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                float d = 0.0f;
-                if (valid) {  // 34-byte blocks are only 2-byte aligned: halfword loads
+                float d = 0.0f, mn = 0.0f;
+                if (valid && Q51) {
+                    // Q5_1 (routed_expert.cpp:124-133): 24-byte blocks, 8-byte aligned. Weight k < 16 = low nibble of byte
+                    // k, k >= 16 = high nibble of byte k - 16, bit k of the 32 high bits on top: unsigned 0..31.
+                    const uint2* b8 = reinterpret_cast<const uint2*>(wrow + u64(g) * kQ51Block);
+                    const uint2 hd = __ldg(b8), qa = __ldg(b8 + 1), qb = __ldg(b8 + 2);
+                    d = half_bits_to_float(hd.x & 0xffffu);
+                    mn = half_bits_to_float(hd.x >> 16);
+                    const u32 qs[4] = {qa.x, qa.y, qb.x, qb.y};
+                    auto spread = [](u32 x) { return ((x & 1u) | ((x & 2u) << 7) | ((x & 4u) << 14) | ((x & 8u) << 21)) << 4; };
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        q[i] = (qs[i] & 0x0f0f0f0fu) | spread(hd.y >> (4 * i));
+                        q[4 + i] = ((qs[i] >> 4) & 0x0f0f0f0fu) | spread(hd.y >> (16 + 4 * i));
+                    }
+                } else if (valid) {  // 34-byte blocks are only 2-byte aligned: halfword loads
                     const u16* b16 = reinterpret_cast<const u16*>(wrow + u64(g) * kQ8Block);
                     d = half_bits_to_float(b16[0]);
 #pragma unroll
@@ -291,7 +318,9 @@ __global__ void __launch_bounds__(256) down_q8_chain4_kernel(b200moe_down_view v
                             dot = __dp4a((int)q[2], (int)c0.z, dot); dot = __dp4a((int)q[3], (int)c0.w, dot);
                             dot = __dp4a((int)q[4], (int)c1.x, dot); dot = __dp4a((int)q[5], (int)c1.y, dot);
                             dot = __dp4a((int)q[6], (int)c1.z, dot); dot = __dp4a((int)q[7], (int)c1.w, dot);
-                            term = __fmul_rn(s_deltas[r * groups + g], __fmul_rn(d, static_cast<float>(dot)));
+                            float combined = __fmul_rn(d, static_cast<float>(dot));
+                            if (Q51) combined = __fadd_rn(combined, __fmul_rn(mn, static_cast<float>(s_sums[r * groups + g])));
+                            term = __fmul_rn(s_deltas[r * groups + g], combined);
                         }
 #pragma unroll
                         for (u32 k = 0; k < 8; ++k) {  // chain c takes groups c, c + 4, ... ascending
@@ -324,10 +353,15 @@ int launch_gate_up_q4k(const b200moe_gate_up_view& v, cudaStream_t stream) {
     if (v.max_union == 0) return B200MOE_OK;
     const u32 smem = kR * (H + H / 32 * 8) + 2 * kR * 32 * 4;
     const dim3 grid(I / 32, v.max_union);
-#define B200_GU(L)                                                        \
-    {                                                                     \
-        if (int rc = set_smem(gate_up_q4k_kernel<L>, smem)) return rc;    \
-        gate_up_q4k_kernel<L><<<grid, 256, smem, stream>>>(v);            \
+#define B200_GU(L)                                                                   \
+    {                                                                                \
+        if (v.shape.gate_type == B200MOE_TYPE_Q5_K) {                                \
+            if (int rc = set_smem(gate_up_q4k_kernel<L, true>, smem)) return rc;     \
+            gate_up_q4k_kernel<L, true><<<grid, 256, smem, stream>>>(v);             \
+        } else {                                                                     \
+            if (int rc = set_smem(gate_up_q4k_kernel<L, false>, smem)) return rc;    \
+            gate_up_q4k_kernel<L, false><<<grid, 256, smem, stream>>>(v);            \
+        }                                                                            \
     }
     switch (lanes_per_row(H / 256)) {
         case 32: B200_GU(32) break;
@@ -363,8 +397,13 @@ int launch_down_q8_chain4(const b200moe_down_view& v, cudaStream_t stream) {
     const u32 H = v.shape.hidden, I = v.shape.inter;
     if (v.max_union == 0) return B200MOE_OK;
     const u32 smem = kR * (I + I / 32 * 8);
-    if (int rc = set_smem(down_q8_chain4_kernel, smem)) return rc;
-    down_q8_chain4_kernel<<<dim3(H / 32, v.max_union), 256, smem, stream>>>(v);
+    if (v.shape.down_type == B200MOE_TYPE_Q5_1) {
+        if (int rc = set_smem(down_q8_chain4_kernel<true>, smem)) return rc;
+        down_q8_chain4_kernel<true><<<dim3(H / 32, v.max_union), 256, smem, stream>>>(v);
+    } else {
+        if (int rc = set_smem(down_q8_chain4_kernel<false>, smem)) return rc;
+        down_q8_chain4_kernel<false><<<dim3(H / 32, v.max_union), 256, smem, stream>>>(v);
+    }
     return after_launch("down_q8_chain4");
 }
 

@@ -3,7 +3,7 @@ the reference checkout by oracle/Makefile). Run where the reference checkout exi
 
     make -C oracle && python tests/golden/make_golden.py
 
-norm_golden.npz (the RMSNorm in front of the FFN) is written by the same run; `--norm-only` writes just that file.
+norm_golden.npz (the RMSNorm in front of the FFN) is written by the same run; `--norm-only` writes just that file; formats_golden.npz (Q5_K / Q5_1 tensors) likewise with `--formats-only`.
 The vectors are small seeded cases of every contract on the path; tests/test_oracle_pins.py::test_golden_vectors
 replays them against the restated oracle wherever the reference itself is absent (e.g. on the GPU box).
 """
@@ -96,7 +96,30 @@ def norm_vectors():
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def format_vectors():
+    """tests/golden/formats_golden.npz: reference_run on Q5_K gate/up and Q5_1 / Q8_0 down tensors."""
+    ref = Ref()
+    rng = np.random.default_rng(20252)
+    E, H, I, K, rows = 2, 256, 128, 2, 2
+    out = {"shape": np.array([E, H, I, K])}
+    for gt, dt, gf, df in ((13, 7, 1, 0), (12, 7, 0, 0), (13, 8, 1, 1)):
+        g, u, d = synth.expert_tensors(rng, E, H, I, gt, dt)
+        x = rng.standard_normal((rows, H), dtype=np.float32)
+        c, dl, s = ref.quantize_a8(x)
+        ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+        raw, status = ref.expert_run(g, u, d, gf, df, H, I, c, dl, s, ids, threads=0)
+        assert not status.any()
+        t = f"{gt}_{dt}"
+        out.update({f"gate_{t}": g, f"up_{t}": u, f"down_{t}": d, f"x_{t}": x, f"ids_{t}": ids, f"raw_{t}": raw})
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "formats_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
-    if "--norm-only" not in sys.argv:
+    if "--norm-only" not in sys.argv and "--formats-only" not in sys.argv:
         main()
-    norm_vectors()
+    if "--formats-only" not in sys.argv:
+        norm_vectors()
+    if "--norm-only" not in sys.argv:
+        format_vectors()

@@ -438,6 +438,24 @@ def test_experts_q4k_qwen_family(gpu, oracle):
     print("qwen family bit-exact on every case:", exact_all)
 
 
+def test_experts_other_formats_q5_k_q5_1(gpu, oracle):
+    """The other stored formats of the same executor (routed_expert.hpp:27-28): Q5_K gate/up (the Q4_K rule with 5-bit
+    quants) and Q5_1 down (four chains, d * dot + m * S): bit for bit, every combination with Q4_K / Q8_0, through
+    the stages and through the layer call; a decode window and one beyond it."""
+    import b200moe
+    from b200moe import synth
+    rng = np.random.default_rng(27)
+    for E, H, I, K, rows, gt, dt in ((6, 512, 256, 2, 7, 13, 7), (8, 2048, 768, 4, 4, 13, 12), (5, 1280, 640, 3, 3, 12, 7),
+                                     (4, 768, 512, 2, 9, 13, 8), (4, 256, 256, 2, 70, 13, 7), (3, 7168, 2048, 2, 2, 13, 7)):
+        gate, up, down = synth.expert_tensors(rng, E, H, I, gt, dt)
+        x = rng.standard_normal((rows, H), dtype=np.float32)
+        ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+        wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
+        sh, osh = shape_pair(H, I, E, K, gt, dt)
+        run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS)
+        run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, first=1, end=E - 1)
+
+
 def test_experts_q4k_grouped_tensor_core_form(gpu, oracle):
     """Windows of 128 rows and more take the grouped form (tcgen05 integer MMAs + the same FP32 chains): stage by stage
     against the oracle like the decode forms. Cases: several token tiles per expert with a ragged last one, experts with

@@ -407,3 +407,37 @@ def test_rmsnorm_against_reference(oracle, ref):
         w = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
         for ww in (w, None):
             assert same(oracle.rmsnorm(x, ww, 1e-6), ref.rmsnorm(x, ww, 1e-6))
+
+
+# ---- the executor's other stored formats: Q5_K gate/up, Q5_1 down (src/cpu/core/routed_expert.hpp:27-28) -----------
+FORMAT_CASES = ((13, 7, 1, 0), (12, 7, 0, 0), (13, 8, 1, 1), (13, 12, 1, None))
+
+
+def test_other_formats_against_reference_executor(oracle, ref):
+    """reference_run (scalar) and Executor (AVX2 + VNNI table, 4 threads) on Q5_K / Q5_1 tensors = the oracle, bit for bit.
+    Q4_K down has no executor form (its reference is evaluate_down_row, pinned above): gate/up taps only there."""
+    rng = np.random.default_rng(91)
+    E, H, I, K, rows = 4, 512, 256, 2, 3
+    for gt, dt, gf, df in FORMAT_CASES:
+        g, u, d = synth.expert_tensors(rng, E, H, I, gt, dt)
+        x = rng.standard_normal((rows, H), dtype=np.float32)
+        c, dl, s = ref.quantize_a8(x)
+        ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+        ex = oracle.experts(L.Shape(H, I, E, K, gt, dt, np.inf), g, u, d, ids, c, dl, s)
+        if df is None:
+            continue
+        for threads in (0, 4):
+            raw, st = ref.expert_run(g, u, d, gf, df, H, I, c, dl, s, ids, threads=threads)
+            assert not st.any() and same(ex["raw"], raw)
+
+
+def test_other_formats_golden_vectors(oracle):
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "formats_golden.npz"))
+    E, H, I, K = (int(v) for v in g["shape"])
+    for gt, dt, _, df in FORMAT_CASES:
+        if df is None:
+            continue
+        t = f"{gt}_{dt}"
+        c, dl, s = oracle.quantize_a8(g[f"x_{t}"])
+        ex = oracle.experts(L.Shape(H, I, E, K, gt, dt, np.inf), g[f"gate_{t}"], g[f"up_{t}"], g[f"down_{t}"], g[f"ids_{t}"], c, dl, s)
+        assert same(ex["raw"], g[f"raw_{t}"])
