@@ -437,6 +437,50 @@ int b200moe_gguf_tensor_at(const void* file, uint64_t index, b200moe_gguf_tensor
 int b200moe_gguf_find(const void* file, const char* name, b200moe_gguf_tensor_info* out);
 int b200moe_gguf_find_moe_layer(const void* file, uint32_t layer, b200moe_gguf_moe_layer* out);
 
+/* ------------------------------------------------------------------------------------------------ Expert residency
+ * A layer whose experts do not all live in HBM: `slots` of the `experts` are resident (caller-owned slot tensors, the
+ * per-expert layout of the full tensors), the rest stays in host memory. Stands where the reference has its tiered
+ * expert residency (include/strix/cuda/tiered_experts.hpp:1-17: publish maps expert ids to slots through a device table,
+ * a miss goes to the host; planner include/strix/residency/expert_residency.hpp:121-147: decayed use scores, free slots
+ * first, an expert seen in the current step is never evicted, ties ascending) - with one deliberate difference: the
+ * reference COMPUTES a missing expert on the CPU and a device kernel spins on a host flag for the answer; here a miss
+ * is a COPY (host -> slot over the same stream) and every expert is computed on the GPU, so no kernel ever waits on
+ * the host and this library keeps having no CPU arithmetic path.
+ *
+ * b200moe_residency_map, per window and in stream order: marks the experts the ids use, waits for that mark list on
+ * the host (one stream synchronisation: the only host wait), copies the missing experts into victim slots, updates the
+ * device table and writes slot_ids[i] = slot of ids[i] (0xffffffff for an id >= experts, which the routes builder then
+ * flags as invalid). The caller runs b200moe_layer / b200moe_ffn stages with shape.experts = slots, the slot tensors
+ * and slot_ids. Results equal the all-resident run bit for bit in the FMA_SLOTS combine form (slot order does not depend
+ * on the expert numbers); the PARTS form orders by expert id and is therefore not offered through slot ids.
+ * A window that uses more distinct experts than there are slots is refused (B200MOE_ERR_WORKSPACE), state unchanged. */
+typedef struct b200moe_residency_desc {
+    b200moe_shape shape;          /* experts = all experts of the layer */
+    const uint8_t* gate_host;     /* full tensors in host memory (pinned memory makes the copies asynchronous) */
+    const uint8_t* up_host;
+    const uint8_t* down_host;
+    uint32_t slots;               /* 1 .. experts */
+    uint8_t* gate_slots;          /* device, slots x per-expert bytes (b200moe_gate_row_bytes * inter) */
+    uint8_t* up_slots;
+    uint8_t* down_slots;          /* device, slots x b200moe_down_row_bytes * hidden */
+    float decay;                  /* score decay per window, 0 = 0.97 (the reference planner's default) */
+} b200moe_residency_desc;
+typedef struct b200moe_residency_stats {
+    uint64_t windows, hits, misses, evictions, bytes_loaded; /* hits / misses count distinct experts per window */
+} b200moe_residency_stats;
+int b200moe_residency_create(const b200moe_residency_desc* desc, void** residency);
+void b200moe_residency_destroy(void* residency);
+int b200moe_residency_map(void* residency, const uint32_t* ids, uint32_t count, uint32_t* slot_ids, void* stream);
+int b200moe_residency_get_stats(const void* residency, b200moe_residency_stats* out);
+/* expert -> slot or -1, host copy of the table ([experts]). */
+int b200moe_residency_table(const void* residency, int32_t* table_host);
+/* The eviction rule on its own (pure host function, no CUDA): slot_expert [slots] (expert in the slot or -1), score
+ * [experts], used [experts] (1 = the window uses it), missing [n_missing] -> victims [n_missing] (slot for each missing
+ * expert, in order): free slots ascending first, then the slots whose expert the window does not use by (score ascending,
+ * expert ascending). B200MOE_ERR_WORKSPACE when there are fewer such slots than missing experts (nothing written). */
+int b200moe_residency_choose_victims(const int32_t* slot_expert, uint32_t slots, const double* score, const uint8_t* used,
+                                     uint32_t experts, const uint32_t* missing, uint32_t n_missing, uint32_t* victims);
+
 #ifdef __cplusplus
 }
 #endif

@@ -124,6 +124,15 @@ class GgufMoeLayer(C.Structure):
     _fields_ = [("gate", GgufTensorInfo), ("up", GgufTensorInfo), ("down", GgufTensorInfo), ("router", GgufTensorInfo), ("shape", Shape)]
 
 
+class ResidencyDesc(C.Structure):
+    _fields_ = [("shape", Shape), ("gate_host", vp), ("up_host", vp), ("down_host", vp), ("slots", u32), ("gate_slots", vp),
+                ("up_slots", vp), ("down_slots", vp), ("decay", f32)]
+
+
+class ResidencyStats(C.Structure):
+    _fields_ = [("windows", u64), ("hits", u64), ("misses", u64), ("evictions", u64), ("bytes_loaded", u64)]
+
+
 # every symbol include/b200moe.h declares (tests check that the library exports each of them)
 EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_quantize_a8", "b200moe_rmsnorm_a8", "b200moe_q8_0_a8",
            "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_routes_static_max_words",
@@ -132,6 +141,8 @@ EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", 
            "b200moe_canonical_sum", "b200moe_fold_parts", "b200moe_select_owner_slots", "b200moe_peer_buffer_create",
            "b200moe_peer_buffer_open", "b200moe_peer_buffer_close", "b200moe_peer_buffer_destroy", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
            "b200moe_ffn", "b200moe_ffn_host", "b200moe_dense_ffn", "b200moe_gguf_open", "b200moe_gguf_close",
+           "b200moe_residency_create", "b200moe_residency_destroy", "b200moe_residency_map",
+           "b200moe_residency_get_stats", "b200moe_residency_table", "b200moe_residency_choose_victims",
            "b200moe_gguf_tensor_count", "b200moe_gguf_data_offset", "b200moe_gguf_alignment", "b200moe_gguf_tensor_at", "b200moe_gguf_find",
            "b200moe_gguf_find_moe_layer"]
 
@@ -179,6 +190,18 @@ def lib():
         L.b200moe_gguf_find.argtypes = [vp, C.c_char_p, C.POINTER(GgufTensorInfo)]
         L.b200moe_gguf_find_moe_layer.restype = C.c_int
         L.b200moe_gguf_find_moe_layer.argtypes = [vp, u32, C.POINTER(GgufMoeLayer)]
+        L.b200moe_residency_create.restype = C.c_int
+        L.b200moe_residency_create.argtypes = [C.POINTER(ResidencyDesc), C.POINTER(vp)]
+        L.b200moe_residency_destroy.restype = None
+        L.b200moe_residency_destroy.argtypes = [vp]
+        L.b200moe_residency_map.restype = C.c_int
+        L.b200moe_residency_map.argtypes = [vp, vp, u32, vp, vp]
+        L.b200moe_residency_get_stats.restype = C.c_int
+        L.b200moe_residency_get_stats.argtypes = [vp, C.POINTER(ResidencyStats)]
+        L.b200moe_residency_table.restype = C.c_int
+        L.b200moe_residency_table.argtypes = [vp, vp]
+        L.b200moe_residency_choose_victims.restype = C.c_int
+        L.b200moe_residency_choose_victims.argtypes = [vp, u32, vp, vp, u32, vp, u32, vp]
         L.b200moe_peer_buffer_create.restype = C.c_int
         L.b200moe_peer_buffer_create.argtypes = [u64, C.POINTER(vp), vp]
         L.b200moe_peer_buffer_open.restype = C.c_int
