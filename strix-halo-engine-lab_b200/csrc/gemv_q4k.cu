@@ -72,17 +72,28 @@ __device__ __forceinline__ void q4k_row(const u8* __restrict__ wrow, u32 nblocks
     float acc[kR];
 #pragma unroll
     for (int r = 0; r < kR; ++r) acc[r] = 0.0f;
+    // The loads of step b0 + BPI are issued before the arithmetic of step b0 (one step of register prefetch): the row walk
+    // is otherwise a chain of load -> dot -> shuffle with nothing in flight.
+    struct Blk { uint4 hdr, q0, q1, h0, h1; };
+    auto load_blk = [&](u32 b) {
+        Blk k;
+        k.hdr = make_uint4(0, 0, 0, 0); k.q0 = k.hdr; k.q1 = k.hdr; k.h0 = k.hdr; k.h1 = k.hdr;
+        if (b < nblocks) {
+            const uint4* blk = reinterpret_cast<const uint4*>(wrow + u64(b) * (Q5K ? kQ5KBlock : kQ4KBlock));
+            k.hdr = __ldg(blk);
+            if (Q5K) { k.h0 = __ldg(blk + 1); k.h1 = __ldg(blk + 2); }  // Q5_K: 32 bytes of high bits between header and nibbles
+            k.q0 = __ldg(blk + (Q5K ? 3 : 1) + 2 * p);
+            k.q1 = __ldg(blk + (Q5K ? 4 : 2) + 2 * p);
+        }
+        return k;
+    };
+    Blk nxt = load_blk(bsub);
     for (u32 b0 = 0; b0 < nblocks; b0 += BPI) {
         const u32 b = b0 + bsub;
         const bool valid = b < nblocks;
-        uint4 hdr = make_uint4(0, 0, 0, 0), q0 = hdr, q1 = hdr, h0 = hdr, h1 = hdr;
-        if (valid) {
-            const uint4* blk = reinterpret_cast<const uint4*>(wrow + u64(b) * (Q5K ? kQ5KBlock : kQ4KBlock));
-            hdr = __ldg(blk);
-            if (Q5K) { h0 = __ldg(blk + 1); h1 = __ldg(blk + 2); }  // Q5_K: 32 bytes of high bits between header and nibbles
-            q0 = __ldg(blk + (Q5K ? 3 : 1) + 2 * p);
-            q1 = __ldg(blk + (Q5K ? 4 : 2) + 2 * p);
-        }
+        const Blk cur = nxt;
+        nxt = load_blk(b + BPI);
+        const uint4 hdr = cur.hdr, q0 = cur.q0, q1 = cur.q1, h0 = cur.h0, h1 = cur.h1;
         const float d = half_bits_to_float(hdr.x & 0xffffu), dm = half_bits_to_float(hdr.x >> 16);
         float Dl, DMl, Dh, DMh;
         q4k_factor(hdr, 2 * p, d, dm, &Dl, &DMl);
