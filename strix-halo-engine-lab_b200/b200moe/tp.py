@@ -10,6 +10,8 @@ takes the all-reduce anyway (one collective less on the wire, sum order not pinn
 
 x is replicated on every rank. The collectives are torch.distributed's; the arithmetic is the C library's.
 """
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
@@ -33,7 +35,30 @@ class DeviceDenseKernels:
         self.shape, self.gate, self.up, self.down = shape_local, gate, up, down
 
     def partial(self, x):
-        return ops.enqueue_dense_ffn(self.shape, self.gate, self.up, self.down, ops.enqueue_quantize_a8(x))
+        """The rank's partial sum [rows][hidden]. Workspace, A8 rows and output are kept per row count (the caller-owned
+        buffers of the C contract): a step is then two library calls and no allocation. The output is overwritten by the
+        next call with the same row count."""
+        from . import A8Rows, DenseView, ExpertWeights, QuantizeA8View
+        rows, width = x.shape
+        buf = self._buffers.get(rows) if hasattr(self, "_buffers") else None
+        if buf is None:
+            if not hasattr(self, "_buffers"):
+                self._buffers = {}
+            dev = self.gate.device
+            ws_bytes = int(lib().b200moe_layer_workspace_bytes(C.byref(self.shape), rows))
+            buf = dict(ws=torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev), ws_bytes=ws_bytes,
+                       codes=torch.empty((rows, width), dtype=torch.int8, device=dev),
+                       deltas=torch.empty((rows, width // 32), dtype=torch.float32, device=dev),
+                       sums=torch.empty((rows, width // 32), dtype=torch.int32, device=dev),
+                       y=torch.empty((rows, self.shape.hidden), dtype=torch.float32, device=dev))
+            self._buffers[rows] = buf
+        a8 = A8Rows(ptr(buf["codes"]), ptr(buf["deltas"]), ptr(buf["sums"]), rows, width, width)
+        q = QuantizeA8View(ptr(x), rows, width, x.stride(0), int(x.dtype == torch.bfloat16), a8, None)
+        check(lib().b200moe_quantize_a8(C.byref(q), stream_ptr()))
+        v = DenseView(self.shape, ExpertWeights(ptr(self.gate), ptr(self.up), ptr(self.down)), rows, a8, ptr(buf["y"]), None,
+                      ptr(buf["ws"]), buf["ws_bytes"])
+        check(lib().b200moe_dense_ffn(C.byref(v), stream_ptr()))
+        return buf["y"]
 
     def fold(self, parts):
         world, rows, hidden = parts.shape
