@@ -133,6 +133,8 @@ class ResidencyStats(C.Structure):
     _fields_ = [("windows", u64), ("hits", u64), ("misses", u64), ("evictions", u64), ("bytes_loaded", u64)]
 
 
+ABI_VERSION = 2  # B200MOE_ABI_VERSION of include/b200moe.h: the layout of the views mirrored above
+
 # every symbol include/b200moe.h declares (tests check that the library exports each of them)
 EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_quantize_a8", "b200moe_rmsnorm_a8", "b200moe_q8_0_a8",
            "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_routes_static_max_words",

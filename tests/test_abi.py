@@ -30,7 +30,7 @@ def test_exports_match_header(lib):
     assert declared == set(b200moe.EXPORTS), declared ^ set(b200moe.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.b200moe_abi_version() == 2
+    assert lib.b200moe_abi_version() == b200moe.ABI_VERSION == header_abi_version()
 
 
 def test_struct_layouts(tmp_path):
@@ -43,7 +43,9 @@ def test_struct_layouts(tmp_path):
              "b200moe_expert_weights": b200moe.ExpertWeights, "b200moe_gate_up_view": b200moe.GateUpView,
              "b200moe_down_view": b200moe.DownView, "b200moe_combine_view": b200moe.CombineView,
              "b200moe_layer_view": b200moe.LayerView, "b200moe_ffn_view": b200moe.FfnView,
-             "b200moe_dense_view": b200moe.DenseView}
+             "b200moe_dense_view": b200moe.DenseView, "b200moe_rmsnorm_view": b200moe.RmsnormView,
+             "b200moe_residency_desc": b200moe.ResidencyDesc, "b200moe_residency_stats": b200moe.ResidencyStats,
+             "b200moe_gguf_tensor_info": b200moe.GgufTensorInfo, "b200moe_gguf_moe_layer": b200moe.GgufMoeLayer}
     src = tmp_path / "sizes.c"
     body = "\n".join(f'    printf("{n} %zu\\n", sizeof({n}));' for n in names)
     src.write_text(f'#include <stdio.h>\n#include "{HEADER}"\nint main(void) {{\n{body}\n    return 0;\n}}\n')
@@ -96,3 +98,15 @@ def test_no_cpu_fallback(lib):
     assert b"no CPU fallback" in lib.b200moe_last_error()
     with pytest.raises(b200moe.B200MoeError):
         b200moe.check(lib.b200moe_quantize_a8(v, None))
+
+
+def header_abi_version():
+    import re
+    text = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "b200moe.h")).read()
+    return int(re.search(r"#define\s+B200MOE_ABI_VERSION\s+(\d+)", text).group(1))
+
+
+def test_graft_entry_build_runs():
+    """build() compiles (incrementally) the library and the oracle and checks exports and ABI version: what the build check runs."""
+    import __graft_entry__ as entry
+    entry.build()
