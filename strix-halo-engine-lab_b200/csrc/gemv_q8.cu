@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(1024) gate_up_q8_kernel(b200moe_gate_up_view v
         run_load((warp < 32 ? gate : up) + u64(warp & 31u) * row_bytes, min(32u, groups), lane, pre);
         have_pre = true;
     }
-    for (u32 p0 = eb; p0 < ee; p0 += kR) {
+    for (u32 p0 = eb + kR * blockIdx.z; p0 < ee; p0 += kR * gridDim.z) {  // grid.z shares an expert's passes of kR entries
         const int nr = static_cast<int>(min(u32(kR), ee - p0));
         __syncthreads();
         if (threadIdx.x < (u32)nr) { s_rows[threadIdx.x] = v.routes.rows[p0 + threadIdx.x]; s_slots[threadIdx.x] = v.routes.slots[p0 + threadIdx.x]; }
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(1024) down_q8_kernel(b200moe_down_view v, u32 
         run_load(down + u64(warp) * row_bytes, min(32u, groups), lane, pre);
         have_pre = true;
     }
-    for (u32 p0 = eb; p0 < ee; p0 += kR) {
+    for (u32 p0 = eb + kR * blockIdx.z; p0 < ee; p0 += kR * gridDim.z) {  // grid.z shares an expert's passes of kR entries
         const int nr = static_cast<int>(min(u32(kR), ee - p0));
         __syncthreads();
         if (threadIdx.x < (u32)nr) s_slots[threadIdx.x] = v.routes.slots[p0 + threadIdx.x];
@@ -295,6 +295,14 @@ int launch_q8_0_a8(const b200moe_q8a8_view& v, cudaStream_t stream) {
     return after_launch("q8_0_a8");
 }
 
+// An expert with many entries (the dense shared expert over a token block) is walked in passes of kR entries; when the
+// grid of (output groups x experts) would leave SMs idle, grid.z shares the passes: up to 16 ways, never more than the
+// passes `entries_bound` entries can need, until there are two CTAs per SM.
+static u32 pass_split(u32 ctas, u32 entries_bound) {
+    const u32 passes = std::max(1u, (entries_bound + kR - 1) / kR), want = (2u * 148u + ctas - 1) / std::max(1u, ctas);
+    return std::max(1u, std::min(std::min(passes, want), 16u));
+}
+
 int launch_gate_up_q8(const b200moe_gate_up_view& v, cudaStream_t stream) {
     if (v.max_union == 0) return B200MOE_OK;
     const u32 H = v.shape.hidden, I = v.shape.inter;
@@ -302,7 +310,7 @@ int launch_gate_up_q8(const b200moe_gate_up_view& v, cudaStream_t stream) {
     const u32 nw = kRoutedWarps;   // 64 weight rows per CTA: two per warp, the second one prefetched
     const u32 smem = kR * (H + H / 32 * 4) + 2 * kR * 32 * 4 + nw * kStageBytes;
     if (int rc = set_smem(gate_up_q8_kernel, smem)) return rc;
-    gate_up_q8_kernel<<<dim3(I / 32, v.max_union), nw * 32, smem, stream>>>(v, align);
+    gate_up_q8_kernel<<<dim3(I / 32, v.max_union, pass_split(I / 32 * v.max_union, v.x.rows)), nw * 32, smem, stream>>>(v, align);
     return after_launch("gate_up_q8");
 }
 
@@ -313,7 +321,7 @@ int launch_down_q8(const b200moe_down_view& v, cudaStream_t stream) {
     const u32 nw = kRoutedWarps;   // 32 weight rows per CTA: one per warp, every row of the expert in flight at once
     const u32 smem = kR * (I + I / 32 * 4) + nw * kStageBytes;
     if (int rc = set_smem(down_q8_kernel, smem)) return rc;
-    down_q8_kernel<<<dim3(H / 32, v.max_union), nw * 32, smem, stream>>>(v, align);
+    down_q8_kernel<<<dim3(H / 32, v.max_union, pass_split(H / 32 * v.max_union, v.act.rows)), nw * 32, smem, stream>>>(v, align);
     return after_launch("down_q8");
 }
 
