@@ -647,6 +647,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="config 4 arm: launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-peer-return", action="store_true",
                     help="expert parallelism, PARTS form: return the partial sums with an NCCL all-to-all instead of the combine kernel's peer stores")
+    ap.add_argument("--form", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="Q4_K decode GEMV form: 0 = by plan, 1 = row streaming, 2 = segment streaming, 3 = per block (measurement hook)")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
                     help="N > 1: independent replicas (rows sharded, weights replicated, no collective) or expert parallelism "
                          "(experts / N per rank, all-gather dispatch + all-to-all return over NCCL)")
@@ -662,6 +664,8 @@ def main():
     from b200moe import ops, synth
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    if args.form:
+        b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, args.form)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:

@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 2
+#define B200MOE_ABI_VERSION 3
 
 /* Status codes (values follow strix::weight::Error's role, include/strix/weight/types.hpp:35-40). */
 enum {
@@ -39,7 +39,8 @@ enum {
     B200MOE_ERR_UNSUPPORTED = 2,      /* a format / policy this build does not bind */
     B200MOE_ERR_WORKSPACE = 3,        /* caller-owned scratch is missing or too small */
     B200MOE_ERR_CUDA = 4,             /* a CUDA runtime call failed (text in b200moe_last_error) */
-    B200MOE_ERR_COMM = 5              /* an NCCL call failed */
+    B200MOE_ERR_COMM = 5,             /* an NCCL call failed */
+    B200MOE_ERR_ABORTED = 6           /* a bounded device wait ran out (B200MOE_JOB_WAIT_ABORTED): the outputs are not valid */
 };
 
 /* ggml tensor type ids of the stored expert tensors (include/strix/cuda/qwen_moe.hpp:33). */
@@ -55,12 +56,28 @@ enum {
 #define B200MOE_ROW_NONFINITE_ACTIVATION 2u
 #define B200MOE_ROW_INVALID_DELTA 4u
 #define B200MOE_ROW_PROJECTION_NONFINITE 8u
+/* Job summary only: a bounded wait inside a kernel of the job ran out (a copy that never landed, a peer that never
+ * signalled). Every wait on the device has a poll limit instead of hanging (the reference's bounded wait with a watchdog,
+ * src/cuda/tiered_experts.cu:107-127); the kernel that gives up sets this bit and returns, later stages of the job see it and
+ * write nothing (down, combine), so y keeps what the caller put there. The *_host call returns B200MOE_ERR_ABORTED. */
+#define B200MOE_JOB_WAIT_ABORTED 0x40000000u
 
 int b200moe_abi_version(void);
 /* Text of the last failure on the calling thread ("" when none). Valid until the thread's next failing call. */
 const char* b200moe_last_error(void);
 /* Number of kernels this library has launched in the calling process (all threads); a plain counter for reports. */
 uint64_t b200moe_launch_count(void);
+
+/* Test and measurement hooks: process-wide values read when a kernel is launched. They exist so that the tests can make a
+ * bounded wait run out WITHOUT a device fault and so that the forms of the decode GEMVs can be compared on one input; a
+ * production caller never sets them. The reference has the same kind of seam (TierDev::timeout_ns,
+ * src/cuda/tiered_experts.cu:107-127). Returns B200MOE_ERR_INVALID_ARGUMENT for an unknown key. */
+#define B200MOE_DEBUG_WAIT_LIMIT 0u  /* polls of every bounded wait in the streaming kernels; 0 = the default (2^22) */
+#define B200MOE_DEBUG_STALL_STAGE 1u /* n > 0: in every CTA of the segment-streaming kernels the first producer stops feeding
+                                      * before its n-th stage (no copy of that stage is issued, none is left in flight); 0 = never */
+#define B200MOE_DEBUG_DECODE_FORM 2u /* Q4_K decode windows: 0 = chosen by the plan, 1 = row streaming, 2 = segment streaming,
+                                      * 3 = per-block (each only where it applies) */
+int b200moe_debug_set(uint32_t key, uint32_t value);
 
 /* ------------------------------------------------------------------------------------------------ A8 activations
  * A8 rows: codes [row][stride] int8, deltas / sums [row][stride / 32]; width <= stride, both multiples of 32.
@@ -296,6 +313,7 @@ typedef struct b200moe_combine_view {
      * y_blocks[r / y_block_rows] + (r % y_block_rows) * hidden. When set, y may be NULL and y_bf16 must be NULL. */
     float* const* y_blocks;
     uint32_t y_block_rows;
+    const uint32_t* summary;   /* optional job summary: with B200MOE_JOB_WAIT_ABORTED set nothing is written */
 } b200moe_combine_view;
 int b200moe_combine(const b200moe_combine_view* view, void* stream);
 
@@ -356,6 +374,8 @@ typedef struct b200moe_layer_view {
     void* const* stage_events;
     float* const* y_blocks;     /* optional, with y_block_rows: see b200moe_combine_view */
     uint32_t y_block_rows;
+    uint32_t* summary;          /* optional [1]: receives the job summary (OR of the row status bits and B200MOE_JOB_WAIT_ABORTED);
+                                 * cleared by the call. NULL: the word stays in the workspace */
 } b200moe_layer_view;
 uint64_t b200moe_layer_workspace_bytes(const b200moe_shape* shape, uint32_t capacity);
 int b200moe_layer(const b200moe_layer_view* view, void* stream);
@@ -383,12 +403,14 @@ typedef struct b200moe_ffn_view {
     uint32_t capacity;
     uint32_t grouped_min_rows;
     void* const* stage_events;   /* passed to the layer (see b200moe_layer_view) */
+    uint32_t* summary;           /* optional [1]: the job summary (see b200moe_layer_view) */
 } b200moe_ffn_view;
 uint64_t b200moe_ffn_workspace_bytes(const b200moe_shape* shape, uint32_t capacity);
 int b200moe_ffn(const b200moe_ffn_view* view, void* stream);
 /* The same call from HOST activations: x_host / y_host are host buffers (pinned for overlap); the call copies
  * x to the workspace, runs b200moe_ffn, copies y back and waits for the stream: what a caller holding tokens in host
- * memory pays end to end. view->x and view->y are ignored. */
+ * memory pays end to end. view->x and view->y are ignored. Having waited, it reads the job summary: B200MOE_ERR_ABORTED
+ * when a bounded device wait ran out (y_host is then not valid). */
 int b200moe_ffn_host(const b200moe_ffn_view* view, const void* x_host, float* y_host, void* stream);
 
 /* Dense SwiGLU FFN block (one "expert" applied to every row): y_partial[r] = down . A8(swiglu(gate . x_r, up . x_r))

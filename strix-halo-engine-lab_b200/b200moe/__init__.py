@@ -11,9 +11,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB_PATH = os.path.join(PKG, "libb200moe.so")
 
-OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_COMM = range(6)
+OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_COMM, ERR_ABORTED = range(7)
 TYPE_Q8_0, TYPE_Q4_K = 8, 12
 ROW_INVALID_ROUTE, ROW_NONFINITE_ACTIVATION, ROW_INVALID_DELTA, ROW_PROJECTION_NONFINITE = 1, 2, 4, 8
+JOB_WAIT_ABORTED = 0x40000000
+DEBUG_WAIT_LIMIT, DEBUG_STALL_STAGE, DEBUG_DECODE_FORM = 0, 1, 2
+FORM_AUTO, FORM_ROW_STREAM, FORM_SEGMENT_STREAM, FORM_PER_BLOCK = 0, 1, 2, 3
 SCORE_SOFTMAX, SCORE_SIGMOID, SCORE_SQRT_SOFTPLUS = 0, 1, 2
 KEY_FLOAT_SERIAL, KEY_ORDERED_BITS = 0, 1
 ORDER_SELECTION, ORDER_ASCENDING_ID = 0, 1
@@ -92,7 +95,7 @@ class DownView(C.Structure):
 class CombineView(C.Structure):
     _fields_ = [("raw", vp), ("shared", vp), ("weights", vp), ("ids", vp), ("order", vp), ("rows", u32), ("top_k", u32),
                 ("hidden", u32), ("form", u32), ("parts", u32), ("part_experts", u32), ("only_part", i32), ("y", vp),
-                ("y_bf16", vp), ("row_status", vp), ("y_blocks", vp), ("y_block_rows", u32)]
+                ("y_bf16", vp), ("row_status", vp), ("y_blocks", vp), ("y_block_rows", u32), ("summary", vp)]
 
 
 class LayerView(C.Structure):
@@ -100,7 +103,7 @@ class LayerView(C.Structure):
                 ("shared", vp), ("first", u32), ("end", u32), ("base", u32), ("combine_form", u32), ("parts", u32),
                 ("part_experts", u32), ("only_part", i32), ("raw", vp), ("y", vp), ("y_bf16", vp), ("row_status", vp),
                 ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32), ("stage_events", vp),
-                ("y_blocks", vp), ("y_block_rows", u32)]
+                ("y_blocks", vp), ("y_block_rows", u32), ("summary", vp)]
 
 
 class FfnView(C.Structure):
@@ -108,7 +111,7 @@ class FfnView(C.Structure):
                 ("select_bias", vp), ("x", vp), ("x_is_bf16", u32), ("rows", u32), ("shared", vp), ("combine_form", u32),
                 ("parts", u32), ("part_experts", u32), ("y", vp), ("y_bf16", vp), ("ids", vp), ("route_weights", vp),
                 ("row_status", vp), ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32),
-                ("stage_events", vp)]
+                ("stage_events", vp), ("summary", vp)]
 
 
 class DenseView(C.Structure):
@@ -133,10 +136,10 @@ class ResidencyStats(C.Structure):
     _fields_ = [("windows", u64), ("hits", u64), ("misses", u64), ("evictions", u64), ("bytes_loaded", u64)]
 
 
-ABI_VERSION = 2  # B200MOE_ABI_VERSION of include/b200moe.h: the layout of the views mirrored above
+ABI_VERSION = 3  # B200MOE_ABI_VERSION of include/b200moe.h: the layout of the views mirrored above
 
 # every symbol include/b200moe.h declares (tests check that the library exports each of them)
-EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_quantize_a8", "b200moe_rmsnorm_a8", "b200moe_q8_0_a8",
+EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_debug_set", "b200moe_quantize_a8", "b200moe_rmsnorm_a8", "b200moe_q8_0_a8",
            "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_routes_static_max_words",
            "b200moe_build_routes_static", "b200moe_gate_row_bytes",
            "b200moe_down_row_bytes", "b200moe_expert_bytes", "b200moe_gate_up", "b200moe_down", "b200moe_combine",
@@ -160,6 +163,8 @@ def lib():
         L = C.CDLL(LIB_PATH)
         L.b200moe_last_error.restype = C.c_char_p
         L.b200moe_launch_count.restype = u64
+        L.b200moe_debug_set.restype = C.c_int
+        L.b200moe_debug_set.argtypes = [u32, u32]
         for n in ("b200moe_gate_row_bytes", "b200moe_down_row_bytes", "b200moe_expert_bytes"):
             getattr(L, n).restype = u64
             getattr(L, n).argtypes = [C.POINTER(Shape)]
@@ -228,6 +233,11 @@ def check(rc):
     if rc == ERR_INVALID_ARGUMENT:
         raise InvalidArgument(rc, text)
     raise B200MoeError(rc, text)
+
+
+def debug_set(key, value):
+    """b200moe_debug_set: a process-wide test / measurement hook (DEBUG_* keys). Tests restore 0 when done."""
+    check(lib().b200moe_debug_set(key, value))
 
 
 def launch_count():

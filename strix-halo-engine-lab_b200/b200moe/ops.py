@@ -133,13 +133,13 @@ def enqueue_routed_down(shape, down, routes, max_union, act, raw=None, summary=N
 
 
 def enqueue_moe_combine(form, raw, weights, ids, order=None, shared=None, parts=2, part_experts=1, only_part=-1, bf16=False,
-                        row_status=None):
+                        row_status=None, summary=None, fill=0.0):
     rows, top_k = ids.shape
     hidden = raw.shape[1]
-    y = torch.zeros((rows, hidden), dtype=torch.float32, device=raw.device)
+    y = torch.full((rows, hidden), fill, dtype=torch.float32, device=raw.device)
     yb = torch.zeros((rows, hidden), dtype=torch.bfloat16, device=raw.device) if bf16 else None
     v = CombineView(ptr(raw), ptr(shared), ptr(weights), ptr(ids), ptr(order), rows, top_k, hidden, form, parts, part_experts,
-                    only_part, ptr(y), ptr(yb), ptr(row_status))
+                    only_part, ptr(y), ptr(yb), ptr(row_status), None, 0, ptr(summary))
     check(lib().b200moe_combine(C.byref(v), stream_ptr()))
     return (y, yb) if bf16 else y
 
@@ -202,26 +202,29 @@ class MoeFfn:
         """Eight cudaEvent_t values (ints or None) as the array the views point to; the caller keeps it alive."""
         return (C.c_void_p * 8)(*handles)
 
-    def _view(self, rows, x, y, ids=None, wts=None, shared=None, row_status=None, events=None):
+    def _view(self, rows, x, y, ids=None, wts=None, shared=None, row_status=None, events=None, summary=None, x_is_bf16=None):
         ev = C.cast(events, C.c_void_p) if events is not None else None
+        if x_is_bf16 is None:
+            x_is_bf16 = x is not None and x.dtype == torch.bfloat16
         return FfnView(self.shape, ExpertWeights(ptr(self.gate), ptr(self.up), ptr(self.down)), self.policy, ptr(self.router_weight),
-                       ptr(self.logit_bias), ptr(self.select_bias), ptr(x), 0, rows, ptr(shared), self.combine_form, self.parts,
+                       ptr(self.logit_bias), ptr(self.select_bias), ptr(x), int(x_is_bf16), rows, ptr(shared), self.combine_form, self.parts,
                        self.part_experts, ptr(y), None, ptr(ids), ptr(wts), ptr(row_status), ptr(self.ws), self.ws_bytes,
-                       self.capacity, self.grouped_min_rows, ev)
+                       self.capacity, self.grouped_min_rows, ev, ptr(summary))
 
-    def __call__(self, x, y=None, shared=None, want_routes=False, row_status=None):
+    def __call__(self, x, y=None, shared=None, want_routes=False, row_status=None, summary=None):
+        """x: [rows][hidden] float32 or bfloat16 (widened exactly before the router and the A8 quantiser)."""
         rows = x.shape[0]
         if y is None:
             y = torch.empty((rows, self.shape.hidden), dtype=torch.float32, device=x.device)
         ids = torch.empty((rows, self.shape.top_k), dtype=torch.int32, device=x.device) if want_routes else None
         wts = torch.empty((rows, self.shape.top_k), dtype=torch.float32, device=x.device) if want_routes else None
-        v = self._view(rows, x, y, ids, wts, shared, row_status)
+        v = self._view(rows, x, y, ids, wts, shared, row_status, summary=summary)
         check(lib().b200moe_ffn(C.byref(v), stream_ptr()))
         return (y, ids, wts) if want_routes else y
 
     def host(self, x_host, y_host):
         """x_host / y_host: pinned host tensors; copies in, runs, copies out and waits (the end-to-end call)."""
-        v = self._view(x_host.shape[0], None, None)
+        v = self._view(x_host.shape[0], None, None, x_is_bf16=x_host.dtype == torch.bfloat16)
         check(lib().b200moe_ffn_host(C.byref(v), x_host.data_ptr(), y_host.data_ptr(), stream_ptr()))
         return y_host
 

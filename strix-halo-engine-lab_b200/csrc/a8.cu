@@ -1,6 +1,8 @@
 // A8 activation quantiser: one warp per (row, 32-value group), one value per lane.
 // Contract: src/cpu/core/reference.cpp:35-55 (= src/ds41_formats.cpp:146-165).
 // HBM traffic per row: width * 4 B in (2 B for bfloat16), width * 1.25 B out: negligible beside the expert weights.
+#include <algorithm>
+
 #include "kernels.cuh"
 
 namespace b200moe {
@@ -32,7 +34,20 @@ __global__ void __launch_bounds__(256) quantize_a8_kernel(const void* __restrict
     }
 }
 
+// bfloat16 bit patterns widened to FP32 (exact): the router reads FP32 rows.
+__global__ void __launch_bounds__(256) widen_bf16_kernel(const u16* __restrict__ in, float* __restrict__ out, u64 count) {
+    for (u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += u64(gridDim.x) * blockDim.x)
+        out[i] = __uint_as_float(static_cast<u32>(in[i]) << 16);
+}
+
 }  // namespace
+
+int launch_widen_bf16(const u16* in, float* out, u64 count, cudaStream_t stream) {
+    if (count == 0) return B200MOE_OK;
+    const u32 blocks = static_cast<u32>(std::min<u64>((count + 255) / 256, 148u * 16u));
+    widen_bf16_kernel<<<blocks, 256, 0, stream>>>(in, out, count);
+    return after_launch("widen_bf16");
+}
 
 int launch_quantize_a8(const b200moe_quantize_a8_view& v, cudaStream_t stream) {
     const u32 groups = v.width / 32;

@@ -83,6 +83,11 @@ int prefer_max_shared(const void* kernel) {
 }
 
 namespace {
+std::atomic<u32> g_debug[3] = {{0}, {0}, {0}};
+}
+u32 debug_value(u32 key) { return key < 3 ? g_debug[key].load(std::memory_order_relaxed) : 0u; }
+
+namespace {
 
 constexpr u32 kMaxExperts = 1024, kMaxTopK = 32;
 
@@ -177,6 +182,7 @@ struct FfnScratch {
     float* weights;
     void* x_dev;
     float* y_dev;
+    float* x_f32;  // bfloat16 activations widened for the router
     void* layer;
     u64 bytes;
 };
@@ -192,6 +198,7 @@ FfnScratch carve_ffn(void* ws, const b200moe_shape& s, u32 capacity) {
     F.weights = c.take<float>(u64(capacity) * s.top_k);
     F.x_dev = c.take<float>(u64(capacity) * s.hidden);
     F.y_dev = c.take<float>(u64(capacity) * s.hidden);
+    F.x_f32 = c.take<float>(u64(capacity) * s.hidden);
     const u64 at = (c.used + 255) & ~u64(255);
     F.layer = ws ? static_cast<unsigned char*>(ws) + at : nullptr;
     F.bytes = at + carve_layer(nullptr, s, capacity).bytes;
@@ -214,15 +221,39 @@ bool use_grouped(const b200moe_shape& s, u32 rows, u32 grouped_min_rows, bool ha
     const u32 least = grouped_min_rows ? grouped_min_rows : kGroupedDefaultRows;
     return rows >= least && grouped_fits(s, have_sums);
 }
+// Decode forms of the Q4_K GEMVs: windows of up to kRowStreamRows rows whose whole A8 window fits beside the ring take
+// the row-streaming form, everything else the segment-streaming form (any row length), the per-block form being what is
+// left. B200MOE_DEBUG_DECODE_FORM forces one of them where it applies.
+constexpr u32 kRowStreamRows = 8;
+enum class DecodeForm { row_stream, wide, block };
+DecodeForm pick_decode_form(bool row_stream_fits, bool wide_fits, u32 rows) {
+    const u32 forced = debug_value(B200MOE_DEBUG_DECODE_FORM);
+    if (forced == 1 && row_stream_fits) return DecodeForm::row_stream;
+    if (forced == 2 && wide_fits) return DecodeForm::wide;
+    if (forced == 3) return DecodeForm::block;
+    if (row_stream_fits && rows <= kRowStreamRows) return DecodeForm::row_stream;
+    if (wide_fits) return DecodeForm::wide;
+    return row_stream_fits ? DecodeForm::row_stream : DecodeForm::block;
+}
 int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
     if (!is_kquant(v.shape.gate_type)) return launch_gate_up_q8(v, st);
     if (v.shape.gate_type == B200MOE_TYPE_Q5_K) return launch_gate_up_q4k(v, st);  // the per-block form reads both K-quant layouts
     if (use_grouped(v.shape, rows, grouped_min_rows, v.x.sums != nullptr)) return launch_gate_up_q4k_grouped(v, st);
-    return stream_gate_up_fits(v, rows) ? launch_gate_up_q4k_stream(v, rows, st) : launch_gate_up_q4k(v, st);
+    switch (pick_decode_form(stream_gate_up_fits(v, rows), wide_gate_up_fits(v, rows), rows)) {
+        case DecodeForm::row_stream: return launch_gate_up_q4k_stream(v, rows, st);
+        case DecodeForm::wide: return launch_gate_up_q4k_wide(v, rows, st);
+        default: return launch_gate_up_q4k(v, st);
+    }
 }
 int enqueue_down(const b200moe_down_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
     if (v.shape.down_type == B200MOE_TYPE_Q4_K && use_grouped(v.shape, rows, grouped_min_rows, v.act.sums != nullptr)) return launch_down_q4k_grouped(v, st);
-    if (v.shape.down_type == B200MOE_TYPE_Q4_K) return stream_down_fits(v, rows) ? launch_down_q4k_stream(v, rows, st) : launch_down_q4k(v, st);
+    if (v.shape.down_type == B200MOE_TYPE_Q4_K) {
+        switch (pick_decode_form(stream_down_fits(v, rows), wide_down_fits(v, rows), rows)) {
+            case DecodeForm::row_stream: return launch_down_q4k_stream(v, rows, st);
+            case DecodeForm::wide: return launch_down_q4k_wide(v, rows, st);
+            default: return launch_down_q4k(v, st);
+        }
+    }
     return is_kquant(v.shape.gate_type) ? launch_down_q8_chain4(v, st) : launch_down_q8(v, st);  // chain4: Q8_0 and Q5_1 blocks
 }
 
@@ -236,6 +267,11 @@ extern "C" {
 int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }
 const char* b200moe_last_error(void) { return last_error_slot().c_str(); }
 uint64_t b200moe_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
+int b200moe_debug_set(uint32_t key, uint32_t value) {
+    B200_REQUIRE(key < 3, "debug_set: unknown key %u", key);
+    g_debug[key].store(value, std::memory_order_relaxed);
+    return B200MOE_OK;
+}
 
 uint64_t b200moe_gate_row_bytes(const b200moe_shape* s) { return s ? row_bytes_of(s->gate_type, s->hidden) : 0; }
 uint64_t b200moe_down_row_bytes(const b200moe_shape* s) { return s ? row_bytes_of(s->down_type, s->inter) : 0; }
@@ -393,8 +429,10 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
     cudaStream_t st = as_stream(stream);
 
     u32* row_status = v->row_status ? v->row_status : L.row_status;
+    u32* summary = v->summary ? v->summary : L.summary;
     if (!routes_ready) {
-        const cudaError_t ce = clear_status(L, !v->row_status, v->rows, st);
+        cudaError_t ce = clear_status(L, !v->row_status, v->rows, st);
+        if (ce == cudaSuccess && v->summary) ce = cudaMemsetAsync(v->summary, 0, sizeof(u32), st);
         if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "layer: cudaMemsetAsync: %s", cudaGetErrorString(ce));
     }
 
@@ -416,14 +454,14 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
 
     b200moe_gate_up_view gu{};
     gu.shape = s; gu.weights = v->weights; gu.routes = L.routes; gu.max_union = max_union;
-    gu.x = v->x; gu.act = L.act; gu.row_status = row_status; gu.summary = L.summary;
+    gu.x = v->x; gu.act = L.act; gu.row_status = row_status; gu.summary = summary;
     tap(2);
     if (int rc = enqueue_gate_up(gu, v->rows, st, v->grouped_min_rows)) return rc;
     tap(3);
 
     b200moe_down_view dn{};
     dn.shape = s; dn.weights = v->weights; dn.routes = L.routes; dn.max_union = max_union;
-    dn.act = L.act; dn.raw = raw; dn.summary = L.summary;
+    dn.act = L.act; dn.raw = raw; dn.summary = summary;
     tap(4);
     if (int rc = enqueue_down(dn, v->rows, st, v->grouped_min_rows)) return rc;
     tap(5);
@@ -436,6 +474,7 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
     cv.parts = v->parts; cv.part_experts = v->part_experts; cv.only_part = v->only_part;
     cv.y = v->y; cv.y_bf16 = v->y_bf16; cv.y_blocks = v->y_blocks; cv.y_block_rows = v->y_block_rows;
     cv.row_status = is_kquant(s.gate_type) ? row_status : nullptr;
+    cv.summary = summary;
     tap(6);
     const int rc = launch_combine(cv, st);
     tap(7);
@@ -464,12 +503,17 @@ int b200moe_ffn(const b200moe_ffn_view* v, void* stream) {
     if (!device_ready()) return B200MOE_ERR_CUDA;
     cudaStream_t st = as_stream(stream);
 
-    // The router reads FP32 rows (bfloat16 activations are widened by the A8 kernel only).
-    B200_REQUIRE(!v->x_is_bf16, "ffn: bfloat16 activations need the router logits from the caller (use b200moe_router + b200moe_layer)");
+    // The router reads FP32 rows: bfloat16 activations are widened once (exactly) into the workspace, and both the A8
+    // quantiser and the router read the widened rows (the Qwen prologue's input form, src/cuda/models/qwen/qwen_moe.cu:60-99).
+    const float* x32 = static_cast<const float*>(v->x);
+    if (v->x_is_bf16) {
+        if (int rc = launch_widen_bf16(static_cast<const u16*>(v->x), F.x_f32, u64(v->rows) * s.hidden, st)) return rc;
+        x32 = F.x_f32;
+    }
     b200moe_quantize_a8_view q{};
-    q.x = v->x; q.rows = v->rows; q.width = s.hidden; q.x_stride = s.hidden; q.x_is_bf16 = 0; q.out = F.x;
+    q.x = x32; q.rows = v->rows; q.width = s.hidden; q.x_stride = s.hidden; q.x_is_bf16 = 0; q.out = F.x;
     b200moe_router_view r{};
-    r.x = static_cast<const float*>(v->x); r.x_stride = s.hidden; r.rows = v->rows; r.hidden = s.hidden;
+    r.x = x32; r.x_stride = s.hidden; r.rows = v->rows; r.hidden = s.hidden;
     r.weight = v->router_weight; r.logit_bias = v->logit_bias; r.bias = v->select_bias; r.policy = v->policy;
     r.logits = F.logits; r.scores = F.logits;
     r.ids = v->ids ? v->ids : F.ids; r.weights = v->route_weights ? v->route_weights : F.weights;
@@ -480,7 +524,8 @@ int b200moe_ffn(const b200moe_ffn_view* v, void* stream) {
     b200moe_routes_view rv{};
     if (fused) {
         u32* row_status = v->row_status ? v->row_status : L.row_status;
-        const cudaError_t ce = clear_status(L, !v->row_status, v->rows, st);  // summary word, prologue ticket, row status
+        cudaError_t ce = clear_status(L, !v->row_status, v->rows, st);  // summary word, prologue ticket, row status
+        if (ce == cudaSuccess && v->summary) ce = cudaMemsetAsync(v->summary, 0, sizeof(u32), st);
         if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "ffn: cudaMemsetAsync: %s", cudaGetErrorString(ce));
         rv.ids = r.ids; rv.rows = v->rows; rv.top_k = s.top_k; rv.experts = s.experts;
         rv.split = v->part_experts ? v->part_experts : s.experts / 2;
@@ -500,6 +545,7 @@ int b200moe_ffn(const b200moe_ffn_view* v, void* stream) {
     lv.y = v->y; lv.y_bf16 = v->y_bf16; lv.row_status = v->row_status;
     lv.workspace = F.layer; lv.workspace_bytes = v->workspace_bytes - (static_cast<unsigned char*>(F.layer) - static_cast<unsigned char*>(v->workspace));
     lv.capacity = v->capacity; lv.grouped_min_rows = v->grouped_min_rows; lv.stage_events = v->stage_events;
+    lv.summary = v->summary;
     return layer_impl(&lv, stream, fused);
 }
 
@@ -519,8 +565,12 @@ int b200moe_ffn_host(const b200moe_ffn_view* v, const void* x_host, float* y_hos
     d.x = F.x_dev; d.y = F.y_dev;
     if (int rc = b200moe_ffn(&d, stream)) return rc;
     e = cudaMemcpyAsync(y_host, F.y_dev, n * 4, cudaMemcpyDeviceToHost, st);
+    u32 job = 0;  // the job summary, read back with y: a bounded device wait that ran out must not look like success
+    const u32* summary = v->summary ? v->summary : carve_layer(F.layer, v->shape, v->capacity).summary;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&job, summary, sizeof job, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "ffn_host: D2H copy / synchronize: %s", cudaGetErrorString(e));
+    if (job & B200MOE_JOB_WAIT_ABORTED) return fail(B200MOE_ERR_ABORTED, "ffn_host: a bounded device wait ran out (job summary 0x%x); y_host is not valid", job);
     return B200MOE_OK;
 }
 

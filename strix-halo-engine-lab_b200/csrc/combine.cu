@@ -7,6 +7,8 @@
 //   FMA_SLOTS acc = fma(w[k], raw[k], acc) in slot order (src/cuda/models/qwen/qwen_moe.cu:298-306;
 //             include/strix/moe/combine.hpp:36-59), y = acc (+ shared), optional bfloat16 RNE commit (:330-335).
 // HBM: rows * top_k * hidden * 4 B read, rows * hidden * 4 B written; elementwise over hidden, coalesced.
+#include <algorithm>
+
 #include "kernels.cuh"
 
 namespace b200moe {
@@ -14,52 +16,56 @@ namespace {
 
 constexpr u32 kMaxTopK = 32;
 
-// grid (ceil(hidden / 256), rows); 256 threads.
+// grid (ceil(hidden / 256), min(rows, 65535)); 256 threads; a block walks rows blockIdx.y, blockIdx.y + gridDim.y, ...
 __global__ void __launch_bounds__(256) combine_kernel(b200moe_combine_view v) {
-    const u32 row = blockIdx.y, o = blockIdx.x * blockDim.x + threadIdx.x;
-    if (v.row_status && v.row_status[row]) return;  // fail closed (qwen_moe.cu:291)
+    const u32 o = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v.summary && (*v.summary & B200MOE_JOB_WAIT_ABORTED)) return;  // an aborted stage left raw partly unwritten
     __shared__ float s_w[kMaxTopK];
     __shared__ u32 s_slot[kMaxTopK], s_part[kMaxTopK];
-    if (threadIdx.x < v.top_k) {
-        const u32 k = threadIdx.x;
-        if (v.form == B200MOE_COMBINE_PARTS) {
-            const u32 slot = v.order[row * v.top_k + k];
-            s_slot[k] = slot;
-            s_w[k] = v.weights[slot];
-            s_part[k] = min(v.ids[slot] / v.part_experts, v.parts - 1);
-        } else {
-            s_slot[k] = row * v.top_k + k;
-            s_w[k] = v.weights[row * v.top_k + k];
-        }
-    }
-    __syncthreads();
-    if (o >= v.hidden) return;
-    float out;
-    if (v.form == B200MOE_COMBINE_FMA_SLOTS) {
-        float acc = 0.0f;
-        for (u32 k = 0; k < v.top_k; ++k) acc = __fmaf_rn(s_w[k], v.raw[u64(s_slot[k]) * v.hidden + o], acc);
-        out = v.shared ? __fadd_rn(acc, v.shared[u64(row) * v.hidden + o]) : acc;
-    } else {
-        float total = v.shared ? v.shared[u64(row) * v.hidden + o] : 0.0f, single = 0.0f;
-        u32 k = 0;
-        for (u32 p = 0; p < v.parts; ++p) {  // the slots are sorted by expert id, so each part is one run
-            float sum = 0.0f;
-            while (k < v.top_k && s_part[k] == p) {
-                sum = __fadd_rn(sum, __fmul_rn(s_w[k], v.raw[u64(s_slot[k]) * v.hidden + o]));
-                ++k;
+    for (u32 row = blockIdx.y; row < v.rows; row += gridDim.y) {
+        __syncthreads();  // the previous row's readers are done with the shared arrays
+        if (v.row_status && v.row_status[row]) continue;  // fail closed (qwen_moe.cu:291); uniform over the block
+        if (threadIdx.x < v.top_k) {
+            const u32 k = threadIdx.x;
+            if (v.form == B200MOE_COMBINE_PARTS) {
+                const u32 slot = v.order[row * v.top_k + k];
+                s_slot[k] = slot;
+                s_w[k] = v.weights[slot];
+                s_part[k] = min(v.ids[slot] / v.part_experts, v.parts - 1);
+            } else {
+                s_slot[k] = row * v.top_k + k;
+                s_w[k] = v.weights[row * v.top_k + k];
             }
-            if (static_cast<int>(p) == v.only_part) single = sum;
-            total = __fadd_rn(total, sum);
         }
-        out = v.only_part >= 0 ? single : total;
+        __syncthreads();
+        if (o >= v.hidden) continue;
+        float out;
+        if (v.form == B200MOE_COMBINE_FMA_SLOTS) {
+            float acc = 0.0f;
+            for (u32 k = 0; k < v.top_k; ++k) acc = __fmaf_rn(s_w[k], v.raw[u64(s_slot[k]) * v.hidden + o], acc);
+            out = v.shared ? __fadd_rn(acc, v.shared[u64(row) * v.hidden + o]) : acc;
+        } else {
+            float total = v.shared ? v.shared[u64(row) * v.hidden + o] : 0.0f, single = 0.0f;
+            u32 k = 0;
+            for (u32 p = 0; p < v.parts; ++p) {  // the slots are sorted by expert id, so each part is one run
+                float sum = 0.0f;
+                while (k < v.top_k && s_part[k] == p) {
+                    sum = __fadd_rn(sum, __fmul_rn(s_w[k], v.raw[u64(s_slot[k]) * v.hidden + o]));
+                    ++k;
+                }
+                if (static_cast<int>(p) == v.only_part) single = sum;
+                total = __fadd_rn(total, sum);
+            }
+            out = v.only_part >= 0 ? single : total;
+        }
+        if (v.y_blocks) {  // the row's home rank's buffer: a peer store
+            const u32 blk = row / v.y_block_rows;
+            v.y_blocks[blk][u64(row - blk * v.y_block_rows) * v.hidden + o] = out;
+            continue;
+        }
+        v.y[u64(row) * v.hidden + o] = out;
+        if (v.y_bf16) v.y_bf16[u64(row) * v.hidden + o] = bf16_rne_bits(out);
     }
-    if (v.y_blocks) {  // the row's home rank's buffer: a peer store
-        const u32 blk = row / v.y_block_rows;
-        v.y_blocks[blk][u64(row - blk * v.y_block_rows) * v.hidden + o] = out;
-        return;
-    }
-    v.y[u64(row) * v.hidden + o] = out;
-    if (v.y_bf16) v.y_bf16[u64(row) * v.hidden + o] = bf16_rne_bits(out);
 }
 
 __global__ void __launch_bounds__(256) canonical_sum_kernel(const float* a, const float* b, const float* c, u64 count, float* y) {
@@ -92,7 +98,7 @@ __global__ void __launch_bounds__(256) row_order_kernel(const u32* ids, u32 rows
 int launch_combine(const b200moe_combine_view& v, cudaStream_t stream) {
     if (v.rows == 0) return B200MOE_OK;
     if (int rc = prefer_max_shared(reinterpret_cast<const void*>(combine_kernel))) return rc;
-    combine_kernel<<<dim3((v.hidden + 255) / 256, v.rows), 256, 0, stream>>>(v);
+    combine_kernel<<<dim3((v.hidden + 255) / 256, std::min<u32>(v.rows, 65535u)), 256, 0, stream>>>(v);
     return after_launch("combine");
 }
 int launch_canonical_sum(const float* a, const float* b, const float* c, u64 count, float* y, cudaStream_t stream) {

@@ -28,12 +28,13 @@ __global__ void __launch_bounds__(256) fold_parts_kernel(const float* __restrict
 }
 
 __global__ void __launch_bounds__(256) select_owner_slots_kernel(const float* __restrict__ blocks, u64 block_stride, u32 n_blocks,
-                                                                 u32 experts_per_block, const u32* __restrict__ ids, u32 hidden,
+                                                                 u32 experts_per_block, const u32* __restrict__ ids, u32 slots, u32 hidden,
                                                                  float* __restrict__ raw) {
-    const u32 slot = blockIdx.y;
-    const u32 owner = min(ids[slot] / experts_per_block, n_blocks - 1u);
-    const float* src = blocks + u64(owner) * block_stride + u64(slot) * hidden;
-    for (u32 o = blockIdx.x * blockDim.x + threadIdx.x; o < hidden; o += gridDim.x * blockDim.x) raw[u64(slot) * hidden + o] = src[o];
+    for (u32 slot = blockIdx.y; slot < slots; slot += gridDim.y) {  // grid.y is capped at 65,535
+        const u32 owner = min(ids[slot] / experts_per_block, n_blocks - 1u);
+        const float* src = blocks + u64(owner) * block_stride + u64(slot) * hidden;
+        for (u32 o = blockIdx.x * blockDim.x + threadIdx.x; o < hidden; o += gridDim.x * blockDim.x) raw[u64(slot) * hidden + o] = src[o];
+    }
 }
 
 }  // namespace
@@ -103,7 +104,7 @@ int b200moe_select_owner_slots(const float* blocks, uint64_t block_stride, uint3
     B200_REQUIRE(block_stride >= u64(slots) * hidden, "select_owner_slots: block_stride is below slots * hidden");
     if (slots == 0) return B200MOE_OK;
     if (!device_ready()) return B200MOE_ERR_CUDA;
-    select_owner_slots_kernel<<<dim3((hidden + 1023) / 1024, slots), 256, 0, as_stream(stream)>>>(blocks, block_stride, n_blocks, experts_per_block, ids, hidden, raw);
+    select_owner_slots_kernel<<<dim3((hidden + 1023) / 1024, slots < 65535u ? slots : 65535u), 256, 0, as_stream(stream)>>>(blocks, block_stride, n_blocks, experts_per_block, ids, slots, hidden, raw);
     return after_launch("select_owner_slots");
 }
 

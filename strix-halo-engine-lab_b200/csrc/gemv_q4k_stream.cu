@@ -30,7 +30,7 @@ namespace {
 constexpr int kR = 4;             // entries per pass over an octet
 constexpr u32 kMaxWarps = 16;     // consumer warps at most
 constexpr u32 kWaitLimit = 1u << 22;
-constexpr u32 kAbortBit = 1u << 30;
+constexpr u32 kAbortBit = B200MOE_JOB_WAIT_ABORTED;
 constexpr u32 kOctetsPerItem = 8;
 constexpr u32 kProducers = 4;       // producer warps
 
@@ -522,7 +522,7 @@ __global__ void __launch_bounds__((kMaxWarps + kProducers) * 32, 1) down_q4k_str
     u32* s_flag = reinterpret_cast<u32*>(bars + 2 * plan.stages);
     const Ring ring{smem, bars, reinterpret_cast<volatile u32*>(bars + plan.stages), reinterpret_cast<volatile u32*>(bars + plan.stages) + plan.stages, s_flag};
     ring_init(ring, plan.stages);
-    if (v.summary && (*v.summary & ~kAbortBit)) return;  // a failed projection skips the whole stage (routed_expert.hpp:17-19)
+    if (v.summary && *v.summary) return;  // a failed or aborted projection skips the whole stage (routed_expert.hpp:17-19)
 
     const u32 warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const u32 n_union = v.routes.counts[0];

@@ -54,7 +54,7 @@ constexpr u32 kBarBytes = (6 + 2 * kRawDepth) * 8 + 16;  // full[2], empty[2], r
 constexpr u32 kGroupedSmem = 2 * kStageBytes + kOutBytes + (kMaxUnion + 2) * 4 + kBarBytes + kRawDepth * kRawBlock + 256;
 static_assert(kGroupedSmem > 114u * 1024u && kGroupedSmem <= 227u * 1024u, "one CTA per SM, within the shared memory of an SM");
 constexpr u32 kWaitLimit = 1u << 22;
-constexpr u32 kAbortBit = 1u << 30;
+constexpr u32 kAbortBit = B200MOE_JOB_WAIT_ABORTED;
 // instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N = 64, M = 128
 constexpr u32 kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((kGN >> 3) << 17) | ((kGM >> 4) << 24);
 
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_q4k_kernel(const __grid_
     volatile u32* s_abort = s_tmem + 1;
     unsigned char* raw = smem + ((2 * kStageBytes + kOutBytes + (kMaxUnion + 2) * 4 + kBarBytes + 127u) & ~127u);  // [kRawDepth][kRawBlock]
 
-    if (kDown && a.summary && (*a.summary & ~kAbortBit)) return;  // a failed projection skips the stage (routed_expert.hpp:17-19)
+    if (kDown && a.summary && *a.summary) return;  // a failed or aborted projection skips the stage (routed_expert.hpp:17-19)
 
     const u32 tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const u32 n_union = min(a.routes.counts[0], kMaxUnion);

@@ -8,6 +8,8 @@ namespace b200moe {
 // a8.cu
 int launch_quantize_a8(const b200moe_quantize_a8_view& v, cudaStream_t stream);
 int launch_rmsnorm_a8(const b200moe_rmsnorm_view& v, cudaStream_t stream);
+// out[i] = float(bfloat16 bits in[i]) (exact widening)
+int launch_widen_bf16(const u16* in, float* out, u64 count, cudaStream_t stream);
 
 // router.cu
 // fused_quantize (optional): the A8 quantiser of the same activations is enqueued first
@@ -40,6 +42,15 @@ bool stream_gate_up_fits(const b200moe_gate_up_view& v, u32 rows);
 bool stream_down_fits(const b200moe_down_view& v, u32 rows);
 int launch_gate_up_q4k_stream(const b200moe_gate_up_view& v, u32 rows, cudaStream_t stream);
 int launch_down_q4k_stream(const b200moe_down_view& v, u32 rows, cudaStream_t stream);
+
+// gemv_q4k_wide.cu: the same contracts with SEGMENTS of the rows (and of the entries' A8 rows) streamed by TMA: any row
+// length, windows of any size whose routes fit shared memory
+bool wide_gate_up_fits(const b200moe_gate_up_view& v, u32 rows);
+bool wide_down_fits(const b200moe_down_view& v, u32 rows);
+int launch_gate_up_q4k_wide(const b200moe_gate_up_view& v, u32 rows, cudaStream_t stream);
+int launch_down_q4k_wide(const b200moe_down_view& v, u32 rows, cudaStream_t stream);
+// value of a B200MOE_DEBUG_* hook (api.cu)
+u32 debug_value(u32 key);
 
 // prologue.cu: A8 + router + routes of a decode window (rows <= 8) in one launch; ticket: a zeroed workspace word
 bool prologue_fusable(const b200moe_router_view& r, u32 top_k);

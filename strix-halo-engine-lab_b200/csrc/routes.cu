@@ -18,7 +18,7 @@ namespace {
 constexpr u32 kChunk = routes_detail::kChunk;
 
 using routes_detail::block_exclusive_scan;
-using routes_detail::owned;
+using routes_detail::entry_id;
 using routes_detail::row_order;
 using routes_detail::routes_small_body;
 
@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(1024) routes_count_kernel(b200moe_routes_view 
     const u32 t = threadIdx.x, n = v.rows * v.top_k, s = blockIdx.x * kChunk + t;
     cnt[t] = 0;
     __syncthreads();
-    if (s < n) { const u32 e = v.ids[s]; if (owned(e, v.experts, v.first, end)) atomicAdd(&cnt[e], 1u); }
+    if (s < n) { const u32 e = entry_id(v.ids, s, v.top_k, v.experts, v.first, end); if (e != 0xffffffffu) atomicAdd(&cnt[e], 1u); }
     __syncthreads();
     if (t < v.experts) v.scratch[u64(blockIdx.x) * v.experts + t] = cnt[t];
     for (u32 r = blockIdx.x * blockDim.x + t; r < v.rows; r += gridDim.x * blockDim.x)
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(1024) routes_fill_kernel(b200moe_routes_view v
     __shared__ u32 sid[1024];
     const u32 t = threadIdx.x, n = v.rows * v.top_k, s = blockIdx.x * kChunk + t;
     u32 e = 0xffffffffu;
-    if (s < n) { e = v.ids[s]; if (!owned(e, v.experts, v.first, end)) e = 0xffffffffu; }
+    if (s < n) e = entry_id(v.ids, s, v.top_k, v.experts, v.first, end);
     sid[t] = e;
     __syncthreads();
     if (e == 0xffffffffu) return;

@@ -51,6 +51,17 @@ __device__ inline void row_order(const u32* ids, u32 row, u32 top_k, u32 experts
 }
 
 __device__ __forceinline__ bool owned(u32 e, u32 experts, u32 first, u32 end) { return e < experts && e >= first && e < end; }
+// The expert id slot s contributes an entry for, or 0xffffffff for none: the id must lie in the owned range and must not
+// repeat an earlier slot of the same row. (The host builder throws on a repeated id, src/ds41_moe.cpp:22-23; here the row
+// is flagged INVALID_ROUTE and only the first occurrence keeps its entry, so no expert ever has more entries than the
+// window has rows and a flagged row cannot disturb the entries of a valid one.)
+__device__ __forceinline__ u32 entry_id(const u32* ids, u32 s, u32 top_k, u32 experts, u32 first, u32 end) {
+    const u32 e = ids[s];
+    if (!owned(e, experts, first, end)) return 0xffffffffu;
+    for (u32 i = s - s % top_k; i < s; ++i)
+        if (ids[i] == e) return 0xffffffffu;
+    return e;
+}
 
 // Windows of up to 256 slots (decode): every slot's thread counts what it needs directly from the ids in shared memory
 // - O(slots) work per thread, three block barriers, no scans. Same outputs as the general body below.
@@ -59,8 +70,7 @@ __device__ inline void routes_tiny_body(const b200moe_routes_view& v, u32 end) {
     const u32 t = threadIdx.x, nt = blockDim.x, n = v.rows * v.top_k, K = v.top_k;
     if (t < 4) red[t] = 0;
     for (u32 s = t; s < n; s += nt) {
-        const u32 e = v.ids[s];
-        sid[s] = owned(e, v.experts, v.first, end) ? e : 0xffffffffu;
+        sid[s] = entry_id(v.ids, s, K, v.experts, v.first, end);
     }
     __syncthreads();
     for (u32 s = t; s < n; s += nt) {  // rank among the slots of the same expert (ascending slot = ascending row)
@@ -122,9 +132,8 @@ __device__ inline void routes_small_body(const b200moe_routes_view& v, u32 end) 
     if (t == 0) maxc = 0;
     __syncthreads();
     for (u32 s = t; s < n; s += nt) {
-        u32 e = v.ids[s];
-        if (!owned(e, v.experts, v.first, end)) e = 0xffffffffu;
-        else atomicAdd(&cnt[e], 1u);
+        const u32 e = entry_id(v.ids, s, v.top_k, v.experts, v.first, end);
+        if (e != 0xffffffffu) atomicAdd(&cnt[e], 1u);
         sid[s] = e;
     }
     for (u32 r = t; r < v.rows; r += nt) row_order(v.ids, r, v.top_k, v.experts, v.split, v.out.order, v.out.low_counts, v.row_status);

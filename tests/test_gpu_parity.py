@@ -1,10 +1,11 @@
 """GPU parity: every stage of the CUDA path, called through the C ABI, against the CPU oracle on the same seeded
 inputs - bit for bit (integer work, ids, and every FP32 value whose contract is declared as single IEEE operations).
 
-The one tolerance in this file: the Qwen-family SwiGLU evaluates exp2 in double precision on both sides (C library
-on the host, CUDA math library on the device); the two may differ by one double ulp, which can flip the rounded float
-in about one evaluation per 2^29. Tests of that family therefore allow `QWEN_MISMATCH` differing h codes per million
-and the north-star tolerance (max relative error 1e-3) on outputs, and report exact equality when it holds.
+The one place where exactness is not structural: the Qwen-family SwiGLU evaluates exp2 in double precision on both sides
+(C library on the host, CUDA math library on the device); the two may differ by one double ulp, which flips the rounded
+float in about one evaluation per 2^29. The tests of that family COUNT the A8 groups of h that differ and allow
+`evaluations >> 26` of them - zero at every size used here - so they assert bit equality of every stage; the north-star
+tolerance (max relative error 1e-3) is asserted beside it on whole-layer outputs.
 """
 import math
 
@@ -355,19 +356,22 @@ def test_routes_invalid_ids_set_status(gpu):
     r = ops.enqueue_moe_routes(dv(ids, gpu), 8, 4, row_status=status)
     st = host(status)
     assert st[0] == b200moe.ROW_INVALID_ROUTE and st[1] == b200moe.ROW_INVALID_ROUTE and st[2] == 0
-    assert u32(r.counts)[2] == 11  # the out-of-range id gets no entry
+    assert u32(r.counts)[2] == 10  # neither the out-of-range id nor the second occurrence of a repeated id gets an entry
     with pytest.raises(b200moe.InvalidArgument):
         ops.enqueue_moe_routes(dv(ids, gpu), 2000, 4)
 
 
 # ---------------------------------------------------------------------------------------------------------- experts
-def run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, form, parts=2, shared=None, first=0, end=0, exact=True):
-    """Runs routes -> gate/up -> down -> combine stage by stage with taps; compares every stage with the oracle."""
+def run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, form, parts=2, shared=None, first=0, end=0, exact=True, want=None):
+    """Runs routes -> gate/up -> down -> combine stage by stage with taps; compares every stage with the oracle, bit for
+    bit. exact=False (Qwen family): the A8 groups of h that differ are counted and `evaluations >> 26` of them allowed
+    (the exp2 note in the file header; zero at the sizes used here), the stages behind them within the tolerance then."""
     from b200moe import ops
     rows, K = ids.shape
     H, I, E = sh.hidden, sh.inter, sh.experts
     codes, deltas, sums = oracle.quantize_a8(x)
-    want = oracle.experts(osh, gate, up, down, ids, codes, deltas, sums, first=first, end=end, taps=True)
+    if want is None:
+        want = oracle.experts(osh, gate, up, down, ids, codes, deltas, sums, first=first, end=end, taps=True)
     routes = ops.enqueue_moe_routes(dv(ids.view(np.int32), gpu), E, E // 2, first, end, 0)
     xa = (dv(codes, gpu), dv(deltas, gpu), dv(sums, gpu))
     g_gate, g_up, g_down = dv(gate, gpu), dv(up, gpu), dv(down, gpu)
@@ -382,9 +386,15 @@ def run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, form, parts=2,
         assert same(host(act[1])[own], want["act_deltas"][own]) and np.array_equal(host(act[2])[own], want["act_sums"][own])
         assert same(host(raw)[own], want["raw"][own])
     else:
-        mism = int((host(act[0])[own] != want["act_codes"][own]).sum())
-        assert mism <= max(1, own.sum() * I // 1_000_000), f"{mism} h codes differ"
-        assert max_rel(host(raw)[own], want["raw"][own]) <= REL_TOL
+        diff = (host(act[0])[own].reshape(-1, 32) != want["act_codes"][own].reshape(-1, 32)).any(axis=1)
+        diff |= bits(host(act[1])[own]).reshape(-1) != bits(want["act_deltas"][own]).reshape(-1)
+        allowed = (int(own.sum()) * I) >> 26
+        assert int(diff.sum()) <= allowed, f"{int(diff.sum())} A8 groups of h differ, {allowed} allowed"
+        if diff.any():
+            assert max_rel(host(raw)[own], want["raw"][own]) <= REL_TOL
+        else:
+            assert np.array_equal(host(act[2])[own], want["act_sums"][own]) and same(host(raw)[own], want["raw"][own])
+    exact = exact or not diff.any()
     if first == 0 and end == 0:
         pe = max(1, E // parts)
         wy = oracle.combine(form, want["raw"], wts, ids, shared=shared, parts=parts, part_experts=pe)
@@ -395,10 +405,6 @@ def run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, form, parts=2,
         else:
             assert max_rel(host(gy), wy) <= REL_TOL
     return host(raw), want
-
-
-def qwen_exact(got_raw, want):
-    return same(got_raw, want["raw"])
 
 
 def test_experts_q8_0_ds41_family(gpu, oracle):
@@ -422,20 +428,25 @@ def test_experts_q4k_qwen_family(gpu, oracle):
     import b200moe
     from b200moe import synth
     rng = np.random.default_rng(17)
-    exact_all = True
     for E, H, I, K, rows, dt in ((6, 512, 256, 2, 7, 12), (16, 2048, 768, 8, 4, 12), (8, 256, 512, 3, 21, 12), (6, 512, 256, 2, 7, 8),
                                  (4, 7168, 2048, 2, 3, 12), (4, 1280, 1024, 2, 2, 12), (5, 2560, 640, 3, 3, 8),
-                                 (4, 256, 256, 2, 70, 12), (3, 512, 768, 2, 64, 12)):  # 70 rows: beyond the decode-window form
+                                 (4, 256, 256, 2, 70, 12), (3, 512, 768, 2, 64, 12), (3, 256, 256, 2, 40, 12)):
         gate, up, _ = synth.expert_tensors(rng, E, H, I, 12, 12)
         down = (synth.q4_k_blocks(rng, E * H * (I // 256)) if dt == 12 else synth.q8_0_blocks(rng, E * H * (I // 32))).reshape(-1)
         x = rng.standard_normal((rows, H), dtype=np.float32)
         ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
         wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
         sh, osh = shape_pair(H, I, E, K, 12, dt)
-        raw, want = run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, exact=False)
-        exact_all &= qwen_exact(raw, want)
-        run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, first=1, end=E - 1, exact=False)
-    print("qwen family bit-exact on every case:", exact_all)
+        want = want_part = None
+        # every decode form of the Q4_K GEMVs on the same inputs: by plan, row streaming, segment streaming, per block
+        for form in (b200moe.FORM_AUTO, b200moe.FORM_ROW_STREAM, b200moe.FORM_SEGMENT_STREAM, b200moe.FORM_PER_BLOCK):
+            b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, form)
+            try:
+                _, want = run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, exact=False, want=want)
+                _, want_part = run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, first=1, end=E - 1,
+                                          exact=False, want=want_part)
+            finally:
+                b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, b200moe.FORM_AUTO)
 
 
 def test_experts_other_formats_q5_k_q5_1(gpu, oracle):
@@ -463,17 +474,14 @@ def test_experts_q4k_grouped_tensor_core_form(gpu, oracle):
     import b200moe
     from b200moe import synth
     rng = np.random.default_rng(31)
-    exact_all = True
     for E, H, I, K, rows in ((4, 512, 256, 2, 300), (8, 256, 256, 3, 130), (16, 1024, 512, 4, 128), (3, 2048, 768, 2, 200)):
         gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
         x = rng.standard_normal((rows, H), dtype=np.float32)
         ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
         wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
         sh, osh = shape_pair(H, I, E, K, 12, 12)
-        raw, want = run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, exact=False)
-        exact_all &= qwen_exact(raw, want)
+        run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, exact=False)
         run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, first=1, end=E - 1, exact=False)
-    print("grouped form bit-exact on every case:", exact_all)
 
 
 def test_experts_q4k_collisions_and_empty_experts(gpu, oracle):
@@ -489,11 +497,89 @@ def test_experts_q4k_collisions_and_empty_experts(gpu, oracle):
         x = rng.standard_normal((rows, H), dtype=np.float32)
         ids = np.tile(np.array([[7, 2]], np.uint32), (rows, 1))
         wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
-        run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, exact=False)
+        want = None
+        for form in (b200moe.FORM_AUTO, b200moe.FORM_ROW_STREAM, b200moe.FORM_SEGMENT_STREAM):  # 64 entries: 8 virtual experts of 8
+            b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, form)
+            try:
+                _, want = run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_FMA_SLOTS, exact=False, want=want)
+            finally:
+                b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, b200moe.FORM_AUTO)
     x = rng.standard_normal((6, H), dtype=np.float32)
     ids = np.arange(12, dtype=np.uint32).reshape(6, 2)
     run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, rng.uniform(0.05, 0.6, size=(6, K)).astype(np.float32),
                b200moe.COMBINE_FMA_SLOTS, exact=False)
+
+
+def test_repeated_id_leaves_valid_rows_exact(gpu, oracle):
+    """A row that names one expert twice is flagged INVALID_ROUTE and keeps only the first occurrence's entry; a valid row
+    sharing that expert must stay bit-exact in every decode form (an expert never has more entries than the window has
+    rows). The host builder throws on such a row (src/ds41_moe.cpp:22-23); a device path flags it and fails closed."""
+    import b200moe
+    from b200moe import ops, synth
+    rng = np.random.default_rng(35)
+    E, H, I, K, rows = 6, 512, 256, 2, 2
+    gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
+    x = rng.standard_normal((rows, H), dtype=np.float32)
+    codes, deltas, sums = oracle.quantize_a8(x)
+    ids = np.array([[3, 3], [3, 1]], np.uint32)   # row 0 repeats expert 3, row 1 uses it once
+    sh, osh = shape_pair(H, I, E, K, 12, 12)
+    good = oracle.experts(osh, gate, up, down, np.array([[3, 1]], np.uint32), codes[1:], deltas[1:], sums[1:])["raw"]
+    for form in (b200moe.FORM_AUTO, b200moe.FORM_ROW_STREAM, b200moe.FORM_SEGMENT_STREAM, b200moe.FORM_PER_BLOCK):
+        b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, form)
+        try:
+            status = torch.zeros(rows, dtype=torch.int32, device=gpu)
+            routes = ops.enqueue_moe_routes(dv(ids.view(np.int32), gpu), E, E // 2, row_status=status)
+            assert list(host(status)) == [b200moe.ROW_INVALID_ROUTE, 0]
+            assert u32(routes.counts)[2] == 3 and u32(routes.counts)[1] == 2   # three entries, at most two for one expert
+            act = ops.enqueue_routed_gate_up(sh, dv(gate, gpu), dv(up, gpu), routes, 3, (dv(codes, gpu), dv(deltas, gpu), dv(sums, gpu)), rows * K)
+            raw = host(ops.enqueue_routed_down(sh, dv(down, gpu), routes, 3, act))
+            assert same(raw[2:4], good), form
+        finally:
+            b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, b200moe.FORM_AUTO)
+
+
+def test_bounded_wait_runs_out_and_fails_closed(gpu, oracle):
+    """No device wait is unbounded. With a poll limit of a few thousand and a producer that stops feeding before its first
+    stage (both test hooks; nothing faults, no copy is left in flight), the segment-streaming gate/up kernel returns with
+    B200MOE_JOB_WAIT_ABORTED in the job summary; the down stage and the combine then write nothing, and the host-buffer
+    call reports B200MOE_ERR_ABORTED. The same call without the hooks is bit-exact afterwards."""
+    import b200moe
+    from b200moe import ops, synth
+    rng = np.random.default_rng(36)
+    E, H, I, K, rows = 8, 512, 256, 2, 4
+    gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
+    rw = synth.router_weight(rng, E, H)
+    x = rng.standard_normal((rows, H), dtype=np.float32)
+    codes, deltas, sums = oracle.quantize_a8(x)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+    wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
+    sh, osh = shape_pair(H, I, E, K, 12, 12)
+    xa = (dv(codes, gpu), dv(deltas, gpu), dv(sums, gpu))
+    ffn = ops.MoeFfn(sh, ops.softmax_policy(E, K), dv(gate, gpu), dv(up, gpu), dv(down, gpu), dv(rw, gpu), capacity=rows,
+                     combine_form=b200moe.COMBINE_FMA_SLOTS)
+    xh, yh = torch.from_numpy(x).pin_memory(), torch.full((rows, H), 5.0).pin_memory()
+    b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, b200moe.FORM_SEGMENT_STREAM)
+    b200moe.debug_set(b200moe.DEBUG_WAIT_LIMIT, 4096)
+    b200moe.debug_set(b200moe.DEBUG_STALL_STAGE, 1)
+    try:
+        routes = ops.enqueue_moe_routes(dv(ids.view(np.int32), gpu), E, E // 2)
+        summary = torch.zeros(4, dtype=torch.int32, device=gpu)
+        act = ops.enqueue_routed_gate_up(sh, dv(gate, gpu), dv(up, gpu), routes, rows * K, xa, rows * K, summary=summary)
+        torch.cuda.synchronize()                                   # the launch returned: nothing hangs
+        assert u32(summary)[0] & b200moe.JOB_WAIT_ABORTED
+        sentinel = torch.full((rows * K, H), 7.0, device=gpu)
+        ops.enqueue_routed_down(sh, dv(down, gpu), routes, rows * K, act, raw=sentinel, summary=summary)
+        y = ops.enqueue_moe_combine(b200moe.COMBINE_FMA_SLOTS, sentinel, dv(wts, gpu), dv(ids.view(np.int32), gpu), summary=summary, fill=9.0)
+        assert (host(sentinel) == 7.0).all() and (host(y) == 9.0).all()
+        with pytest.raises(b200moe.B200MoeError) as err:
+            ffn.host(xh, yh)
+        assert err.value.code == b200moe.ERR_ABORTED
+    finally:
+        for key in (b200moe.DEBUG_DECODE_FORM, b200moe.DEBUG_WAIT_LIMIT, b200moe.DEBUG_STALL_STAGE):
+            b200moe.debug_set(key, 0)
+    want = oracle.ffn(osh, O.softmax_policy(E, K), gate, up, down, rw, x, O.COMBINE_FMA_SLOTS)
+    ffn.host(xh, yh)
+    assert same(yh.numpy(), want["y"])
 
 
 def test_routes_maximum_sizes(gpu, oracle):
