@@ -415,52 +415,190 @@ def dense_arm(args, cfg, rank, world, dev):
         dist.destroy_process_group()
 
 
+# ---- config 4: the default workload ---------------------------------------------------------------------------------
+C4_PARTS = 8          # the fold always has 8 expert ranges: 1 GPU and 8 GPUs give the same bits
+C4_GLOBAL_BATCH = 64
+
+
+def c4_config(cfg, batch, world):
+    """The `config` object both arms print (the driver compares them key by key)."""
+    return {"workload": f"c4: {cfg['desc']}, decode, global batch {batch}",
+            "parallelism": f"ep x{world} ({cfg['experts'] // world} experts and {batch // world} home rows per rank)" if world > 1 else "1 gpu (all 256 experts)",
+            "l2": "5.5 GB of distinct routed expert weights per step (far beyond the 126 MB L2)"}
+
+
+class C4Model:
+    """Seeded synthetic config-4 layer. The routed experts are drawn once for one slice of 32 experts (0.8 GB); slice r of
+    the 8 is that slice with every tensor rotated by r * 37 weight rows, so the 256 experts differ while a host only
+    ever draws one slice. expert_host(e) cuts one expert out of that definition without building the 6.3 GB layer."""
+
+    SHIFT_ROWS = 37
+
+    def __init__(self, cfg):
+        from b200moe import synth
+        self.cfg = cfg
+        H, E, I = cfg["hidden"], cfg["experts"], cfg["inter"]
+        self.per = E // C4_PARTS
+        rng0 = np.random.default_rng(400)
+        self.rw = synth.router_weight(rng0, E, H)
+        self.bias = (rng0.standard_normal(E) * 0.1).astype(np.float32)
+        self.shared = synth.expert_tensors(rng0, 1, H, I, 8, 8)
+        self.base = synth.expert_tensors(np.random.default_rng(500), self.per, H, I, 12, 12)
+        self.row_bytes = (H // 256 * 144, H // 256 * 144, I // 256 * 144)
+        self.rows = (I, I, H)
+
+    def shift(self, t, r):
+        return r * self.SHIFT_ROWS * self.row_bytes[t]
+
+    def slice_device(self, r, dev):
+        import torch
+        return tuple(torch.roll(torch.from_numpy(self.base[t]).to(dev), self.shift(t, r)) for t in range(3))
+
+    def expert_host(self, e):
+        r, el = divmod(e, self.per)
+        out = []
+        for t in range(3):
+            n = self.rows[t] * self.row_bytes[t]
+            idx = (np.arange(el * n, (el + 1) * n, dtype=np.int64) - self.shift(t, r)) % self.base[t].size
+            out.append(self.base[t][idx])
+        return out
+
+    def compact(self, ids):
+        """Host tensors holding only the experts `ids` name, and the ids renumbered into them (ascending expert id)."""
+        used = np.unique(ids)
+        parts = [self.expert_host(int(e)) for e in used]
+        tensors = tuple(np.concatenate([p[t] for p in parts]) for t in range(3))
+        return tensors, np.searchsorted(used, ids).astype(np.uint32), len(used)
+
+    def batches(self, n, batch):
+        from b200moe import synth
+        rng = np.random.default_rng(7)
+        return [synth.bf16_round(synth.activations(rng, batch, self.cfg["hidden"])) for _ in range(n)]
+
+
+def c4_oracle_rows(model, x):
+    """The CPU oracle's y for the rows x (config-4 layer: group-limited router, routed Q4_K experts over the experts the
+    rows select, Q8_0 shared expert, 8-range fold). Returns (y, ids)."""
+    from oracle import loader as O
+    cfg = model.cfg
+    H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
+    orc = O.Oracle()
+    _, _, ids, wts = orc.router(O.sigmoid_group_policy(E, TK, 8, 4), x=x, w=model.rw, bias=model.bias)
+    codes, deltas, sums = orc.quantize_a8(x)
+    (g, u, d), local, n_used = model.compact(ids)
+    raw = orc.experts(O.Shape(H, I, n_used, TK, 12, 12, float("inf")), g, u, d, local, codes, deltas, sums)["raw"]
+    sg, su, sd = model.shared
+    shared = orc.experts(O.Shape(H, I, 1, 1, 8, 8, float("inf")), sg, su, sd, np.zeros((x.shape[0], 1), np.uint32), codes, deltas, sums)["raw"]
+    y = orc.combine(O.COMBINE_PARTS, raw, wts, ids, shared=shared, parts=C4_PARTS, part_experts=E // C4_PARTS)
+    return y, ids
+
+
+def c4_cpu_arm(model, x, target_s):
+    """The reference's CPU code on a bounded sample of the step: its routed-expert row kernels (AVX2 / AVX-VNNI table,
+    all host threads) on the sample's routes, its Q8_0 x A8 product for the shared expert's three matrices (rows split
+    over the threads), and the group-limited router, which the reference does not have, from the CPU oracle.
+    Returns (tokens/s, description)."""
+    from oracle import loader as O
+    cfg = model.cfg
+    H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
+    threads = os.cpu_count() or 1
+    orc = O.Oracle()
+    pol = O.sigmoid_group_policy(E, TK, 8, 4)
+    _, _, ids, _ = orc.router(pol, x=x, w=model.rw, bias=model.bias)
+    (g, u, d), local, _ = model.compact(ids)
+    codes, deltas, _ = orc.quantize_a8(x)
+    sg, su, sd = model.shared
+    have_ref = O.Ref.available()
+    ref = O.Ref() if have_ref else None
+
+    def once(reps):
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            orc.router(pol, x=x, w=model.rw, bias=model.bias)
+        t_router = time.perf_counter() - t0
+        if have_ref:
+            t_experts, _ = ref.time_experts_q4k(g, u, d, H, I, TK, x, local, threads, reps)
+            t_shared = sum(ref.time_gemv_q8_0_a8(w, width, c, dl, threads, reps)[0]
+                           for w, width, c, dl in ((sg, H, codes, deltas), (su, H, codes, deltas),
+                                                   (sd, I, np.ascontiguousarray(codes[:, :I]), np.ascontiguousarray(deltas[:, :I // 32]))))
+        else:
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                c4_oracle_rows(model, x)
+            t_experts, t_shared = time.perf_counter() - t0 - t_router, 0.0
+        return t_router + t_experts + t_shared
+
+    one = once(1)
+    reps = max(1, min(200, int(target_s / max(one, 1e-6))))
+    sec = once(reps)
+    value = x.shape[0] * reps / sec
+    kind = "reference" if have_ref else "port"
+    what = (f"{reps} x {x.shape[0]} tokens of one step ({sec:.1f} s): reference row kernels (isa {ref.isa()}) for the routed experts on the sample's routes + "
+            "reference gemv_q8_0_a8 for the shared expert, own threaded driver with a kept pool; group-limited router from the CPU oracle "
+            "(the reference has none)") if have_ref else f"{reps} x {x.shape[0]} tokens of one step through the CPU oracle port ({sec:.1f} s)"
+    return value, {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": what}
+
+
+def c4_reference_arm(args, cfg, rank, world):
+    if rank != 0:
+        return
+    model = C4Model(cfg)
+    x = model.batches(1, C4_GLOBAL_BATCH)[0][:8]
+    total = max(1, args.steps + args.warmup)
+    value, base = c4_cpu_arm(model, x, target_s=min(45.0, 0.05 * total + 15.0))
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 * C4_GLOBAL_BATCH / value, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic", "config": c4_config(cfg, C4_GLOBAL_BATCH, world),
+            "cpu_baseline": base, "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
 def large_arm(args, cfg, rank, world, dev):
-    """Config 4: 256 routed Q4_K experts (group-limited sigmoid router) + a replicated Q8_0 shared expert, `--batch` tokens
-    per rank (default 64). One GPU holds every expert; N GPUs run expert parallelism with experts / N per rank
-    (b200moe.ep). A step = shared expert + routed experts + the rank-ordered fold y = ((shared + S_0) + S_1) ...;
-    one set of weights (6.3 GB of routed experts: far beyond L2)."""
+    """Config 4, decode at a FIXED global batch of 64 rows per step (strong scaling): 256 routed Q4_K experts behind a
+    sigmoid + bias, group-limited router plus one Q8_0 shared expert. One GPU holds every expert (b200moe_ffn, the fold
+    over 8 expert ranges); N GPUs run expert parallelism through b200moe_ep_ffn: experts / N and 64 / N home rows per rank,
+    dispatch and return by the library's peer-store kernels with flag waits, no collective on the data path. Same kernels
+    and the same total work at every N. A step = shared expert + routed experts + fold for the 64 rows."""
     import torch
     import torch.distributed as dist
     import b200moe
-    from b200moe import ep, ops, synth
+    from b200moe import ep, ops
 
-    K, W = args.steps if args.steps != 2000 else 100, max(min(args.warmup, 20), 3)
-    B = args.batch if args.batch != 8 else 64
+    K, W = args.steps if args.steps != 2000 else 40, max(min(args.warmup, 20), 3)
+    B = args.batch if args.batch != 8 else C4_GLOBAL_BATCH
+    assert B % world == 0 and cfg["experts"] % world == 0, "the global batch and the experts must split over the ranks"
+    R = B // world
     H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
-    PARTS = 8                                                # the fold always has 8 expert ranges: 1 and 8 GPUs give the same bits
     per = E // world
+    model = C4Model(cfg)
     shape = ops.make_shape(H, I, E, TK, 12, 12)
     sh_shape = ops.make_shape(H, I, 1, 1, 8, 8)
     policy = ops.sigmoid_group_policy(E, TK, 8, 4)
-    rng0 = np.random.default_rng(400)
-    rw = torch.from_numpy(synth.router_weight(rng0, E, H)).to(dev)
-    bias = torch.from_numpy((rng0.standard_normal(E) * 0.1).astype(np.float32)).to(dev)
-    sg, su, sd = (torch.from_numpy(a).to(dev) for a in synth.expert_tensors(rng0, 1, H, I, 8, 8))
-    parts = []
-    for r in range(world if world > 1 else PARTS):           # experts are generated in 8 (or world) seeded slices
-        if world > 1 and r != rank:
-            continue
-        n_e = per if world > 1 else E // PARTS
-        parts.append(synth.expert_tensors(np.random.default_rng(500 + r), n_e, H, I, 12, 12))
-    gate, up, down = (torch.from_numpy(np.concatenate([p[i] for p in parts])).to(dev) for i in range(3))
+    rw, bias = torch.from_numpy(model.rw).to(dev), torch.from_numpy(model.bias).to(dev)
+    sg, su, sd = (torch.from_numpy(a).to(dev) for a in model.shared)
+    slices = range(C4_PARTS) if world == 1 else range(rank * C4_PARTS // world, (rank + 1) * C4_PARTS // world)
+    parts = [model.slice_device(r, dev) for r in slices]
+    gate, up, down = (torch.cat([p[t] for p in parts]) for t in range(3))
     del parts
-    rng = np.random.default_rng(7 + rank)
     NX = 4
-    xs_host = [torch.from_numpy(synth.bf16_round(synth.activations(rng, B, H))).pin_memory() for _ in range(NX)]
+    batches = model.batches(NX, B)
+    xs_host = [torch.from_numpy(np.ascontiguousarray(x[rank * R:(rank + 1) * R])).pin_memory() for x in batches]
     xs = [x.to(dev) for x in xs_host]
-    ys_host = torch.empty((B, H), dtype=torch.float32).pin_memory()
+    ys_host = torch.empty((R, H), dtype=torch.float32).pin_memory()
+    ys = [torch.empty((R, H), dtype=torch.float32, device=dev) for _ in range(NX)]
+    summary = torch.zeros(1, dtype=torch.int32, device=dev)
     if world > 1:
-        kern = ep.DeviceKernels(shape, policy, rw, gate, up, down, world * B, b200moe.COMBINE_PARTS, world, rank, select_bias=bias)
-        routed = ep.EpMoeFfn(kern, B, TK, H, b200moe.COMBINE_PARTS, peer_return=not args.no_peer_return, device=dev)
-        fn = lambda x, shared: routed(x, shared)
+        layer = ep.PeerEpFfn(shape, policy, rw, gate, up, down, R, select_bias=bias)
+        routed = lambda x, shared, y, ev=None: b200moe.check(b200moe.lib().b200moe_ep_ffn(layer.handle, C.byref(layer.view(x, y, shared, summary, ev)), b200moe.stream_ptr()))
     else:
-        ffn = ops.MoeFfn(shape, policy, gate, up, down, rw, capacity=B, combine_form=b200moe.COMBINE_PARTS, parts=PARTS, select_bias=bias)
-        fn = lambda x, shared: ffn(x, shared=shared)
+        ffn = ops.MoeFfn(shape, policy, gate, up, down, rw, capacity=B, combine_form=b200moe.COMBINE_PARTS, parts=C4_PARTS, select_bias=bias)
+        routed = lambda x, shared, y, ev=None: b200moe.check(b200moe.lib().b200moe_ffn(C.byref(ffn._view(R, x, y, shared=shared, events=ev, summary=summary)), b200moe.stream_ptr()))
 
-    def step(x):
+    def step(s, x=None, ev=None):
+        x = xs[s % NX] if x is None else x
         shared = ops.enqueue_dense_ffn(sh_shape, sg, su, sd, ops.enqueue_quantize_a8(x))
-        return fn(x, shared)
+        routed(x, shared, ys[s % NX], ev)
+        return ys[s % NX]
 
     def barrier():
         if world > 1:
@@ -468,78 +606,166 @@ def large_arm(args, cfg, rank, world, dev):
         torch.cuda.synchronize()
 
     for s in range(W):
-        step(xs[s % NX])
+        step(s)
     barrier()
-    # NX consecutive steps captured into one CUDA graph (kernels, NCCL collectives and peer stores alike): the replay
-    # removes the per-launch host cost that otherwise dominates a step this short. Eager launches if the capture fails.
-    graph, mode = None, "per-step launches"
-    if not args.no_graph and world == 1:  # (with NCCL collectives inside, the capture of this step stalled on 2 GPUs: ranks stay eager)
+    assert int(summary.item()) == 0, f"job summary {int(summary.item()):#x} after the warm-up"
+
+    # ---- parity of one step against the CPU oracle, outside every timed region ------------------------------------
+    parity = None
+    y0 = step(0)                                              # every rank: the exchange needs all of them in every step
+    barrier()
+    if rank == 0 and not args.no_check:
+        n = min(R, 8)
+        y0 = y0.cpu().numpy()[:n]
+        want, _ = c4_oracle_rows(model, batches[0][:n])
+        err = float(np.max(np.abs(y0 - want).max(axis=-1) / np.maximum(np.abs(want).max(axis=-1), 1e-30)))
+        parity = {"rows_checked": n, "bits_equal": bool(np.array_equal(y0.view(np.uint32), want.view(np.uint32))), "max_rel": err,
+                  "against": "CPU oracle (oracle/), same seeded inputs, outside the timed regions"}
+    barrier()
+
+    # ---- distinct experts and entries per step on this rank: the algorithmic bytes of the routed GEMVs -----------
+    gate_up_bytes, down_bytes = expert_bytes(cfg)
+    uniq, entries = [], []
+    for x in batches:
+        _, _, ids, _ = ops.enqueue_router(policy, x=torch.from_numpy(x).to(dev), weight=rw, bias=bias)
+        ids = ids.cpu().numpy()
+        mine = ids[(ids >= rank * per) & (ids < (rank + 1) * per)]
+        uniq.append(len(np.unique(mine)))
+        entries.append(mine.size)
+    uniq, entries = np.array(uniq, np.float64), np.array(entries, np.float64)
+
+    # ---- timed region 1: the K-step block, replayed from a CUDA graph, repeated until the region is >= 0.25 s ------
+    graph, mode, per_graph = None, "per-step launches", 0
+    if not args.no_graph:
         try:
             cap = torch.cuda.Stream()
             cap.wait_stream(torch.cuda.current_stream())
             g = torch.cuda.CUDAGraph()
             launches_before = b200moe.launch_count()
             with torch.cuda.graph(g, stream=cap):
-                kept = [step(xs[s]) for s in range(NX)]
+                for s in range(NX):
+                    step(s)
             per_graph = b200moe.launch_count() - launches_before
             graph, mode = g, f"CUDA graph replay of {NX} steps"
-            for _ in range(2):
-                graph.replay()
         except Exception as e:  # noqa: BLE001 - any capture problem: measure the eager path and say so
             graph, mode = None, f"per-step launches (graph capture failed: {type(e).__name__})"
+    ok = torch.tensor([1 if graph is not None else 0], dtype=torch.int32, device=dev)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if not int(ok.item()):
+        graph = None
+        mode = mode if mode.startswith("per-step") else "per-step launches (a peer's capture failed)"
+
+    def run_block(k):
+        if graph is not None:
+            for _ in range(k // NX):
+                graph.replay()
+            for s in range(k % NX):
+                step(s)
+        else:
+            for s in range(k):
+                step(s)
+
+    run_block(K)
     barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run_block(K)
+    e1.record()
+    barrier()
+    pilot = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(pilot, op=dist.ReduceOp.MAX)
+    reps = max(1, int(math.ceil(250.0 / max(float(pilot.item()), 1e-3))))
     launches0 = b200moe.launch_count()
     sampler = ClockSampler(dev.index)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    if graph is not None:
-        for _ in range(K // NX):
-            graph.replay()
-        for s in range(K % NX):
-            step(xs[s])
-    else:
-        for s in range(K):
-            step(xs[s % NX])
+    for _ in range(reps):
+        run_block(K)
     e1.record()
     barrier()
     dev_ms = e0.elapsed_time(e1)
-    launches = (b200moe.launch_count() - launches0) + (per_graph * (K // NX) if graph is not None else 0)
+    eager = b200moe.launch_count() - launches0
+    launches_per_step = (eager + (per_graph * (K // NX) * reps if graph is not None else 0)) / (K * reps)
+
+    # ---- timed region 2: the same steps launched one by one, CUDA events around the routed gate/up kernel -----------
+    evs = []
+    for s in range(NX):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    taps = [ops.MoeFfn.stage_events([None, None, a.cuda_event, b.cuda_event, None, None, None, None]) for a, b in evs]
+    kern_ms = []
+    for _ in range(max(2, min(10, K // NX))):
+        for s in range(NX):
+            step(s, ev=taps[s])
+        torch.cuda.synchronize()
+        kern_ms += [evs[s][0].elapsed_time(evs[s][1]) for s in range(NX)]
+    kern_ms = np.array(kern_ms).reshape(-1, NX)
+    barrier()
+
+    # ---- timed region 3: end to end, pinned host rows in, pinned host y out, every step ---------------------------
+    def run_host(k):
+        for s in range(k):
+            ys_host.copy_(step(s, x=xs_host[s % NX].to(dev, non_blocking=True)), non_blocking=True)
+        torch.cuda.synchronize()
+
+    run_host(NX)
     barrier()
     t0 = time.perf_counter()
-    for s in range(K):
-        ys_host.copy_(step(xs_host[s % NX].to(dev, non_blocking=True)), non_blocking=True)
+    run_host(K)
     barrier()
     host_ms = 1000.0 * (time.perf_counter() - t0)
     sampler.stop_flag = True
     sampler.join(timeout=2)
-    t = torch.tensor([dev_ms, host_ms], dtype=torch.float64, device=dev)
+    assert int(summary.item()) == 0, f"job summary {int(summary.item()):#x}: a bounded wait ran out during the timed steps"
+
+    algo = uniq * gate_up_bytes + entries * (H * 1.25)              # per batch: distinct local experts + the entries' A8 rows
+    stats = torch.tensor([dev_ms, host_ms, float(kern_ms.mean()), float((algo / (kern_ms.mean(axis=0) * 1e-3)).mean() / 1e9), float(algo.mean()),
+                          float(uniq.mean())], dtype=torch.float64, device=dev)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, host_ms = (float(v) for v in t.cpu())
-    tokens = B * K * world
+        allr = [torch.empty_like(stats) for _ in range(world)]
+        dist.all_gather(allr, stats)
+        allr = torch.stack(allr).cpu().numpy()
+    else:
+        allr = stats.cpu().numpy()[None]
+    dev_ms, host_ms = float(allr[:, 0].max()), float(allr[:, 1].max())
+    slow = int(np.argmax(allr[:, 2]))                                # the rank whose gate/up launches take longest
+    tokens = B * K * reps
     peak, peak_kind = peaks()
-    gate_up_bytes, down_bytes = expert_bytes(cfg)
-    rank_bytes = (E // world) * (gate_up_bytes + down_bytes)   # upper bound: every local expert hit in the step
-    achieved = rank_bytes / (dev_ms / K * 1e-3) / 1e9
+    achieved = float(allr[slow, 3])
     line = {
         "metric": METRIC, "value": tokens / (dev_ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {B} per rank",
-                   "parallelism": f"ep x{world} ({per} experts per rank)" if world > 1 else "1 gpu (all 256 experts)",
-                   "l2": "6.3 GB of routed expert weights per layer (far beyond L2)", "launch": mode + ((" + NCCL all-gather dispatch, " + ("all-to-all return" if args.no_peer_return else "peer-store return (CUDA IPC) + 1-word all-reduce")) if world > 1 else "")},
+        "ms_per_step": dev_ms / (K * reps), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic", "config": c4_config(cfg, B, world),
         "clocks": sampler.summary(),
-        "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
+        "e2e": {"value": B * K / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
                 "ms_per_step": host_ms / K},
-        "gpu_launches": int(launches),
-        "roofline": {"kernel": "whole step (upper bound: all local routed expert bytes / step time)", "bound": "hbm", "achieved": achieved,
-                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy", "traffic": None},
+        "gpu_launches": int(round(launches_per_step * K)),
+        "roofline": {"kernel": "q4k_wide_kernel<gate/up> (routed experts, segment-streaming GEMV)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy", "frac_of_nominal_8tbs": achieved / 8000.0,
+                     "traffic": None, "traffic_note": "dram bytes per launch of this kernel from an ncu capture: profiles/wide_kernels_c4_decode.md",
+                     "algorithmic_bytes_per_launch": float(allr[slow, 4]), "avg_launch_us": float(allr[slow, 2]) * 1000.0,
+                     "distinct_experts_per_step_on_that_rank": float(allr[slow, 5]), "rank": slow},
+        "extra": {"timed_steps": K * reps, "timed_region_s": dev_ms / 1000.0, "launch": mode + (
+                      "; dispatch and return by the library's peer-store kernels with bounded flag waits (CUDA IPC windows, no collective)" if world > 1 else ""),
+                  "launches_per_step": launches_per_step, "rows_per_rank": R,
+                  "step_hbm_gbs_per_rank": float(np.mean(uniq) * (gate_up_bytes + down_bytes) / (dev_ms / (K * reps) * 1e-3) / 1e9)},
     }
+    if parity is not None:
+        line["parity"] = parity
     if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            _, base = c4_cpu_arm(model, batches[0][:8], target_s=10.0)
+            line["cpu_baseline"] = base
+        if world == 1 and not args.no_extra:
+            line["extra"]["c2_b8"] = c2_summary(args, dev)
         print(json.dumps(line), flush=True)
     if world > 1:
+        layer.close()
         dist.destroy_process_group()
 
 
@@ -634,50 +860,15 @@ def ep_arm(args, cfg, rank, world, dev):
     dist.destroy_process_group()
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=200)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(CONFIGS))
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=4, help="distinct layers of weights rotated between steps")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="config 4 arm: launch every step eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--no-peer-return", action="store_true",
-                    help="expert parallelism, PARTS form: return the partial sums with an NCCL all-to-all instead of the combine kernel's peer stores")
-    ap.add_argument("--form", type=int, default=0, choices=[0, 1, 2, 3],
-                    help="Q4_K decode GEMV form: 0 = by plan, 1 = row streaming, 2 = segment streaming, 3 = per block (measurement hook)")
-    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
-                    help="N > 1: independent replicas (rows sharded, weights replicated, no collective) or expert parallelism "
-                         "(experts / N per rank, all-gather dispatch + all-to-all return over NCCL)")
-    args = ap.parse_args()
-    cfg = CONFIGS[args.workload]
-    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
-    if args.impl == "reference":
-        return reference_arm(args, cfg, rank, world)
-
+def decode_arm(args, cfg, rank, world, dev):
+    """Configs 1 and 2: one MoE decode layer on every GPU (replicas at N > 1), rotating over several layers of distinct
+    weights. Returns the JSON line as a dict."""
     import torch
     import torch.distributed as dist
     import b200moe
     from b200moe import ops, synth
 
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
-    if args.form:
-        b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, args.form)
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    if cfg.get("prefill"):
-        return prefill_arm(args, cfg, rank, world, dev)
-    if cfg.get("dense"):
-        return dense_arm(args, cfg, rank, world, dev)
-    if cfg.get("large"):
-        return large_arm(args, cfg, rank, world, dev)
-    if world > 1 and args.parallelism == "ep":
-        return ep_arm(args, cfg, rank, world, dev)
+    local = dev.index
     K, W, L = args.steps, max(args.warmup, 3), args.layers
     B = cfg.get("batch", args.batch) if args.batch == 8 else args.batch
     H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
@@ -831,10 +1022,72 @@ def main():
         "extra": {"step_hbm_gbs_graph": step_bytes / (dev_ms / K * 1e-3) / 1e9, "ms_per_step_no_graph": plain_ms_total / K,
                   "tokens_per_s_no_graph": tokens / (plain_ms_total / 1000.0), "launches_per_step": launches_per_step},
     }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        _, base = cpu_arm(cfg, B, target_s=12.0)
+        line["cpu_baseline"] = base
+    return line
+
+
+
+
+def c2_summary(args, dev):
+    """Config 2 at batch 8 measured in the same run (the headline of earlier reports): value and the gate/up roofline."""
+    import copy
+    a = copy.copy(args)
+    a.steps, a.warmup, a.batch, a.layers, a.no_cpu_baseline, a.workload = 400, 50, 8, 4, True, "c2"
+    line = decode_arm(a, CONFIGS["c2"], 0, 1, dev)
+    return {"workload": line["config"]["workload"], "value": line["value"], "ms_per_step": line["ms_per_step"], "e2e": line["e2e"]["value"],
+            "gate_up_kernel": line["roofline"]["kernel"], "gate_up_frac": line["roofline"]["frac"], "gate_up_us": line["roofline"]["avg_launch_us"]}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c4", choices=sorted(CONFIGS))
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=4, help="distinct layers of weights rotated between steps")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison of one step with the CPU oracle (the `parity` key)")
+    ap.add_argument("--no-extra", action="store_true", help="config 4 on one GPU: skip the config 2 batch 8 figures under extra.c2_b8")
+    ap.add_argument("--no-graph", action="store_true", help="config 4 arm: launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-peer-return", action="store_true",
+                    help="expert parallelism, PARTS form: return the partial sums with an NCCL all-to-all instead of the combine kernel's peer stores")
+    ap.add_argument("--form", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="Q4_K decode GEMV form: 0 = by plan, 1 = row streaming, 2 = segment streaming, 3 = per block (measurement hook)")
+    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
+                    help="N > 1: independent replicas (rows sharded, weights replicated, no collective) or expert parallelism "
+                         "(experts / N per rank, all-gather dispatch + all-to-all return over NCCL)")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.workload]
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        return c4_reference_arm(args, cfg, rank, world) if cfg.get("large") else reference_arm(args, cfg, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    import b200moe
+    from b200moe import ops, synth
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    if args.form:
+        b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, args.form)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if cfg.get("prefill"):
+        return prefill_arm(args, cfg, rank, world, dev)
+    if cfg.get("dense"):
+        return dense_arm(args, cfg, rank, world, dev)
+    if cfg.get("large"):
+        return large_arm(args, cfg, rank, world, dev)
+    if world > 1 and args.parallelism == "ep":
+        return ep_arm(args, cfg, rank, world, dev)
+    line = decode_arm(args, cfg, rank, world, dev)
     if rank == 0:
-        if world == 1 and not args.no_cpu_baseline:
-            _, base = cpu_arm(cfg, B, target_s=12.0)
-            line["cpu_baseline"] = base
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -345,6 +345,53 @@ int b200moe_fold_parts(const float* parts, uint32_t n_parts, uint64_t part_strid
 int b200moe_select_owner_slots(const float* blocks, uint64_t block_stride, uint32_t n_blocks, uint32_t experts_per_block,
                                const uint32_t* ids, uint32_t slots, uint32_t hidden, float* raw, void* stream);
 
+/* ------------------------------------------------------------------------------------------ expert parallelism, one call
+ * The whole expert-parallel step of a rank behind one enqueue-only call: route the rank's home rows, dispatch them to the
+ * ranks whose experts they selected, run the local experts, return the partial sums, fold. Both exchanges are kernels of
+ * this library storing into the peers' memory over NVLink (windows created with b200moe_peer_buffer_create and mapped with
+ * b200moe_peer_buffer_open on every rank; plain peer stores, no multicast, no collective library, no host wait), each
+ * followed by per-source arrival flags that the receiver polls with a BOUNDED wait: a peer that never signals costs
+ * wait_polls polls (about a second by default), then the job summary gets B200MOE_JOB_WAIT_ABORTED and y is not written.
+ * Stands where the reference has its two-rank split over Communicator::exchange (include/strix/dist/communicator.hpp:180;
+ * include/strix/ds41_moe.hpp:5-11; restrict_routes / reference_half_sum, src/ds41_moe.cpp:45-61, :99-115): rank r owns
+ * experts [r * E / W, (r + 1) * E / W) and passes only those tensors; a row's A8 record goes only to the ranks that own
+ * one of its experts (the all-to-all-v of the dispatch; positions are fixed by the global row index, so no counts are
+ * negotiated); y = (((shared + S_0) + S_1) + ...) + S_{W-1}: the bits of b200moe_ffn with combine PARTS and parts = W.
+ * Every rank calls b200moe_ep_ffn once per step with the same rows_per_rank; steps alternate between two halves of
+ * the window, so a captured CUDA graph must hold an even number of steps. Set-up calls (create / destroy) allocate and
+ * synchronise; b200moe_ep_ffn does neither. */
+typedef struct b200moe_ep_desc {
+    b200moe_shape shape;           /* experts = all routed experts of the layer */
+    b200moe_route_policy policy;
+    uint32_t world, rank;          /* 1 <= world <= 8 (one node), experts % world == 0 */
+    uint32_t rows_per_rank;        /* home rows of every rank per step */
+    uint32_t wait_polls;           /* bound of the flag waits, 0 = the default (about a second) */
+    void* const* windows;          /* HOST array [world]: device address, in this process, of every rank's window (own included),
+                                    * each b200moe_ep_window_bytes() long and zero-filled before the first step */
+} b200moe_ep_desc;
+typedef struct b200moe_ep_step_view {
+    b200moe_expert_weights weights; /* the rank's experts only: [experts / world][...] */
+    const float* router_weight;     /* [experts][hidden], replicated */
+    const float* logit_bias;        /* optional */
+    const float* select_bias;       /* when policy.selection_bias */
+    const void* x;                  /* [rows][hidden] FP32 or bfloat16: the rank's home rows */
+    uint32_t x_is_bf16;
+    uint32_t rows;                  /* == rows_per_rank */
+    const float* shared;            /* optional [rows][hidden]: the shared expert's output for the home rows */
+    float* y;                       /* [rows][hidden] */
+    uint16_t* y_bf16;               /* optional */
+    uint32_t* summary;              /* optional [1]: job summary (see b200moe_layer_view) */
+    void* workspace;
+    uint64_t workspace_bytes;       /* b200moe_ep_workspace_bytes(ep) */
+    uint32_t grouped_min_rows;      /* as b200moe_layer_view, applied to the world * rows_per_rank window */
+    void* const* stage_events;      /* optional timing taps of the local experts (see b200moe_layer_view) */
+} b200moe_ep_step_view;
+uint64_t b200moe_ep_window_bytes(const b200moe_shape* shape, uint32_t world, uint32_t rows_per_rank);
+int b200moe_ep_create(const b200moe_ep_desc* desc, void** ep);
+void b200moe_ep_destroy(void* ep);
+uint64_t b200moe_ep_workspace_bytes(const void* ep);
+int b200moe_ep_ffn(void* ep, const b200moe_ep_step_view* view, void* stream);
+
 /* ------------------------------------------------------------------------------------------------ whole layer
  * Routes from the router's ids, gate/up, down and the combine. Decode GEMVs below grouped_min_rows rows, the grouped
  * tensor-core GEMM from there (0 = never). Replaces enqueue_moe_layer(MoeLayerView)

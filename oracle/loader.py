@@ -435,6 +435,28 @@ class Ref:
                                           _p(router_w, f32p), _p(x, f32p), rows, threads, reps, _p(y, f32p), _p(ids, u32p))
         return sec, y, ids
 
+    def time_experts_q4k(self, gate, up, down, hidden, inter, top_k, x, ids, threads, reps):
+        """Seconds for `reps` calls of the routed Q4_K experts (reference row kernels) on the given routes; raw of the last call."""
+        x = np.ascontiguousarray(x, np.float32)
+        ids = np.ascontiguousarray(ids, np.uint32)
+        rows = x.shape[0]
+        raw = np.zeros((rows * top_k, hidden), np.float32)
+        self.lib.ref_time_experts_q4k.restype = C.c_double
+        sec = self.lib.ref_time_experts_q4k(_p(gate, u8p), _p(up, u8p), _p(down, u8p), hidden, inter, top_k, _p(x, f32p), rows,
+                                            _p(ids, u32p), threads, reps, _p(raw, f32p))
+        return sec, raw
+
+    def time_gemv_q8_0_a8(self, weight, width, codes, deltas, threads, reps):
+        """Seconds for `reps` dense Q8_0 x A8 products (the CPU backend's kernel, output rows split over the threads)."""
+        weight = np.ascontiguousarray(weight, np.uint8).reshape(-1)
+        row_bytes = width // 32 * 34
+        count, rows = weight.size // row_bytes, codes.shape[0]
+        out = np.zeros((rows, count), np.float32)
+        self.lib.ref_time_gemv_q8_0_a8.restype = C.c_double
+        sec = self.lib.ref_time_gemv_q8_0_a8(_p(weight, u8p), row_bytes, width, count, rows, _p(codes, i8p), _p(deltas, f32p), threads, reps,
+                                             _p(out, f32p))
+        return sec, out
+
     def isa(self):
         """Row-kernel table of the routed-expert executor on this host."""
         return self.lib.ref_expert_isa().decode()

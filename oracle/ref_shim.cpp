@@ -9,6 +9,8 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <condition_variable>
+#include <mutex>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -304,38 +306,150 @@ int ref_combine(u32 form, u32 rows, u32 top_k, u32 width, const float* w, const 
 // Q4_K down contract is the gate/up row rule over K = inter, include/strix/moe_a8_down_contract.hpp:9-11; its executor
 // itself only binds Q5_1 / Q8_0 down, src/cpu/core/routed_expert.hpp:27-28), its Gfx1151Exp and its A8 rule, its
 // router (reference_router's dot order + route_scores_ref / route_select_ref) - over all host threads with the
-// executor's item split ((expert, 32-output group), then (expert, 16 hidden outputs)). Returns seconds for `reps`
-// layer calls; y receives the last call's output (Qwen merge form) so the caller can check it.
-static void parallel_items(unsigned threads, u32 n, const std::function<void(u32)>& fn) {
-    std::atomic<u32> next{0};
-    auto work = [&] { for (;;) { const u32 i = next.fetch_add(1, std::memory_order_relaxed); if (i >= n) break; fn(i); } };
-    std::vector<std::thread> pool;
-    for (unsigned t = 1; t < threads; ++t) pool.emplace_back(work);
-    work();
-    for (auto& t : pool) t.join();
+// executor's item split ((expert, 32-output group), then (expert, 16 hidden outputs)). The worker threads are created
+// once and kept (a pool, as Executor keeps its own), so that no thread start or join sits inside a timed call.
+}  // extern "C"
+
+namespace {
+
+class Pool {
+  public:
+    explicit Pool(unsigned threads) : n_(std::max(1u, threads)) {
+        for (unsigned t = 1; t < n_; ++t) workers_.emplace_back([this] { loop(); });
+    }
+    ~Pool() {
+        { std::lock_guard<std::mutex> l(m_); stop_ = true; ++epoch_; }
+        cv_.notify_all();
+        for (auto& t : workers_) t.join();
+    }
+    unsigned size() const { return n_; }
+    void run(u32 n, const std::function<void(u32)>& fn) {
+        { std::lock_guard<std::mutex> l(m_); fn_ = &fn; count_ = n; next_.store(0); busy_ = n_ - 1; ++epoch_; }
+        cv_.notify_all();
+        work();
+        std::unique_lock<std::mutex> l(m_);
+        done_.wait(l, [this] { return busy_ == 0; });
+    }
+
+  private:
+    void work() { for (;;) { const u32 i = next_.fetch_add(1, std::memory_order_relaxed); if (i >= count_) break; (*fn_)(i); } }
+    void loop() {
+        std::uint64_t seen = 0;
+        for (;;) {
+            { std::unique_lock<std::mutex> l(m_); cv_.wait(l, [&] { return epoch_ != seen; }); seen = epoch_; if (stop_) return; }
+            work();
+            { std::lock_guard<std::mutex> l(m_); if (--busy_ == 0) done_.notify_one(); }
+        }
+    }
+    unsigned n_;
+    std::vector<std::thread> workers_;
+    std::mutex m_;
+    std::condition_variable cv_, done_;
+    const std::function<void(u32)>* fn_ = nullptr;
+    u32 count_ = 0;
+    std::atomic<u32> next_{0};
+    unsigned busy_ = 0;
+    std::uint64_t epoch_ = 0;
+    bool stop_ = false;
+};
+
+Pool& pool_of(unsigned threads) {
+    static std::mutex m;
+    static std::unique_ptr<Pool> pool;
+    std::lock_guard<std::mutex> l(m);
+    if (!pool || pool->size() != std::max(1u, threads)) pool.reset(new Pool(threads));
+    return *pool;
 }
 
-double ref_time_layer_q4k(const u8* gate, const u8* up, const u8* down, u32 experts, u32 hidden, u32 inter, u32 top_k,
-                          const float* router_w, const float* x, u32 rows, unsigned threads, u32 reps, float* y, u32* ids_out) {
+// The routed experts of one layer call on given routes: A8 of x, gate/up + SwiGLU + A8 of h, down -> raw slot vectors.
+void experts_q4k(Pool& pool, const u8* gate, const u8* up, const u8* down, u32 hidden, u32 inter, u32 top_k, const float* x, u32 rows,
+                 const u32* ids, std::vector<float>& raw) {
     const ex::detail::Kernels* k = &ex::detail::scalar_kernels();
     if (strix::cpu::caps().avx2) if (const auto* a = strix::cpu::arch::avx2::expert_kernels()) k = a;
     const u32 blocks = hidden / 256, groups = inter / 32, dblocks = inter / 256;
     const std::size_t grow = (std::size_t)blocks * 144, drow = (std::size_t)dblocks * 144;
+    const auto& exp = zero_exp();
+    // A8 of the input (strix::cpu reference table)
+    std::vector<i8> xc((std::size_t)rows * hidden);
+    std::vector<float> xd((std::size_t)rows * hidden / 32);
+    std::vector<i32> xs(xd.size());
+    for (u32 r = 0; r < rows; ++r)
+        strix::cpu::reference_kernels().quantize_a8(x + (std::size_t)r * hidden, hidden, xc.data() + (std::size_t)r * hidden,
+                                                   xd.data() + (std::size_t)r * hidden / 32, xs.data() + (std::size_t)r * hidden / 32);
+    // group slots by expert (stable), as Executor::prepare
+    const std::size_t slots = (std::size_t)rows * top_k;
+    std::vector<u32> order(slots);
+    for (u32 i = 0; i < order.size(); ++i) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](u32 a, u32 b) { return ids[a] < ids[b]; });
+    std::vector<u32> ex_begin, ex_id;
+    for (u32 p = 0; p < order.size(); ++p)
+        if (p == 0 || ids[order[p]] != ids[order[p - 1]]) { ex_id.push_back(ids[order[p]]); ex_begin.push_back(p); }
+    ex_begin.push_back((u32)order.size());
+    std::vector<ex::RowA8> rowa(rows);
+    for (u32 r = 0; r < rows; ++r) rowa[r] = {xc.data() + (std::size_t)r * hidden, xd.data() + (std::size_t)r * hidden / 32, xs.data() + (std::size_t)r * hidden / 32};
+    std::vector<i8> hc(slots * inter);
+    std::vector<float> hd(slots * groups);
+    std::vector<i32> hs(slots * groups);
+    const u32 n_ex = (u32)ex_id.size();
+    pool.run(n_ex * groups, [&](u32 item) {
+        const u32 e = item / groups, grp = item % groups, expert = ex_id[e];
+        for (u32 p = ex_begin[e]; p < ex_begin[e + 1]; p += ex::detail::kMaxAssign) {
+            const u32 na = std::min(ex::detail::kMaxAssign, ex_begin[e + 1] - p);
+            const ex::RowA8* rp[ex::detail::kMaxAssign];
+            for (u32 a = 0; a < na; ++a) rp[a] = &rowa[order[p + a] / top_k];
+            float g[ex::detail::kMaxAssign][32], u[ex::detail::kMaxAssign][32];
+            for (u32 l = 0; l < 32; ++l) {
+                float tg[ex::detail::kMaxAssign], tu[ex::detail::kMaxAssign];
+                const std::size_t off = ((std::size_t)expert * inter + grp * 32 + l) * grow;
+                k->gate[0](gate + off, blocks, rp, na, tg);
+                k->gate[0](up + off, blocks, rp, na, tu);
+                for (u32 a = 0; a < na; ++a) { g[a][l] = tg[a]; u[a][l] = tu[a]; }
+            }
+            for (u32 a = 0; a < na; ++a) {
+                float hv[32];
+                for (u32 l = 0; l < 32; ++l) hv[l] = (g[a][l] / (1.0F + exp.expf(-g[a][l]))) * u[a][l];
+                const std::size_t s = order[p + a];
+                strix::cpu::reference_kernels().quantize_a8(hv, 32, hc.data() + s * inter + grp * 32, &hd[s * groups + grp], &hs[s * groups + grp]);
+            }
+        }
+    });
+    raw.assign(slots * hidden, 0.0F);
+    pool.run(n_ex * (hidden / 16), [&](u32 item) {
+        const u32 per = hidden / 16, e = item / per, o0 = (item % per) * 16, expert = ex_id[e];
+        for (u32 p = ex_begin[e]; p < ex_begin[e + 1]; p += ex::detail::kMaxAssign) {
+            const u32 na = std::min(ex::detail::kMaxAssign, ex_begin[e + 1] - p);
+            ex::RowA8 ha[ex::detail::kMaxAssign];
+            const ex::RowA8* rp[ex::detail::kMaxAssign];
+            for (u32 a = 0; a < na; ++a) {
+                const std::size_t s = order[p + a];
+                ha[a] = {hc.data() + s * inter, hd.data() + s * groups, hs.data() + s * groups};
+                rp[a] = &ha[a];
+            }
+            for (u32 l = 0; l < 16; ++l) {
+                float t[ex::detail::kMaxAssign];
+                k->gate[0](down + ((std::size_t)expert * hidden + o0 + l) * drow, dblocks, rp, na, t);
+                for (u32 a = 0; a < na; ++a) raw[(std::size_t)order[p + a] * hidden + o0 + l] = t[a];
+            }
+        }
+    });
+}
+
+}  // namespace
+
+extern "C" {
+
+// Router (softmax policy) + routed experts + Qwen merge, `reps` times. Returns seconds; y receives the last call's output
+// so the caller can check it.
+double ref_time_layer_q4k(const u8* gate, const u8* up, const u8* down, u32 experts, u32 hidden, u32 inter, u32 top_k,
+                          const float* router_w, const float* x, u32 rows, unsigned threads, u32 reps, float* y, u32* ids_out) {
+    Pool& pool = pool_of(threads);
     const strix::moe::RoutePolicy policy{strix::moe::RouteScore::softmax, false, strix::moe::RouteKey::float_serial,
                                          strix::moe::RouteOrder::selection, experts, top_k, 1U, 1U, true, true, 1e-20F, 1.0F};
-    const auto& exp = zero_exp();
     const auto t0 = std::chrono::steady_clock::now();
     for (u32 rep = 0; rep < reps; ++rep) {
-        // A8 of the input (strix::cpu reference table)
-        std::vector<i8> xc((std::size_t)rows * hidden);
-        std::vector<float> xd((std::size_t)rows * hidden / 32);
-        std::vector<i32> xs(xd.size());
-        for (u32 r = 0; r < rows; ++r)
-            strix::cpu::reference_kernels().quantize_a8(x + (std::size_t)r * hidden, hidden, xc.data() + (std::size_t)r * hidden,
-                                                       xd.data() + (std::size_t)r * hidden / 32, xs.data() + (std::size_t)r * hidden / 32);
         // router: declared dot order (src/ds41_moe.cpp:72-82), softmax transform, k-pass selection
         std::vector<float> logits((std::size_t)rows * experts);
-        parallel_items(threads, rows * experts, [&](u32 i) {
+        pool.run(rows * experts, [&](u32 i) {
             const u32 r = i / experts, e = i % experts;
             float lanes[32] = {};
             for (u32 c = 0; c < hidden; ++c) lanes[c % 32] = lanes[c % 32] + router_w[(std::size_t)e * hidden + c] * x[(std::size_t)r * hidden + c];
@@ -350,67 +464,44 @@ double ref_time_layer_q4k(const u8* gate, const u8* up, const u8* down, u32 expe
             strix::moe::route_select_ref(policy, s, {}, std::span<u32>(ids.data() + (std::size_t)r * top_k, top_k),
                                          std::span<float>(rw.data() + (std::size_t)r * top_k, top_k));
         }
-        // group slots by expert (stable), as Executor::prepare
-        std::vector<u32> order(ids.size());
-        for (u32 i = 0; i < order.size(); ++i) order[i] = i;
-        std::stable_sort(order.begin(), order.end(), [&](u32 a, u32 b) { return ids[a] < ids[b]; });
-        std::vector<u32> ex_begin, ex_id;
-        for (u32 p = 0; p < order.size(); ++p)
-            if (p == 0 || ids[order[p]] != ids[order[p - 1]]) { ex_id.push_back(ids[order[p]]); ex_begin.push_back(p); }
-        ex_begin.push_back((u32)order.size());
-        std::vector<ex::RowA8> rowa(rows);
-        for (u32 r = 0; r < rows; ++r) rowa[r] = {xc.data() + (std::size_t)r * hidden, xd.data() + (std::size_t)r * hidden / 32, xs.data() + (std::size_t)r * hidden / 32};
-        const std::size_t slots = order.size();
-        std::vector<i8> hc(slots * inter);
-        std::vector<float> hd(slots * groups);
-        std::vector<i32> hs(slots * groups);
-        const u32 n_ex = (u32)ex_id.size();
-        parallel_items(threads, n_ex * groups, [&](u32 item) {
-            const u32 e = item / groups, grp = item % groups, expert = ex_id[e];
-            for (u32 p = ex_begin[e]; p < ex_begin[e + 1]; p += ex::detail::kMaxAssign) {
-                const u32 na = std::min(ex::detail::kMaxAssign, ex_begin[e + 1] - p);
-                const ex::RowA8* rp[ex::detail::kMaxAssign];
-                for (u32 a = 0; a < na; ++a) rp[a] = &rowa[order[p + a] / top_k];
-                float g[ex::detail::kMaxAssign][32], u[ex::detail::kMaxAssign][32];
-                for (u32 l = 0; l < 32; ++l) {
-                    float tg[ex::detail::kMaxAssign], tu[ex::detail::kMaxAssign];
-                    const std::size_t off = ((std::size_t)expert * inter + grp * 32 + l) * grow;
-                    k->gate[0](gate + off, blocks, rp, na, tg);
-                    k->gate[0](up + off, blocks, rp, na, tu);
-                    for (u32 a = 0; a < na; ++a) { g[a][l] = tg[a]; u[a][l] = tu[a]; }
-                }
-                for (u32 a = 0; a < na; ++a) {
-                    float hv[32];
-                    for (u32 l = 0; l < 32; ++l) hv[l] = (g[a][l] / (1.0F + exp.expf(-g[a][l]))) * u[a][l];
-                    const std::size_t s = order[p + a];
-                    strix::cpu::reference_kernels().quantize_a8(hv, 32, hc.data() + s * inter + grp * 32, &hd[s * groups + grp], &hs[s * groups + grp]);
-                }
-            }
-        });
-        std::vector<float> raw(slots * hidden);
-        parallel_items(threads, n_ex * (hidden / 16), [&](u32 item) {
-            const u32 per = hidden / 16, e = item / per, o0 = (item % per) * 16, expert = ex_id[e];
-            for (u32 p = ex_begin[e]; p < ex_begin[e + 1]; p += ex::detail::kMaxAssign) {
-                const u32 na = std::min(ex::detail::kMaxAssign, ex_begin[e + 1] - p);
-                ex::RowA8 ha[ex::detail::kMaxAssign];
-                const ex::RowA8* rp[ex::detail::kMaxAssign];
-                for (u32 a = 0; a < na; ++a) {
-                    const std::size_t s = order[p + a];
-                    ha[a] = {hc.data() + s * inter, hd.data() + s * groups, hs.data() + s * groups};
-                    rp[a] = &ha[a];
-                }
-                for (u32 l = 0; l < 16; ++l) {
-                    float t[ex::detail::kMaxAssign];
-                    k->gate[0](down + ((std::size_t)expert * hidden + o0 + l) * drow, dblocks, rp, na, t);
-                    for (u32 a = 0; a < na; ++a) raw[(std::size_t)order[p + a] * hidden + o0 + l] = t[a];
-                }
-            }
-        });
+        std::vector<float> raw;
+        experts_q4k(pool, gate, up, down, hidden, inter, top_k, x, rows, ids.data(), raw);
         // Qwen merge (combine_ref fma_f32, base 0)
         std::vector<float> zero((std::size_t)rows * hidden, 0.0F);
         strix::moe::combine_ref(strix::moe::CombineForm::fma_f32, rows, top_k, hidden, rw, raw, zero, std::span<float>(y, (std::size_t)rows * hidden));
         if (ids_out) std::memcpy(ids_out, ids.data(), ids.size() * 4);
     }
+    return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+}
+
+// The routed experts alone on the caller's routes (ids [rows][top_k] into the given tensors), `reps` times: what the
+// benchmark's CPU arm times for a layer whose router the reference does not have (group-limited selection). raw_out
+// [rows * top_k][hidden] receives the last call's raw slot vectors.
+double ref_time_experts_q4k(const u8* gate, const u8* up, const u8* down, u32 hidden, u32 inter, u32 top_k, const float* x, u32 rows,
+                            const u32* ids, unsigned threads, u32 reps, float* raw_out) {
+    Pool& pool = pool_of(threads);
+    std::vector<float> raw;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (u32 rep = 0; rep < reps; ++rep) experts_q4k(pool, gate, up, down, hidden, inter, top_k, x, rows, ids, raw);
+    const double sec = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if (raw_out) std::memcpy(raw_out, raw.data(), raw.size() * 4);
+    return sec;
+}
+
+// The dense Q8_0 x A8 product of the CPU backend (strix::cpu::Kernels::gemv_q8_0_a8, scalar) with the output rows
+// partitioned over the host threads, which docs/architecture/backends.md:94-98 allows a Stream to do. `reps` times.
+double ref_time_gemv_q8_0_a8(const u8* weight, u32 row_bytes, u32 width, u32 count, u32 rows, const i8* codes, const float* deltas,
+                             unsigned threads, u32 reps, float* out) {
+    Pool& pool = pool_of(threads);
+    const auto& kernels = strix::cpu::reference_kernels();
+    const u32 chunk = 64, chunks = (count + chunk - 1) / chunk;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (u32 rep = 0; rep < reps; ++rep)
+        pool.run(chunks, [&](u32 item) {
+            const u32 c0 = item * chunk, n = std::min(chunk, count - c0);
+            const strix::cpu::Q8a8View v{weight + (std::size_t)c0 * row_bytes, codes, deltas, out + c0, row_bytes, width, n, rows, width, count, 0U};
+            kernels.gemv_q8_0_a8(v, {});
+        });
     return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
 }
 

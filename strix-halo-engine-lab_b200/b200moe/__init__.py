@@ -114,6 +114,17 @@ class FfnView(C.Structure):
                 ("stage_events", vp), ("summary", vp)]
 
 
+class EpDesc(C.Structure):
+    _fields_ = [("shape", Shape), ("policy", RoutePolicy), ("world", u32), ("rank", u32), ("rows_per_rank", u32), ("wait_polls", u32),
+                ("windows", vp)]
+
+
+class EpStepView(C.Structure):
+    _fields_ = [("weights", ExpertWeights), ("router_weight", vp), ("logit_bias", vp), ("select_bias", vp), ("x", vp), ("x_is_bf16", u32),
+                ("rows", u32), ("shared", vp), ("y", vp), ("y_bf16", vp), ("summary", vp), ("workspace", vp), ("workspace_bytes", u64),
+                ("grouped_min_rows", u32), ("stage_events", vp)]
+
+
 class DenseView(C.Structure):
     _fields_ = [("shape", Shape), ("weights", ExpertWeights), ("rows", u32), ("x", A8Rows), ("y", vp), ("y_bf16", vp),
                 ("workspace", vp), ("workspace_bytes", u64)]
@@ -144,7 +155,8 @@ EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", 
            "b200moe_build_routes_static", "b200moe_gate_row_bytes",
            "b200moe_down_row_bytes", "b200moe_expert_bytes", "b200moe_gate_up", "b200moe_down", "b200moe_combine",
            "b200moe_canonical_sum", "b200moe_fold_parts", "b200moe_select_owner_slots", "b200moe_peer_buffer_create",
-           "b200moe_peer_buffer_open", "b200moe_peer_buffer_close", "b200moe_peer_buffer_destroy", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
+           "b200moe_peer_buffer_open", "b200moe_peer_buffer_close", "b200moe_peer_buffer_destroy",
+           "b200moe_ep_window_bytes", "b200moe_ep_create", "b200moe_ep_destroy", "b200moe_ep_workspace_bytes", "b200moe_ep_ffn", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
            "b200moe_ffn", "b200moe_ffn_host", "b200moe_dense_ffn", "b200moe_gguf_open", "b200moe_gguf_close",
            "b200moe_residency_create", "b200moe_residency_destroy", "b200moe_residency_map",
            "b200moe_residency_get_stats", "b200moe_residency_table", "b200moe_residency_choose_victims",
@@ -216,6 +228,16 @@ def lib():
         for n in ("b200moe_peer_buffer_close", "b200moe_peer_buffer_destroy"):
             getattr(L, n).restype = C.c_int
             getattr(L, n).argtypes = [vp]
+        L.b200moe_ep_window_bytes.restype = u64
+        L.b200moe_ep_window_bytes.argtypes = [C.POINTER(Shape), u32, u32]
+        L.b200moe_ep_create.restype = C.c_int
+        L.b200moe_ep_create.argtypes = [C.POINTER(EpDesc), C.POINTER(vp)]
+        L.b200moe_ep_destroy.restype = None
+        L.b200moe_ep_destroy.argtypes = [vp]
+        L.b200moe_ep_workspace_bytes.restype = u64
+        L.b200moe_ep_workspace_bytes.argtypes = [vp]
+        L.b200moe_ep_ffn.restype = C.c_int
+        L.b200moe_ep_ffn.argtypes = [vp, C.POINTER(EpStepView), vp]
         L.b200moe_fold_parts.restype = C.c_int
         L.b200moe_fold_parts.argtypes = [vp, u32, u64, vp, u64, vp, vp, vp]
         L.b200moe_select_owner_slots.restype = C.c_int

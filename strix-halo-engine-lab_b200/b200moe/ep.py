@@ -28,8 +28,87 @@ import ctypes as C
 import torch
 import torch.distributed as dist
 
-from . import COMBINE_FMA_SLOTS, COMBINE_PARTS, check, lib, ptr, stream_ptr
+from . import COMBINE_FMA_SLOTS, COMBINE_PARTS, EpDesc, EpStepView, ExpertWeights, check, lib, ptr, stream_ptr
 from . import ops
+
+
+class PeerEpFfn:
+    """b200moe_ep_ffn: the whole expert-parallel step of a rank behind ONE C call - route, dispatch, local experts, return,
+    fold - with both exchanges done by the library's own kernels storing into the peers' windows over NVLink (no
+    collective, no host wait; bounded flag waits on the device). torch.distributed is used once, at set-up, to hand the
+    windows' CUDA IPC handles round; world 1 (no process group) runs the same kernels against the rank's own window.
+    gate / up / down hold the rank's experts only; every rank passes the same number of rows per step."""
+
+    def __init__(self, shape, policy, router_weight, gate, up, down, rows, group=None, logit_bias=None, select_bias=None,
+                 wait_polls=0, grouped_min_rows=0, extra_windows=0):
+        L = lib()
+        multi = dist.is_available() and dist.is_initialized()
+        self.group = group
+        self.world = dist.get_world_size(group) if multi else 1 + extra_windows
+        self.rank = dist.get_rank(group) if multi else 0
+        self.shape, self.policy, self.rows = shape, policy, rows
+        self.router_weight, self.gate, self.up, self.down = router_weight, gate, up, down
+        self.logit_bias, self.select_bias, self.grouped_min_rows = logit_bias, select_bias, grouped_min_rows
+        nbytes = int(L.b200moe_ep_window_bytes(C.byref(shape), self.world, rows))
+        if nbytes == 0:
+            raise ValueError("expert parallelism: 1 <= world <= 8 and rows >= 1")
+        self.mine, self.opened, self.silent = C.c_void_p(), [], []
+        handle = C.create_string_buffer(64)
+        check(L.b200moe_peer_buffer_create(nbytes, C.byref(self.mine), handle))
+        windows = (C.c_void_p * self.world)()
+        if multi:
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, handle.raw, group=group)
+            for r in range(self.world):
+                if r == self.rank:
+                    windows[r] = self.mine.value
+                else:
+                    q = C.c_void_p()
+                    check(L.b200moe_peer_buffer_open(everyone[r], C.byref(q)))
+                    self.opened.append(q.value)
+                    windows[r] = q.value
+        else:
+            windows[0] = self.mine.value
+            for r in range(1, self.world):   # windows nobody serves (tests of the bounded wait): plain local buffers
+                q, h = C.c_void_p(), C.create_string_buffer(64)
+                check(L.b200moe_peer_buffer_create(nbytes, C.byref(q), h))
+                self.silent.append(q.value)
+                windows[r] = q.value
+        desc = EpDesc(shape, policy, self.world, self.rank, rows, wait_polls, C.cast(windows, C.c_void_p))
+        self.handle = C.c_void_p()
+        check(L.b200moe_ep_create(C.byref(desc), C.byref(self.handle)))
+        self.ws_bytes = int(L.b200moe_ep_workspace_bytes(self.handle))
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=gate.device)
+        if multi:
+            dist.barrier(group=group)
+
+    def view(self, x, y, shared=None, summary=None, events=None):
+        ev = C.cast(events, C.c_void_p) if events is not None else None
+        return EpStepView(ExpertWeights(ptr(self.gate), ptr(self.up), ptr(self.down)), ptr(self.router_weight), ptr(self.logit_bias),
+                          ptr(self.select_bias), ptr(x), int(x.dtype == torch.bfloat16), x.shape[0], ptr(shared), ptr(y), None,
+                          ptr(summary), ptr(self.ws), self.ws_bytes, self.grouped_min_rows, ev)
+
+    def __call__(self, x, shared=None, y=None, summary=None):
+        if y is None:
+            y = torch.empty((x.shape[0], self.shape.hidden), dtype=torch.float32, device=x.device)
+        check(lib().b200moe_ep_ffn(self.handle, C.byref(self.view(x, y, shared, summary)), stream_ptr()))
+        return y
+
+    def close(self):
+        L = lib()
+        torch.cuda.synchronize()
+        if self.group is not None or (dist.is_available() and dist.is_initialized()):
+            dist.barrier(group=self.group)
+        if self.handle:
+            L.b200moe_ep_destroy(self.handle)
+            self.handle = None
+        for q in self.opened:
+            L.b200moe_peer_buffer_close(q)
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier(group=self.group)
+        for q in self.silent + ([self.mine.value] if self.mine else []):
+            L.b200moe_peer_buffer_destroy(q)
+        self.opened, self.silent, self.mine = [], [], None
 
 
 class DeviceKernels:

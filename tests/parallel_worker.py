@@ -110,7 +110,7 @@ class OracleDenseKernels:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["ep_parts", "ep_parts_peer", "ep_fma", "tp", "tp_allreduce"])
+    ap.add_argument("--case", required=True, choices=["ep_parts", "ep_parts_peer", "ep_fma", "ep_c_abi", "tp", "tp_allreduce"])
     ap.add_argument("--backend", default="gloo")
     ap.add_argument("--out", required=True)
     a = ap.parse_args()
@@ -127,7 +127,20 @@ def main():
         orc = O.Oracle()
     put = lambda arr: torch.from_numpy(np.ascontiguousarray(arr)).to(dev)
 
-    if a.case.startswith("ep"):
+    if a.case == "ep_c_abi":   # the whole step behind b200moe_ep_ffn: peer-store dispatch and return, no collective on the path
+        gate, up, down, rw, x, shared = ep_inputs(world)
+        per = E // world
+        gb, db = (I * (H // 256) * 144), (H * (I // 256) * 144)
+        sl = lambda t, b: put(t.reshape(-1)[rank * per * b:(rank + 1) * per * b])
+        layer = ep.PeerEpFfn(ops.make_shape(H, I, E, K, 12, 12), ops.softmax_policy(E, K), put(rw), sl(gate, gb), sl(up, gb), sl(down, db), ROWS)
+        summary = torch.zeros(1, dtype=torch.int32, device=dev)
+        for step in range(5):          # odd and even steps: both halves of the window, the step counters, a changing x
+            scale = np.float32(1.0 + 0.25 * step)
+            y = layer(put(x[rank * ROWS:(rank + 1) * ROWS] * scale), put(shared[rank * ROWS:(rank + 1) * ROWS]), summary=summary)
+        torch.cuda.synchronize()
+        assert int(summary.item()) == 0, f"job summary {int(summary.item()):#x}"
+        layer.close()
+    elif a.case.startswith("ep"):
         form = b200moe.COMBINE_PARTS if a.case.startswith("ep_parts") else b200moe.COMBINE_FMA_SLOTS
         gate, up, down, rw, x, shared = ep_inputs(world)
         per = E // world

@@ -765,6 +765,57 @@ def test_layer_expert_parallel_fold(gpu, oracle):
     assert same(host(part), oracle.combine(O.COMBINE_PARTS, ex["raw"], wts, ids, parts=parts, part_experts=per, only_part=p))
 
 
+def test_ep_entry_point_single_rank(gpu, oracle):
+    """b200moe_ep_ffn with one rank: the same kernels as on N GPUs (route, dispatch into the rank's own window, flag
+    waits, restricted routes, combine through the block table, fold), compared with the oracle's PARTS combine with one
+    part; FP32 and bfloat16 inputs, five steps (both halves of the window, the device step counter)."""
+    import b200moe
+    from b200moe import ep, ops, synth
+    rng = np.random.default_rng(41)
+    E, H, I, K, rows = 16, 512, 256, 4, 5
+    gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
+    rw = synth.router_weight(rng, E, H)
+    sh, osh = shape_pair(H, I, E, K, 12, 12)
+    layer = ep.PeerEpFfn(sh, ops.softmax_policy(E, K), dv(rw, gpu), dv(gate, gpu), dv(up, gpu), dv(down, gpu), rows)
+    summary = torch.zeros(1, dtype=torch.int32, device=gpu)
+    try:
+        for step in range(5):
+            x = synth.bf16_round(synth.activations(rng, rows, H))
+            shared = rng.standard_normal((rows, H), dtype=np.float32)
+            want = oracle.ffn(osh, O.softmax_policy(E, K), gate, up, down, rw, x, O.COMBINE_PARTS, parts=1, part_experts=E, shared=shared)
+            gx = dv(x, gpu).to(torch.bfloat16) if step % 2 else dv(x, gpu)
+            y = layer(gx, dv(shared, gpu), summary=summary)
+            assert same(host(y), want["y"]), step
+            assert host(summary)[0] == 0
+    finally:
+        layer.close()
+
+
+def test_ep_wait_for_a_silent_peer_is_bounded(gpu, oracle):
+    """Failure detection without a fault: a two-rank set-up whose second window belongs to nobody, so no peer ever signals.
+    The dispatch wait gives up after wait_polls polls (well under a second here), the step returns, the job summary holds
+    B200MOE_JOB_WAIT_ABORTED and y keeps the caller's bytes; the device stays usable (a normal call follows)."""
+    import b200moe
+    from b200moe import ep, ops, synth
+    rng = np.random.default_rng(42)
+    E, H, I, K, rows = 16, 512, 256, 4, 3
+    gate, up, down = synth.expert_tensors(rng, E // 2, H, I, 12, 12)
+    rw = synth.router_weight(rng, E, H)
+    sh, _ = shape_pair(H, I, E, K, 12, 12)
+    layer = ep.PeerEpFfn(sh, ops.softmax_policy(E, K), dv(rw, gpu), dv(gate, gpu), dv(up, gpu), dv(down, gpu), rows, wait_polls=2000,
+                         extra_windows=1)
+    try:
+        summary = torch.zeros(1, dtype=torch.int32, device=gpu)
+        y = torch.full((rows, H), 3.0, device=gpu)
+        layer(dv(synth.activations(rng, rows, H), gpu), y=y, summary=summary)
+        torch.cuda.synchronize()
+        assert u32(summary)[0] & b200moe.JOB_WAIT_ABORTED
+        assert (host(y) == 3.0).all()
+    finally:
+        layer.close()
+    test_quantize_a8(gpu, oracle)   # the context is intact
+
+
 def test_dense_ffn_tensor_parallel_split(gpu, oracle):
     """Config-5 family at reduced size: dense Q4_K SwiGLU block, column-parallel gate/up and row-parallel down over
     whole super-blocks; each share's partial equals the oracle's partial bit for bit (modulo the SwiGLU note above),

@@ -58,10 +58,11 @@ def max_rel(a, b):
     return float(np.max(np.abs(a - b)) / max(np.max(np.abs(b)), 1e-30))
 
 
-def ep_expected(oracle, form, world):
+def ep_expected(oracle, form, world, x_scale=1.0):
     gate, up, down, rw, x, shared = W.ep_inputs(world)
     sh = O.Shape(W.H, W.I, W.E, W.K, 12, 12, float("inf"))
-    return oracle.ffn(sh, O.softmax_policy(W.E, W.K), gate, up, down, rw, x, form, parts=world, part_experts=W.E // world, shared=shared)["y"]
+    return oracle.ffn(sh, O.softmax_policy(W.E, W.K), gate, up, down, rw, x * np.float32(x_scale), form, parts=world, part_experts=W.E // world,
+                      shared=shared)["y"]
 
 
 def tp_expected(oracle, world):
@@ -116,6 +117,19 @@ def test_expert_parallel_two_gpus_nccl(oracle, case, form):
     # the Qwen-family SwiGLU may differ by one code in rare elements (see test_gpu_parity.py): tolerance, bits reported
     assert max_rel(got, want) <= REL_TOL
     print("bit-exact:", np.array_equal(bits(got), bits(want)))
+
+
+@pytest.mark.gpu
+def test_expert_parallel_two_gpus_c_abi(oracle):
+    """b200moe_ep_ffn on two GPUs: dispatch and return are the library's peer stores with flag waits (no collective);
+    five steps, the last one compared with the oracle's single-process run over the whole window, bit for bit."""
+    if not _two_gpus():
+        pytest.skip("needs 2 CUDA devices")
+    world = 2
+    got = np.concatenate(run_ranks("ep_c_abi", "nccl", world))
+    want = ep_expected(oracle, 0, world, x_scale=2.0)   # step 4 of the worker: x * (1 + 0.25 * 4)
+    assert max_rel(got, want) <= REL_TOL
+    assert np.array_equal(bits(got), bits(want))
 
 
 @pytest.mark.gpu
