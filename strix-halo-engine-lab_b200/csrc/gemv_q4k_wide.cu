@@ -18,6 +18,14 @@
 //    (pair p, row): a lane walks its row's super-blocks in ascending order across the item's stages, the serial chains
 //    acc_p += pair_p never leave their lane, and (a0 + a1) + (a2 + a3) is two xor-shuffles at the end of the item.
 //  * gate/up: the group meets on an mbarrier once per item and eight warps run SwiGLU + the A8 rule of one entry each.
+//  * Two forms of the integer dots, chosen per item by its entry count. Up to kMmaMinEntries - 1 entries: dp4a, lane =
+//    (pair, row), 16 dp4a per (super-block, pair, entry). From kMmaMinEntries entries: the warp's 8 rows x up to 8 entries
+//    x 32 weights of a group are ONE mma.sync.m16n8k32 (A = the entries' codes, signed; B = the rows' nibbles as unsigned
+//    bytes, high nibbles left in place as 16 q; the k order inside a group is permuted the same way on both sides, which
+//    an exact integer sum does not see). The accumulator fragment gives lane (entry, t) the dots of rows 2t and 2t + 1,
+//    and the lane runs the same FP32 operation sequence on them with the rows' factors fetched from a per-warp scratch:
+//    the kernel is bound by issue slots (ncu: 76 % issue active at config 4), and this form needs about half the
+//    instructions of the dp4a form at 8 entries. Both forms produce the contract's bits.
 //
 // Every wait is bounded (plan.wait_limit polls): a waiter that runs out raises the CTA's abort flag, every role leaves
 // its loops, the producers wait (bounded) for the copies they still have in flight, B200MOE_JOB_WAIT_ABORTED is set in the
@@ -42,6 +50,8 @@ constexpr u32 kThreads = (kConsumerWarps + kGroups) * 32;  // one producer warp 
 constexpr u32 kItemRows = 64;
 constexpr u32 kEndItem = 0xffffffffu;
 constexpr u32 kCostFixed = 4, kCostEntry = 3;           // estimated cost of an item: fixed + per entry
+constexpr u32 kMmaMinEntries = 5;                       // items with at least this many entries take the mma form
+constexpr u32 kFacFloats = 128;                         // per-warp scratch of the mma form: [D, DM, D', DM'][pair][row]
 constexpr u32 kSmemBudget = 227u * 1024u;
 constexpr u32 kDefaultWaitLimit = 1u << 22;
 
@@ -52,7 +62,7 @@ struct WidePlan {
     u32 stages;         // ring depth per group
     u32 row_seg_bytes;  // S * 144
     u32 w_bytes;        // 64 * row_seg_bytes
-    u32 x_entry_bytes;  // S * 320: codes, deltas, sums of one entry over the stage's K range
+    u32 x_entry_bytes;  // >= S * 320: codes, deltas, sums of one entry over the stage's K range (+ padding)
     u32 stage_bytes;
     u32 n_chunks;       // items per (virtual) expert
     u32 max_union;      // bound of the union
@@ -74,7 +84,13 @@ struct WideArgs {
     u32 out_width;         // inter (gate/up) or hidden (down)
 };
 
-struct VExpert { u32 expert, begin, ne, cum; };
+struct VExpert {  // one word: expert index (10 bits, experts <= 1024), first entry in the routes (14 bits, slots <= 8192), entries (4 bits)
+    u32 bits;
+    __host__ __device__ static VExpert make(u32 expert, u32 begin, u32 ne) { return VExpert{expert | (begin << 10) | (ne << 24)}; }
+    __host__ __device__ u32 expert() const { return bits & 0x3ffu; }
+    __host__ __device__ u32 begin() const { return (bits >> 10) & 0x3fffu; }
+    __host__ __device__ u32 ne() const { return bits >> 24; }
+};
 
 __device__ __forceinline__ u32 warp_inclusive_scan(u32 v, u32 lane) {
 #pragma unroll
@@ -85,15 +101,15 @@ __device__ __forceinline__ u32 virtual_cost(u32 ne) { return kCostFixed + kCostE
 
 // First item whose cumulative cost start is >= B (items: virtual expert major, chunks ascending; an item of virtual
 // expert jv costs virtual_cost(ne) and starts at cum[jv] * nc + chunk * cost). B >= total * nc gives n_virtual * nc.
-__device__ u32 item_at(const VExpert* table, u32 n_virtual, u32 nc, u64 total_items_cost, u64 B) {
+__device__ u32 item_at(const VExpert* table, const u32* cum, u32 n_virtual, u32 nc, u64 total_items_cost, u64 B) {
     if (B >= total_items_cost) return n_virtual * nc;
     u32 lo = 0, hi = n_virtual - 1;  // last jv with cum[jv] * nc <= B
     while (lo < hi) {
         const u32 mid = (lo + hi + 1) >> 1;
-        if (u64(table[mid].cum) * nc <= B) lo = mid; else hi = mid - 1;
+        if (u64(cum[mid]) * nc <= B) lo = mid; else hi = mid - 1;
     }
-    const u32 c = virtual_cost(table[lo].ne);
-    const u64 excl = u64(table[lo].cum) * nc;
+    const u32 c = virtual_cost(table[lo].ne());
+    const u64 excl = u64(cum[lo]) * nc;
     return lo * nc + static_cast<u32>((B - excl + c - 1) / c);
 }
 
@@ -135,6 +151,59 @@ __device__ __forceinline__ void stage_rows_n(u32 nr, const uint4* blk, u32 nbk, 
     }
 }
 
+// ---- the mma form of one stage ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_s8u8(int& c0, int& c1, u32 a0, u32 a2, u32 b0, u32 b1) {
+    // D (16 x 8, s32) = A (16 x 32, s8, row) * B (32 x 8, u8, col); rows 8 .. 15 of A are zero (at most 8 entries).
+    int c2, c3;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+                 : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+                 : "r"(a0), "r"(0), "r"(a2), "r"(0), "r"(b0), "r"(b1), "r"(0));
+}
+// x_2p + x_2p+1 of one (row, entry, super-block, pair) from the two exact group dots; hi16 = 16 * dot of the odd group.
+__device__ __forceinline__ float pair_from_dots(float Dl, float DMl, float Dh, float DMh, int lo, int hi16, float El, float Eh, float Sl, float Sh) {
+    const float xl = __fmul_rn(El, __fsub_rn(__fmul_rn(Dl, static_cast<float>(lo)), __fmul_rn(DMl, Sl)));
+    const float xh = __fmul_rn(Eh, __fsub_rn(__fmul_rn(Dh, static_cast<float>(hi16 >> 4)), __fmul_rn(DMh, Sh)));
+    return __fadd_rn(xl, xh);
+}
+// One stage of the warp's 8 weight rows against up to 8 staged A8 rows with tensor-core dots. w8: the warp's first row of
+// the stage (rows row_seg_bytes apart); fac: the warp's scratch. Lane = (e = lane >> 2, t = lane & 3): acc[4 * i + p] is the
+// chain acc_p of (row 2t + i, entry e). Lanes of absent entries compute on stale shared memory and are never stored.
+__device__ __forceinline__ void stage_rows_mma(const unsigned char* w8, u32 row_seg_bytes, u32 nbk, u32 lane, const unsigned char* xs,
+                                               u32 x_entry_bytes, u32 S, float* fac, float* acc) {
+    const u32 p = lane >> 3, rr = lane & 7u;   // factor decode: lane = (pair, row), as in the dp4a form
+    const u32 e = lane >> 2, t = lane & 3u;    // mma fragments: lane = (entry or weight row, k slice)
+    const unsigned char* xe = xs + e * x_entry_bytes;
+    const unsigned char* wdec = w8 + rr * row_seg_bytes;
+    const unsigned char* wfrag = w8 + e * row_seg_bytes + 16u + 8u * t;   // B fragment: weight row n = lane >> 2
+#pragma unroll 1
+    for (u32 b = 0; b < nbk; ++b) {
+        const uint4 hdr = *reinterpret_cast<const uint4*>(wdec + kQ4KBlock * b);
+        const Factors f = q4k_factors(hdr, p);
+        __syncwarp();   // the previous block's readers are done with the scratch
+        fac[(0 * 4 + p) * 8 + rr] = f.Dl; fac[(1 * 4 + p) * 8 + rr] = f.DMl; fac[(2 * 4 + p) * 8 + rr] = f.Dh; fac[(3 * 4 + p) * 8 + rr] = f.DMh;  // bank = lane
+        __syncwarp();
+        const float4 e0 = *reinterpret_cast<const float4*>(xe + 256u * S + 32u * b), e1 = *reinterpret_cast<const float4*>(xe + 256u * S + 32u * b + 16u);
+        const int4 s0 = *reinterpret_cast<const int4*>(xe + 288u * S + 32u * b), s1 = *reinterpret_cast<const int4*>(xe + 288u * S + 32u * b + 16u);
+        const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+        const int Sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int pp = 0; pp < 4; ++pp) {
+            const uint2 w = *reinterpret_cast<const uint2*>(wfrag + kQ4KBlock * b + 32u * pp);   // 8 bytes = 16 nibbles: k slice t of groups 2pp, 2pp + 1
+            const uint2 al = *reinterpret_cast<const uint2*>(xe + 256u * b + 64u * pp + 8u * t);          // the entry's codes, group 2pp, same k slice
+            const uint2 ah = *reinterpret_cast<const uint2*>(xe + 256u * b + 64u * pp + 32u + 8u * t);    // group 2pp + 1
+            int l0, l1, h0, h1;
+            mma_s8u8(l0, l1, al.x, al.y, w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu);
+            mma_s8u8(h0, h1, ah.x, ah.y, w.x & 0xf0f0f0f0u, w.y & 0xf0f0f0f0u);
+            const float El = E[2 * pp], Eh = E[2 * pp + 1];
+            const float Sl = small_int_to_float(Sg[2 * pp]), Sh = small_int_to_float(Sg[2 * pp + 1]);
+            const float2 Dl = *reinterpret_cast<const float2*>(fac + (0 * 4 + pp) * 8 + 2 * t), DMl = *reinterpret_cast<const float2*>(fac + (1 * 4 + pp) * 8 + 2 * t);
+            const float2 Dh = *reinterpret_cast<const float2*>(fac + (2 * 4 + pp) * 8 + 2 * t), DMh = *reinterpret_cast<const float2*>(fac + (3 * 4 + pp) * 8 + 2 * t);
+            acc[pp] = __fadd_rn(acc[pp], pair_from_dots(Dl.x, DMl.x, Dh.x, DMh.x, l0, h0, El, Eh, Sl, Sh));
+            acc[4 + pp] = __fadd_rn(acc[4 + pp], pair_from_dots(Dl.y, DMl.y, Dh.y, DMh.y, l1, h1, El, Eh, Sl, Sh));
+        }
+    }
+}
+
 template <bool DOWN>
 __global__ void __launch_bounds__(kThreads, 1)
 q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, WideArgs a, WidePlan plan) {
@@ -148,7 +217,9 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
     float* s_gu = reinterpret_cast<float*>(at);  // [group][buffer][gate | up][entry][32]
     if (!DOWN) at += kGroups * 2 * 2 * kKE * 32 * 4;
     VExpert* table = reinterpret_cast<VExpert*>(at);
-    at += u64(plan.vmax) * sizeof(VExpert);
+    at += (u64(plan.vmax) * sizeof(VExpert) + 15) & ~u64(15);  // what follows holds 8- and 16-byte objects
+    float* s_fac = reinterpret_cast<float*>(at);  // [consumer warp][kFacFloats]
+    at += kConsumerWarps * kFacFloats * 4;
     u64* full = reinterpret_cast<u64*>(at);
     u64* empty = full + kGroups * plan.stages;
     u64* gu_bar = empty + kGroups * plan.stages;
@@ -167,6 +238,7 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
     // ---- the virtual expert list (the stage area is free until the first copy is issued: it holds the copied routes)
     u32* t_beg = reinterpret_cast<u32*>(smem);
     u32* t_exp = t_beg + plan.max_union + 1;
+    u32* t_cum = t_exp + plan.max_union;  // exclusive cost prefix of every virtual expert: only the work split reads it
     for (u32 j = tid; j <= n_union; j += kThreads) {
         t_beg[j] = __ldg(a.routes.begins + j);
         if (j < n_union) t_exp[j] = __ldg(a.routes.experts + j);
@@ -182,7 +254,8 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
             u32 pos = n_virtual + iv - nv, cum = total + ic - cost;
             for (u32 k = 0; k < nv && pos < plan.vmax; ++k, ++pos) {
                 const u32 part = min(kKE, ne - k * kKE);
-                table[pos] = VExpert{t_exp[j], eb + k * kKE, part, cum};
+                table[pos] = VExpert::make(t_exp[j], eb + k * kKE, part);
+                t_cum[pos] = cum;
                 cum += virtual_cost(part);
             }
             n_virtual += __shfl_sync(0xffffffffu, iv, 31);
@@ -192,8 +265,8 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
         __syncwarp();
         if (lane == 0) {
             const u64 all = u64(total) * plan.n_chunks;
-            const u32 lo = item_at(table, n_virtual, plan.n_chunks, all, all * blockIdx.x / gridDim.x);
-            const u32 hi = item_at(table, n_virtual, plan.n_chunks, all, all * (blockIdx.x + 1) / gridDim.x);
+            const u32 lo = item_at(table, t_cum, n_virtual, plan.n_chunks, all, all * blockIdx.x / gridDim.x);
+            const u32 hi = item_at(table, t_cum, n_virtual, plan.n_chunks, all, all * (blockIdx.x + 1) / gridDim.x);
             ctl[2] = lo;
             ctl[3] = hi - lo;
         }
@@ -219,15 +292,16 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
             k = __shfl_sync(0xffffffffu, k, 0);
             const bool end = k >= n_local;
             const u32 item = first_item + k;
-            VExpert ve{0, 0, 0, 0};
+            VExpert ve{0};
             u32 chunk = 0;
             if (!end) {
                 const u32 jv = item / plan.n_chunks;
                 chunk = item - jv * plan.n_chunks;
                 ve = table[jv];
             }
+            const u32 ve_ne = ve.ne();
             u32 r = 0;
-            if (e < ve.ne) r = __ldg((DOWN ? a.routes.slots : a.routes.rows) + ve.begin + e);
+            if (e < ve_ne) r = __ldg((DOWN ? a.routes.slots : a.routes.rows) + ve.begin() + e);
             const u32 nsegs = end ? 1u : plan.nseg;
             for (u32 s = 0; s < nsegs; ++s, ++t) {
                 const u32 slot = t % plan.stages, use = t / plan.stages;
@@ -244,20 +318,20 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
                 unsigned char* dst = g_stage + u64(slot) * plan.stage_bytes;
                 if (lane == 0) {
                     g_item[slot] = item;
-                    mbar_expect_tx(&g_full[slot], plan.w_bytes + ve.ne * nbk * 320u);
+                    mbar_expect_tx(&g_full[slot], plan.w_bytes + ve_ne * nbk * 320u);
                 }
                 __syncwarp();
                 if (lane == 0) {
                     const u32 x = s * plan.S * (kQ4KBlock / 4);  // 32-bit elements: a multiple of 36, i.e. of 144 bytes
                     if (DOWN) {
-                        tma_2d(dst, &tm0, x, ve.expert * a.rows_per_expert + kItemRows * chunk, &g_full[slot]);
+                        tma_2d(dst, &tm0, x, ve.expert() * a.rows_per_expert + kItemRows * chunk, &g_full[slot]);
                     } else {
-                        const u32 y = ve.expert * a.rows_per_expert + 32u * chunk;
+                        const u32 y = ve.expert() * a.rows_per_expert + 32u * chunk;
                         tma_2d(dst, &tm0, x, y, &g_full[slot]);
                         tma_2d(dst + 32u * plan.row_seg_bytes, &tm1, x, y, &g_full[slot]);
                     }
                 }
-                if (e < ve.ne) {
+                if (e < ve_ne) {
                     unsigned char* xd = dst + plan.w_bytes + e * plan.x_entry_bytes;
                     if (part == 0) bulk_g2s(xd, a.in.codes + u64(r) * in_stride + u64(s) * plan.S * 256u, nbk * 256u, &g_full[slot]);
                     else if (part == 1) bulk_g2s(xd + 256u * plan.S, a.in.deltas + u64(r) * in_gs + u64(s) * plan.S * 8u, nbk * 32u, &g_full[slot]);
@@ -277,6 +351,7 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
     // ------------------------------------------------------------------------------------------ consumer warps
     const u32 g = warp / kGroupWarps, w = warp % kGroupWarps;
     const u32 p = lane >> 3, rr = lane & 7u;
+    float* fac = s_fac + warp * kFacFloats;
     u64* g_full = full + g * plan.stages;
     u64* g_empty = empty + g * plan.stages;
     const u32* g_item = slot_item + g * plan.stages;
@@ -293,7 +368,8 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
         if (item == kEndItem) break;
         const u32 jv = item / plan.n_chunks, chunk = item - jv * plan.n_chunks;
         const VExpert ve = table[jv];
-        const u32 n1 = min(ve.ne, 4u), n2 = ve.ne - n1;
+        const u32 ne = ve.ne(), vbegin = ve.begin();
+        const bool mma = ne >= kMmaMinEntries;
         float acc[kKE];
 #pragma unroll
         for (int r = 0; r < (int)kKE; ++r) acc[r] = 0.0f;
@@ -308,29 +384,44 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
             const uint4* blk = reinterpret_cast<const uint4*>(st + (8u * w + rr) * plan.row_seg_bytes);
             const unsigned char* xs = st + plan.w_bytes;
             const u32 nbk = min(plan.S, plan.nb - s * plan.S);
-            stage_rows_n(n1, blk, nbk, p, xs, plan.x_entry_bytes, plan.S, acc);
-            if (n2) stage_rows_n(n2, blk, nbk, p, xs + 4u * plan.x_entry_bytes, plan.x_entry_bytes, plan.S, acc + 4);
+            if (mma) stage_rows_mma(st + 8u * w * plan.row_seg_bytes, plan.row_seg_bytes, nbk, lane, xs, plan.x_entry_bytes, plan.S, fac, acc);
+            else stage_rows_n(ne, blk, nbk, p, xs, plan.x_entry_bytes, plan.S, acc);
             __syncwarp();
             if (lane == 0) mbar_arrive(&g_empty[slot]);  // the stage is free for the producer
         }
         if (!ok) break;
+        // mma form: lane (e = lane >> 2, t = lane & 3) holds the four chains of rows 2t and 2t + 1 of entry e
+        const float m0 = __fadd_rn(__fadd_rn(acc[0], acc[1]), __fadd_rn(acc[2], acc[3]));
+        const float m1 = __fadd_rn(__fadd_rn(acc[4], acc[5]), __fadd_rn(acc[6], acc[7]));
+        const u32 me = lane >> 2, mt = lane & 3u;
         if (DOWN) {
+            if (mma) {
+                if (me < ne) {
+                    float* dst = a.raw + u64(__ldg(a.routes.slots + vbegin + me)) * a.out_width + kItemRows * chunk + 8u * w + 2u * mt;
+                    *reinterpret_cast<float2*>(dst) = make_float2(m0, m1);
+                }
+            } else {
 #pragma unroll
-            for (int r = 0; r < (int)kKE; ++r) {
-                if (r < (int)ve.ne) {
-                    const float val = tree4(acc[r]);
-                    if (p == 0) a.raw[u64(__ldg(a.routes.slots + ve.begin + r)) * a.out_width + kItemRows * chunk + 8u * w + rr] = val;
+                for (int r = 0; r < (int)kMmaMinEntries - 1; ++r) {
+                    if (r < (int)ne) {
+                        const float val = tree4(acc[r]);
+                        if (p == 0) a.raw[u64(__ldg(a.routes.slots + vbegin + r)) * a.out_width + kItemRows * chunk + 8u * w + rr] = val;
+                    }
                 }
             }
         } else {
             // the item's 2 x 32 outputs of every entry meet in shared memory; then one warp per entry runs the epilogue
             float* gu = s_gu + u64((g * 2 + (kl & 1u)) * 2) * kKE * 32;
-            float* mine = gu + (w >> 2) * kKE * 32 + 8u * (w & 3u) + rr;
+            if (mma) {
+                if (me < ne) *reinterpret_cast<float2*>(gu + (w >> 2) * kKE * 32 + me * 32 + 8u * (w & 3u) + 2u * mt) = make_float2(m0, m1);
+            } else {
+                float* mine = gu + (w >> 2) * kKE * 32 + 8u * (w & 3u) + rr;
 #pragma unroll
-            for (int r = 0; r < (int)kKE; ++r) {
-                if (r < (int)ve.ne) {
-                    const float val = tree4(acc[r]);
-                    if (p == 0) mine[r * 32] = val;
+                for (int r = 0; r < (int)kMmaMinEntries - 1; ++r) {
+                    if (r < (int)ne) {
+                        const float val = tree4(acc[r]);
+                        if (p == 0) mine[r * 32] = val;
+                    }
                 }
             }
             __syncwarp();
@@ -338,15 +429,15 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
             ok = mbar_wait(&gu_bar[g], kl & 1u, plan.wait_limit, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (w < ve.ne) {  // SwiGLU + the A8 rule over the 32 outputs of entry w
+            if (w < ne) {  // SwiGLU + the A8 rule over the 32 outputs of entry w
                 const float gv = gu[w * 32 + lane], uv = gu[kKE * 32 + w * 32 + lane];
-                const u32 slot_id = __ldg(a.routes.slots + ve.begin + w), o_col = 32u * chunk + lane;
+                const u32 slot_id = __ldg(a.routes.slots + vbegin + w), o_col = 32u * chunk + lane;
                 if (a.gate_out) { a.gate_out[u64(slot_id) * a.out_width + o_col] = gv; a.up_out[u64(slot_id) * a.out_width + o_col] = uv; }
                 const float h = swiglu_qwen(gv, uv);
                 const bool bad = __any_sync(0xffffffffu, !finite_f(gv) || !finite_f(uv) || !finite_f(h));
                 if (bad) {  // fail closed: nothing of the group is written (routed_expert.cpp:147-156)
                     if (lane == 0) {
-                        if (a.row_status) atomicOr(&a.row_status[__ldg(a.routes.rows + ve.begin + w)], B200MOE_ROW_PROJECTION_NONFINITE);
+                        if (a.row_status) atomicOr(&a.row_status[__ldg(a.routes.rows + vbegin + w)], B200MOE_ROW_PROJECTION_NONFINITE);
                         if (a.summary) atomicOr(a.summary, B200MOE_ROW_PROJECTION_NONFINITE);
                     }
                 } else {
@@ -409,8 +500,8 @@ int rows_map(const u8* base, u64 row_bytes, u64 rows, u32 S, u32 box_rows, CUten
 u32 round_up(u32 v, u32 a) { return (v + a - 1) / a * a; }
 
 u32 fixed_smem(const WidePlan& p, bool down) {
-    return (down ? 0u : kGroups * 2 * 2 * kKE * 32 * 4) + p.vmax * static_cast<u32>(sizeof(VExpert)) + (2 * kGroups * p.stages + kGroups) * 8 +
-           kGroups * p.stages * 4 + 64;
+    return (down ? 0u : kGroups * 2 * 2 * kKE * 32 * 4) + round_up(p.vmax * static_cast<u32>(sizeof(VExpert)), 16) + kConsumerWarps * kFacFloats * 4 +
+           (2 * kGroups * p.stages + kGroups) * 8 + kGroups * p.stages * 4 + 64;
 }
 u32 plan_smem(const WidePlan& p, bool down) { return kGroups * p.stages * p.stage_bytes + fixed_smem(p, down); }
 
@@ -422,7 +513,10 @@ bool make_plan(u32 K, u32 n_chunks, u32 max_union, u64 slots, bool down, WidePla
     p->nseg = (p->nb + p->S - 1) / p->S;
     p->row_seg_bytes = p->S * kQ4KBlock;
     p->w_bytes = kItemRows * p->row_seg_bytes;
+    // codes, deltas, sums of one entry over a stage, padded so that entries lie 8 (mod 32) words apart: the mma form reads
+    // 8 bytes per lane at (entry, k slice) and four entries then cover all banks once
     p->x_entry_bytes = p->S * 320u;
+    while ((p->x_entry_bytes / 4) % 32 != 8 && (p->x_entry_bytes / 4) % 32 != 24) p->x_entry_bytes += 16;
     p->stage_bytes = round_up(p->w_bytes + kKE * p->x_entry_bytes, 128);
     p->n_chunks = n_chunks;
     p->max_union = max_union;
@@ -431,7 +525,7 @@ bool make_plan(u32 K, u32 n_chunks, u32 max_union, u64 slots, bool down, WidePla
     for (p->stages = 4; p->stages >= 2; --p->stages)
         if (plan_smem(*p, down) <= kSmemBudget) break;
     if (p->stages < 2) return false;
-    if ((2 * max_union + 2) * 4 > kGroups * p->stages * p->stage_bytes) return false;  // the copied routes borrow the stage area
+    if ((2 * max_union + 2 + p->vmax) * 4 > kGroups * p->stages * p->stage_bytes) return false;  // the copied routes and the cost prefix borrow the stage area
     p->wait_limit = kDefaultWaitLimit;
     p->stall_stage = 0xffffffffu;
     return true;

@@ -24,23 +24,24 @@ __device__ __forceinline__ void mbar_arrive(u64* bar) {
 __device__ __forceinline__ void mbar_expect_tx(u64* bar, u32 bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(u64* bar, u32 parity) {
+// One poll. The instruction may suspend the warp until the phase completes or `hint_ns` nanoseconds have passed: a waiting
+// warp then issues nothing, instead of spinning in the issue slots that the working warps of its scheduler need.
+__device__ __forceinline__ bool mbar_try_wait(u64* bar, u32 parity, u32 hint_ns = 0) {
     u32 ok;
     asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(saddr(bar)), "r"(parity)
+        : "r"(saddr(bar)), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
 // Bounded wait: false when `limit` polls ran out (the abort flag is then raised) or another role has raised it.
+constexpr u32 kWaitHintNs = 1000;
 __device__ __forceinline__ bool mbar_wait(u64* bar, u32 parity, u32 limit, volatile u32* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;  // the common case: the phase is already complete
     for (u32 i = 0; i < limit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u) {
-            if (*abort_flag) return false;
-            __nanosleep(32);
-        }
+        if (mbar_try_wait(bar, parity, kWaitHintNs)) return true;
+        if ((i & 7u) == 7u && *abort_flag) return false;
     }
     *abort_flag = 1;
     return false;
