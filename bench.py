@@ -324,7 +324,8 @@ def dense_arm(args, cfg, rank, world, dev):
                  np.ascontiguousarray(d3[:, start // 256:(start + size) // 256]).reshape(-1))
         kernels.append(tp.DeviceDenseKernels(shape, *(torch.from_numpy(a).to(dev) for a in share)))
         del gate, up, down, share
-    ffns = [tp.TpDenseFfn(k) for k in kernels] if world > 1 else None
+    # N > 1: share + exchange + rank-ordered fold behind ONE C call per step (b200moe_tp_dense: peer stores, flag waits)
+    ffns = [tp.PeerTpDense(k.shape, k.gate, k.up, k.down, B, payload_bf16=args.tp_payload == "bf16") for k in kernels] if world > 1 else None
     rng = np.random.default_rng(7)                            # the same rows on every rank (x is replicated under TP)
     NX = 4
     xs_host = [torch.from_numpy(synth.activations(rng, B, H)).pin_memory() for _ in range(NX)]
@@ -343,7 +344,9 @@ def dense_arm(args, cfg, rank, world, dev):
         step(s, xs[s % NX])
     barrier()
     graph, mode, G = None, "per-step launches", layers * NX // math.gcd(layers, NX)
-    if not args.no_graph and world == 1:
+    if world > 1:
+        G *= 2          # every layer's exchange alternates between two window halves: an even number of its steps per graph
+    if not args.no_graph:
         try:
             cap = torch.cuda.Stream()
             cap.wait_stream(torch.cuda.current_stream())
@@ -397,7 +400,8 @@ def dense_arm(args, cfg, rank, world, dev):
         "config": {"workload": f"{args.workload}: {cfg['desc']}, batch {B}",
                    "parallelism": f"tp x{world} (inter share {size} of {I} on rank 0)" if world > 1 else "1 gpu",
                    "l2": f"{layers} distinct layers rotated ({layers * rank_bytes / 2 ** 20:.0f} MB per rank per rotation, L2 is 126 MB)",
-                   "launch": mode + (" + NCCL all-gather of the partial sums + rank-ordered fold" if world > 1 else "")},
+                   "launch": mode + (f"; partial sums exchanged by the library's peer stores ({args.tp_payload} payload) with bounded flag waits, "
+                                     "folded in rank order on every rank (no collective)" if world > 1 else "")},
         "clocks": sampler.summary(),
         "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
                 "ms_per_step": host_ms / K},
@@ -588,7 +592,7 @@ def large_arm(args, cfg, rank, world, dev):
     ys = [torch.empty((R, H), dtype=torch.float32, device=dev) for _ in range(NX)]
     summary = torch.zeros(1, dtype=torch.int32, device=dev)
     if world > 1:
-        layer = ep.PeerEpFfn(shape, policy, rw, gate, up, down, R, select_bias=bias)
+        layer = ep.PeerEpFfn(shape, policy, rw, gate, up, down, R, select_bias=bias, fold_parts=C4_PARTS)
         routed = lambda x, shared, y, ev=None: b200moe.check(b200moe.lib().b200moe_ep_ffn(layer.handle, C.byref(layer.view(x, y, shared, summary, ev)), b200moe.stream_ptr()))
     else:
         ffn = ops.MoeFfn(shape, policy, gate, up, down, rw, capacity=B, combine_form=b200moe.COMBINE_PARTS, parts=C4_PARTS, select_bias=bias)
@@ -1055,6 +1059,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="config 4 arm: launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-peer-return", action="store_true",
                     help="expert parallelism, PARTS form: return the partial sums with an NCCL all-to-all instead of the combine kernel's peer stores")
+    ap.add_argument("--tp-payload", default="bf16", choices=["bf16", "fp32"], help="config 5, N > 1: what the partial sums cross NVLink as")
     ap.add_argument("--form", type=int, default=0, choices=[0, 1, 2, 3],
                     help="Q4_K decode GEMV form: 0 = by plan, 1 = row streaming, 2 = segment streaming, 3 = per block (measurement hook)")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],

@@ -314,6 +314,10 @@ typedef struct b200moe_combine_view {
     float* const* y_blocks;
     uint32_t y_block_rows;
     const uint32_t* summary;   /* optional job summary: with B200MOE_JOB_WAIT_ABORTED set nothing is written */
+    /* only_part >= 0 with only_part_count = n > 1: the n partial sums S_only_part .. S_only_part+n-1 are written, sum i at
+     * the destination of sum 0 plus i * part_stride floats (a rank that owns n consecutive expert ranges of the fold). */
+    uint32_t only_part_count;  /* 0 or 1: one sum */
+    uint64_t part_stride;
 } b200moe_combine_view;
 int b200moe_combine(const b200moe_combine_view* view, void* stream);
 
@@ -356,7 +360,8 @@ int b200moe_select_owner_slots(const float* blocks, uint64_t block_stride, uint3
  * include/strix/ds41_moe.hpp:5-11; restrict_routes / reference_half_sum, src/ds41_moe.cpp:45-61, :99-115): rank r owns
  * experts [r * E / W, (r + 1) * E / W) and passes only those tensors; a row's A8 record goes only to the ranks that own
  * one of its experts (the all-to-all-v of the dispatch; positions are fixed by the global row index, so no counts are
- * negotiated); y = (((shared + S_0) + S_1) + ...) + S_{W-1}: the bits of b200moe_ffn with combine PARTS and parts = W.
+ * negotiated); y = (((shared + S_0) + S_1) + ...) + S_{F-1} over F = fold_parts expert ranges (a rank returns the sums of
+ * its F / W ranges): the bits of b200moe_ffn with combine PARTS and parts = F.
  * Every rank calls b200moe_ep_ffn once per step with the same rows_per_rank; steps alternate between two halves of
  * the window, so a captured CUDA graph must hold an even number of steps. Set-up calls (create / destroy) allocate and
  * synchronise; b200moe_ep_ffn does neither. */
@@ -366,6 +371,8 @@ typedef struct b200moe_ep_desc {
     uint32_t world, rank;          /* 1 <= world <= 8 (one node), experts % world == 0 */
     uint32_t rows_per_rank;        /* home rows of every rank per step */
     uint32_t wait_polls;           /* bound of the flag waits, 0 = the default (about a second) */
+    uint32_t fold_parts;           /* expert ranges of the fold, a multiple of world dividing experts; 0 = world. With the same
+                                    * value at every world size (8, say) 1, 2, 4 and 8 GPUs give the same bits */
     void* const* windows;          /* HOST array [world]: device address, in this process, of every rank's window (own included),
                                     * each b200moe_ep_window_bytes() long and zero-filled before the first step */
 } b200moe_ep_desc;
@@ -386,7 +393,7 @@ typedef struct b200moe_ep_step_view {
     uint32_t grouped_min_rows;      /* as b200moe_layer_view, applied to the world * rows_per_rank window */
     void* const* stage_events;      /* optional timing taps of the local experts (see b200moe_layer_view) */
 } b200moe_ep_step_view;
-uint64_t b200moe_ep_window_bytes(const b200moe_shape* shape, uint32_t world, uint32_t rows_per_rank);
+uint64_t b200moe_ep_window_bytes(const b200moe_shape* shape, uint32_t world, uint32_t rows_per_rank, uint32_t fold_parts);
 int b200moe_ep_create(const b200moe_ep_desc* desc, void** ep);
 void b200moe_ep_destroy(void* ep);
 uint64_t b200moe_ep_workspace_bytes(const void* ep);
@@ -423,6 +430,8 @@ typedef struct b200moe_layer_view {
     uint32_t y_block_rows;
     uint32_t* summary;          /* optional [1]: receives the job summary (OR of the row status bits and B200MOE_JOB_WAIT_ABORTED);
                                  * cleared by the call. NULL: the word stays in the workspace */
+    uint32_t only_part_count;   /* see b200moe_combine_view */
+    uint64_t part_stride;
 } b200moe_layer_view;
 uint64_t b200moe_layer_workspace_bytes(const b200moe_shape* shape, uint32_t capacity);
 int b200moe_layer(const b200moe_layer_view* view, void* stream);
@@ -475,6 +484,40 @@ typedef struct b200moe_dense_view {
     uint64_t workspace_bytes;     /* b200moe_layer_workspace_bytes(shape, rows) */
 } b200moe_dense_view;
 int b200moe_dense_ffn(const b200moe_dense_view* view, void* stream);
+
+/* ------------------------------------------------------------------------------------------ tensor parallelism, one call
+ * The dense block under tensor parallelism behind one enqueue-only call: the rank's share of b200moe_dense_ffn (gate / up
+ * column shares and the matching down K share stored compacted: shape.inter = the share) and the exchange of the partial
+ * sums. Every rank stores its [rows][hidden] partial - FP32, or rounded to bfloat16 when payload_bf16 is set, the payload of
+ * the usual row-parallel all-reduce - into block `rank` of every rank's window (b200moe_peer_buffer_create / _open; plain
+ * peer stores over NVLink, no collective library, no host wait) followed by an arrival flag; then every rank folds the W
+ * blocks in rank order, y = (((+0 + P_0) + P_1) + ...) + P_{W-1} in FP32: an all-reduce with a fixed association order, the
+ * reference's rule for its two-rank shared expert (include/strix/ds41_shexp_tp.hpp:7-9; src/core/tp_join.hpp:16-78). The
+ * flag wait is bounded as in b200moe_ep_ffn (B200MOE_JOB_WAIT_ABORTED, y not written). x is replicated: every rank passes
+ * the same rows. Steps alternate between two halves of the window: a captured CUDA graph holds an even number of steps. */
+typedef struct b200moe_tp_desc {
+    b200moe_shape shape;          /* experts = top_k = 1; inter = THIS rank's share (whole 256-wide super-blocks) */
+    uint32_t world, rank;         /* 1 <= world <= 8 */
+    uint32_t rows;                /* most rows of a step */
+    uint32_t payload_bf16;        /* != 0: the partials cross NVLink as bfloat16 (RNE) and are widened before the FP32 fold */
+    uint32_t wait_polls;          /* 0 = the default (about a second) */
+    void* const* windows;         /* HOST array [world] of device addresses, each b200moe_tp_window_bytes() long, zero-filled */
+} b200moe_tp_desc;
+typedef struct b200moe_tp_step_view {
+    b200moe_expert_weights weights; /* the rank's share */
+    uint32_t rows;
+    b200moe_a8_rows x;              /* [rows][hidden], the same on every rank */
+    float* y;                       /* [rows][hidden]: the folded sum, on every rank */
+    uint16_t* y_bf16;               /* optional */
+    uint32_t* summary;              /* optional [1] */
+    void* workspace;
+    uint64_t workspace_bytes;       /* b200moe_tp_workspace_bytes(tp) */
+} b200moe_tp_step_view;
+uint64_t b200moe_tp_window_bytes(uint32_t hidden, uint32_t world, uint32_t rows, uint32_t payload_bf16);
+int b200moe_tp_create(const b200moe_tp_desc* desc, void** tp);
+void b200moe_tp_destroy(void* tp);
+uint64_t b200moe_tp_workspace_bytes(const void* tp);
+int b200moe_tp_dense(void* tp, const b200moe_tp_step_view* view, void* stream);
 
 /* ------------------------------------------------------------------------------------------------ GGUF container
  * Reader for the files the expert tensors come in, with the reference reader's admission rules (strix::gguf::read_file,

@@ -95,7 +95,8 @@ class DownView(C.Structure):
 class CombineView(C.Structure):
     _fields_ = [("raw", vp), ("shared", vp), ("weights", vp), ("ids", vp), ("order", vp), ("rows", u32), ("top_k", u32),
                 ("hidden", u32), ("form", u32), ("parts", u32), ("part_experts", u32), ("only_part", i32), ("y", vp),
-                ("y_bf16", vp), ("row_status", vp), ("y_blocks", vp), ("y_block_rows", u32), ("summary", vp)]
+                ("y_bf16", vp), ("row_status", vp), ("y_blocks", vp), ("y_block_rows", u32), ("summary", vp), ("only_part_count", u32),
+                ("part_stride", u64)]
 
 
 class LayerView(C.Structure):
@@ -103,7 +104,7 @@ class LayerView(C.Structure):
                 ("shared", vp), ("first", u32), ("end", u32), ("base", u32), ("combine_form", u32), ("parts", u32),
                 ("part_experts", u32), ("only_part", i32), ("raw", vp), ("y", vp), ("y_bf16", vp), ("row_status", vp),
                 ("workspace", vp), ("workspace_bytes", u64), ("capacity", u32), ("grouped_min_rows", u32), ("stage_events", vp),
-                ("y_blocks", vp), ("y_block_rows", u32), ("summary", vp)]
+                ("y_blocks", vp), ("y_block_rows", u32), ("summary", vp), ("only_part_count", u32), ("part_stride", u64)]
 
 
 class FfnView(C.Structure):
@@ -116,13 +117,22 @@ class FfnView(C.Structure):
 
 class EpDesc(C.Structure):
     _fields_ = [("shape", Shape), ("policy", RoutePolicy), ("world", u32), ("rank", u32), ("rows_per_rank", u32), ("wait_polls", u32),
-                ("windows", vp)]
+                ("fold_parts", u32), ("windows", vp)]
 
 
 class EpStepView(C.Structure):
     _fields_ = [("weights", ExpertWeights), ("router_weight", vp), ("logit_bias", vp), ("select_bias", vp), ("x", vp), ("x_is_bf16", u32),
                 ("rows", u32), ("shared", vp), ("y", vp), ("y_bf16", vp), ("summary", vp), ("workspace", vp), ("workspace_bytes", u64),
                 ("grouped_min_rows", u32), ("stage_events", vp)]
+
+
+class TpDesc(C.Structure):
+    _fields_ = [("shape", Shape), ("world", u32), ("rank", u32), ("rows", u32), ("payload_bf16", u32), ("wait_polls", u32), ("windows", vp)]
+
+
+class TpStepView(C.Structure):
+    _fields_ = [("weights", ExpertWeights), ("rows", u32), ("x", A8Rows), ("y", vp), ("y_bf16", vp), ("summary", vp), ("workspace", vp),
+                ("workspace_bytes", u64)]
 
 
 class DenseView(C.Structure):
@@ -156,6 +166,7 @@ EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", 
            "b200moe_down_row_bytes", "b200moe_expert_bytes", "b200moe_gate_up", "b200moe_down", "b200moe_combine",
            "b200moe_canonical_sum", "b200moe_fold_parts", "b200moe_select_owner_slots", "b200moe_peer_buffer_create",
            "b200moe_peer_buffer_open", "b200moe_peer_buffer_close", "b200moe_peer_buffer_destroy",
+           "b200moe_tp_window_bytes", "b200moe_tp_create", "b200moe_tp_destroy", "b200moe_tp_workspace_bytes", "b200moe_tp_dense",
            "b200moe_ep_window_bytes", "b200moe_ep_create", "b200moe_ep_destroy", "b200moe_ep_workspace_bytes", "b200moe_ep_ffn", "b200moe_layer_workspace_bytes", "b200moe_layer", "b200moe_ffn_workspace_bytes",
            "b200moe_ffn", "b200moe_ffn_host", "b200moe_dense_ffn", "b200moe_gguf_open", "b200moe_gguf_close",
            "b200moe_residency_create", "b200moe_residency_destroy", "b200moe_residency_map",
@@ -229,7 +240,7 @@ def lib():
             getattr(L, n).restype = C.c_int
             getattr(L, n).argtypes = [vp]
         L.b200moe_ep_window_bytes.restype = u64
-        L.b200moe_ep_window_bytes.argtypes = [C.POINTER(Shape), u32, u32]
+        L.b200moe_ep_window_bytes.argtypes = [C.POINTER(Shape), u32, u32, u32]
         L.b200moe_ep_create.restype = C.c_int
         L.b200moe_ep_create.argtypes = [C.POINTER(EpDesc), C.POINTER(vp)]
         L.b200moe_ep_destroy.restype = None
@@ -238,6 +249,16 @@ def lib():
         L.b200moe_ep_workspace_bytes.argtypes = [vp]
         L.b200moe_ep_ffn.restype = C.c_int
         L.b200moe_ep_ffn.argtypes = [vp, C.POINTER(EpStepView), vp]
+        L.b200moe_tp_window_bytes.restype = u64
+        L.b200moe_tp_window_bytes.argtypes = [u32, u32, u32, u32]
+        L.b200moe_tp_create.restype = C.c_int
+        L.b200moe_tp_create.argtypes = [C.POINTER(TpDesc), C.POINTER(vp)]
+        L.b200moe_tp_destroy.restype = None
+        L.b200moe_tp_destroy.argtypes = [vp]
+        L.b200moe_tp_workspace_bytes.restype = u64
+        L.b200moe_tp_workspace_bytes.argtypes = [vp]
+        L.b200moe_tp_dense.restype = C.c_int
+        L.b200moe_tp_dense.argtypes = [vp, C.POINTER(TpStepView), vp]
         L.b200moe_fold_parts.restype = C.c_int
         L.b200moe_fold_parts.argtypes = [vp, u32, u64, vp, u64, vp, vp, vp]
         L.b200moe_select_owner_slots.restype = C.c_int

@@ -37,10 +37,11 @@ class PeerEpFfn:
     fold - with both exchanges done by the library's own kernels storing into the peers' windows over NVLink (no
     collective, no host wait; bounded flag waits on the device). torch.distributed is used once, at set-up, to hand the
     windows' CUDA IPC handles round; world 1 (no process group) runs the same kernels against the rank's own window.
-    gate / up / down hold the rank's experts only; every rank passes the same number of rows per step."""
+    gate / up / down hold the rank's experts only; every rank passes the same number of rows per step. fold_parts: the
+    number of expert ranges of the fold (0 = world); the same value at every world size gives the same bits."""
 
     def __init__(self, shape, policy, router_weight, gate, up, down, rows, group=None, logit_bias=None, select_bias=None,
-                 wait_polls=0, grouped_min_rows=0, extra_windows=0):
+                 wait_polls=0, grouped_min_rows=0, extra_windows=0, fold_parts=0):
         L = lib()
         multi = dist.is_available() and dist.is_initialized()
         self.group = group
@@ -49,9 +50,9 @@ class PeerEpFfn:
         self.shape, self.policy, self.rows = shape, policy, rows
         self.router_weight, self.gate, self.up, self.down = router_weight, gate, up, down
         self.logit_bias, self.select_bias, self.grouped_min_rows = logit_bias, select_bias, grouped_min_rows
-        nbytes = int(L.b200moe_ep_window_bytes(C.byref(shape), self.world, rows))
+        nbytes = int(L.b200moe_ep_window_bytes(C.byref(shape), self.world, rows, fold_parts))
         if nbytes == 0:
-            raise ValueError("expert parallelism: 1 <= world <= 8 and rows >= 1")
+            raise ValueError("expert parallelism: 1 <= world <= 8, rows >= 1, fold_parts a multiple of world")
         self.mine, self.opened, self.silent = C.c_void_p(), [], []
         handle = C.create_string_buffer(64)
         check(L.b200moe_peer_buffer_create(nbytes, C.byref(self.mine), handle))
@@ -74,7 +75,7 @@ class PeerEpFfn:
                 check(L.b200moe_peer_buffer_create(nbytes, C.byref(q), h))
                 self.silent.append(q.value)
                 windows[r] = q.value
-        desc = EpDesc(shape, policy, self.world, self.rank, rows, wait_polls, C.cast(windows, C.c_void_p))
+        desc = EpDesc(shape, policy, self.world, self.rank, rows, wait_polls, fold_parts, C.cast(windows, C.c_void_p))
         self.handle = C.c_void_p()
         check(L.b200moe_ep_create(C.byref(desc), C.byref(self.handle)))
         self.ws_bytes = int(L.b200moe_ep_workspace_bytes(self.handle))

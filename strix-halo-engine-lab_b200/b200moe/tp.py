@@ -67,6 +67,87 @@ class DeviceDenseKernels:
         return y
 
 
+class PeerTpDense:
+    """b200moe_tp_dense: the rank's share of the dense block and the exchange of the partial sums behind ONE C call. The
+    partials go to every rank's window by the library's peer stores (FP32, or bfloat16 with payload_bf16), every rank folds
+    them in rank order: an all-reduce with a fixed association order and no collective library on the path.
+    torch.distributed is used once, at set-up, to hand the windows' CUDA IPC handles round; world 1 needs no process group."""
+
+    def __init__(self, shape_local, gate, up, down, rows, group=None, payload_bf16=False, wait_polls=0, extra_windows=0):
+        from . import TpDesc
+        L = lib()
+        multi = dist.is_available() and dist.is_initialized()
+        self.group, self.shape, self.rows = group, shape_local, rows
+        self.world = dist.get_world_size(group) if multi else 1 + extra_windows
+        self.rank = dist.get_rank(group) if multi else 0
+        self.gate, self.up, self.down = gate, up, down
+        nbytes = int(L.b200moe_tp_window_bytes(shape_local.hidden, self.world, rows, int(payload_bf16)))
+        self.mine, self.opened, self.silent = C.c_void_p(), [], []
+        handle = C.create_string_buffer(64)
+        check(L.b200moe_peer_buffer_create(nbytes, C.byref(self.mine), handle))
+        windows = (C.c_void_p * self.world)()
+        if multi:
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, handle.raw, group=group)
+            for r in range(self.world):
+                if r == self.rank:
+                    windows[r] = self.mine.value
+                else:
+                    q = C.c_void_p()
+                    check(L.b200moe_peer_buffer_open(everyone[r], C.byref(q)))
+                    self.opened.append(q.value)
+                    windows[r] = q.value
+        else:
+            windows[0] = self.mine.value
+            for r in range(1, self.world):
+                q, h = C.c_void_p(), C.create_string_buffer(64)
+                check(L.b200moe_peer_buffer_create(nbytes, C.byref(q), h))
+                self.silent.append(q.value)
+                windows[r] = q.value
+        desc = TpDesc(shape_local, self.world, self.rank, rows, int(payload_bf16), wait_polls, C.cast(windows, C.c_void_p))
+        self.handle = C.c_void_p()
+        check(L.b200moe_tp_create(C.byref(desc), C.byref(self.handle)))
+        self.ws_bytes = int(L.b200moe_tp_workspace_bytes(self.handle))
+        dev = gate.device
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
+        H = shape_local.hidden
+        self.codes = torch.empty((rows, H), dtype=torch.int8, device=dev)
+        self.deltas = torch.empty((rows, H // 32), dtype=torch.float32, device=dev)
+        self.sums = torch.empty((rows, H // 32), dtype=torch.int32, device=dev)
+        self.y = torch.empty((rows, H), dtype=torch.float32, device=dev)
+        if multi:
+            dist.barrier(group=group)
+
+    def __call__(self, x, summary=None, y=None):
+        """x [rows][hidden] float32 (the same on every rank) -> y, the folded sum (kept in a buffer of this object)."""
+        from . import A8Rows, ExpertWeights, QuantizeA8View, TpStepView
+        rows, width = x.shape
+        a8 = A8Rows(ptr(self.codes), ptr(self.deltas), ptr(self.sums), rows, width, width)
+        q = QuantizeA8View(ptr(x), rows, width, x.stride(0), int(x.dtype == torch.bfloat16), a8, None)
+        check(lib().b200moe_quantize_a8(C.byref(q), stream_ptr()))
+        y = self.y[:rows] if y is None else y
+        v = TpStepView(ExpertWeights(ptr(self.gate), ptr(self.up), ptr(self.down)), rows, a8, ptr(y), None, ptr(summary), ptr(self.ws), self.ws_bytes)
+        check(lib().b200moe_tp_dense(self.handle, C.byref(v), stream_ptr()))
+        return y
+
+    def close(self):
+        L = lib()
+        torch.cuda.synchronize()
+        multi = dist.is_available() and dist.is_initialized()
+        if multi:
+            dist.barrier(group=self.group)
+        if self.handle:
+            L.b200moe_tp_destroy(self.handle)
+            self.handle = None
+        for q in self.opened:
+            L.b200moe_peer_buffer_close(q)
+        if multi:
+            dist.barrier(group=self.group)
+        for q in self.silent + ([self.mine.value] if self.mine else []):
+            L.b200moe_peer_buffer_destroy(q)
+        self.opened, self.silent, self.mine = [], [], None
+
+
 class TpDenseFfn:
     def __init__(self, kernels, group=None, allreduce=False):
         self.k, self.group, self.allreduce = kernels, group, allreduce

@@ -221,17 +221,17 @@ bool use_grouped(const b200moe_shape& s, u32 rows, u32 grouped_min_rows, bool ha
     const u32 least = grouped_min_rows ? grouped_min_rows : kGroupedDefaultRows;
     return rows >= least && grouped_fits(s, have_sums);
 }
-// Decode forms of the Q4_K GEMVs: windows of up to kRowStreamRows rows whose whole A8 window fits beside the ring take
-// the row-streaming form, everything else the segment-streaming form (any row length), the per-block form being what is
-// left. B200MOE_DEBUG_DECODE_FORM forces one of them where it applies.
-constexpr u32 kRowStreamRows = 8;
+// Decode forms of the Q4_K GEMVs: windows of up to kRowStreamRows rows over rows of up to kRowStreamK weights (a ring of
+// whole rows then keeps all sixteen consumer warps fed) take the row-streaming form, everything else the segment-streaming
+// form (any row length), the per-block form being what is left. B200MOE_DEBUG_DECODE_FORM forces one of them where it applies.
+constexpr u32 kRowStreamRows = 8, kRowStreamK = 2048;
 enum class DecodeForm { row_stream, wide, block };
-DecodeForm pick_decode_form(bool row_stream_fits, bool wide_fits, u32 rows) {
+DecodeForm pick_decode_form(bool row_stream_fits, bool wide_fits, u32 rows, u32 K) {
     const u32 forced = debug_value(B200MOE_DEBUG_DECODE_FORM);
     if (forced == 1 && row_stream_fits) return DecodeForm::row_stream;
     if (forced == 2 && wide_fits) return DecodeForm::wide;
     if (forced == 3) return DecodeForm::block;
-    if (row_stream_fits && rows <= kRowStreamRows) return DecodeForm::row_stream;
+    if (row_stream_fits && rows <= kRowStreamRows && (K <= kRowStreamK || !wide_fits)) return DecodeForm::row_stream;
     if (wide_fits) return DecodeForm::wide;
     return row_stream_fits ? DecodeForm::row_stream : DecodeForm::block;
 }
@@ -239,7 +239,7 @@ int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st, u3
     if (!is_kquant(v.shape.gate_type)) return launch_gate_up_q8(v, st);
     if (v.shape.gate_type == B200MOE_TYPE_Q5_K) return launch_gate_up_q4k(v, st);  // the per-block form reads both K-quant layouts
     if (use_grouped(v.shape, rows, grouped_min_rows, v.x.sums != nullptr)) return launch_gate_up_q4k_grouped(v, st);
-    switch (pick_decode_form(stream_gate_up_fits(v, rows), wide_gate_up_fits(v, rows), rows)) {
+    switch (pick_decode_form(stream_gate_up_fits(v, rows), wide_gate_up_fits(v, rows), rows, v.shape.hidden)) {
         case DecodeForm::row_stream: return launch_gate_up_q4k_stream(v, rows, st);
         case DecodeForm::wide: return launch_gate_up_q4k_wide(v, rows, st);
         default: return launch_gate_up_q4k(v, st);
@@ -248,7 +248,7 @@ int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st, u3
 int enqueue_down(const b200moe_down_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
     if (v.shape.down_type == B200MOE_TYPE_Q4_K && use_grouped(v.shape, rows, grouped_min_rows, v.act.sums != nullptr)) return launch_down_q4k_grouped(v, st);
     if (v.shape.down_type == B200MOE_TYPE_Q4_K) {
-        switch (pick_decode_form(stream_down_fits(v, rows), wide_down_fits(v, rows), rows)) {
+        switch (pick_decode_form(stream_down_fits(v, rows), wide_down_fits(v, rows), rows, v.shape.inter)) {
             case DecodeForm::row_stream: return launch_down_q4k_stream(v, rows, st);
             case DecodeForm::wide: return launch_down_q4k_wide(v, rows, st);
             default: return launch_down_q4k(v, st);
@@ -385,6 +385,8 @@ int b200moe_combine(const b200moe_combine_view* v, void* stream) {
     if (v->form == B200MOE_COMBINE_PARTS) {
         B200_REQUIRE(v->ids && v->order, "combine(parts): ids / order are null");
         B200_REQUIRE(v->parts && v->part_experts && v->only_part < static_cast<int>(v->parts), "combine(parts): parts / part_experts / only_part are inconsistent");
+        B200_REQUIRE(v->only_part_count <= 1 || (v->only_part >= 0 && v->only_part + v->only_part_count <= v->parts && v->part_stride && !v->y_bf16),
+                     "combine(parts): only_part_count needs only_part >= 0, a part_stride and no y_bf16");
     }
     if (v->rows == 0) return B200MOE_OK;
     if (!device_ready()) return B200MOE_ERR_CUDA;
@@ -421,6 +423,9 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
     B200_REQUIRE(v->combine_form <= B200MOE_COMBINE_FMA_SLOTS, "layer: unknown combine form %u", v->combine_form);
     if (v->y && v->combine_form == B200MOE_COMBINE_PARTS)
         B200_REQUIRE(v->parts && v->part_experts && v->only_part < static_cast<int>(v->parts), "layer: parts / part_experts / only_part are inconsistent");
+    B200_REQUIRE(v->only_part_count <= 1 || (v->combine_form == B200MOE_COMBINE_PARTS && v->only_part >= 0 && v->only_part + v->only_part_count <= v->parts &&
+                                             v->part_stride && !v->y_bf16),
+                 "layer: only_part_count needs the PARTS form, only_part >= 0, a part_stride and no y_bf16");
     const LayerScratch L = carve_layer(v->workspace, s, v->capacity);
     if (!v->workspace || v->workspace_bytes < L.bytes)
         return fail(B200MOE_ERR_WORKSPACE, "layer: workspace of %llu bytes needed, %llu given", (unsigned long long)L.bytes, (unsigned long long)v->workspace_bytes);
@@ -472,6 +477,7 @@ static int layer_impl(const b200moe_layer_view* v, void* stream, bool routes_rea
     cv.raw = raw; cv.shared = v->shared; cv.weights = v->route_weights; cv.ids = v->ids; cv.order = L.routes.order;
     cv.rows = v->rows; cv.top_k = s.top_k; cv.hidden = s.hidden; cv.form = v->combine_form;
     cv.parts = v->parts; cv.part_experts = v->part_experts; cv.only_part = v->only_part;
+    cv.only_part_count = v->only_part_count; cv.part_stride = v->part_stride;
     cv.y = v->y; cv.y_bf16 = v->y_bf16; cv.y_blocks = v->y_blocks; cv.y_block_rows = v->y_block_rows;
     cv.row_status = is_kquant(s.gate_type) ? row_status : nullptr;
     cv.summary = summary;

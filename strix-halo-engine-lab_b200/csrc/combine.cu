@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(256) combine_kernel(b200moe_combine_view v) {
             out = v.shared ? __fadd_rn(acc, v.shared[u64(row) * v.hidden + o]) : acc;
         } else {
             float total = v.shared ? v.shared[u64(row) * v.hidden + o] : 0.0f, single = 0.0f;
+            const u32 first_part = v.only_part >= 0 ? static_cast<u32>(v.only_part) : 0u, n_parts = v.only_part_count > 1 ? v.only_part_count : 1u;
             u32 k = 0;
             for (u32 p = 0; p < v.parts; ++p) {  // the slots are sorted by expert id, so each part is one run
                 float sum = 0.0f;
@@ -54,6 +55,11 @@ __global__ void __launch_bounds__(256) combine_kernel(b200moe_combine_view v) {
                     ++k;
                 }
                 if (static_cast<int>(p) == v.only_part) single = sum;
+                else if (v.only_part >= 0 && p > first_part && p < first_part + n_parts) {  // the further sums of a rank that owns several ranges
+                    const u64 at = u64(p - first_part) * v.part_stride;
+                    if (v.y_blocks) { const u32 blk = row / v.y_block_rows; v.y_blocks[blk][at + u64(row - blk * v.y_block_rows) * v.hidden + o] = sum; }
+                    else v.y[at + u64(row) * v.hidden + o] = sum;
+                }
                 total = __fadd_rn(total, sum);
             }
             out = v.only_part >= 0 ? single : total;

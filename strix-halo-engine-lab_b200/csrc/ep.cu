@@ -43,7 +43,7 @@ struct EpLayout {
 constexpr u64 kFlagBytes = 256;                // dispatch flags at +0, return flags at +128 (kMaxWorld words each)
 
 u64 up256(u64 v) { return (v + 255) & ~u64(255); }
-EpLayout make_layout(const b200moe_shape& s, u32 world, u32 rows) {
+EpLayout make_layout(const b200moe_shape& s, u32 world, u32 rows, u32 fold) {
     const u64 n = u64(world) * rows;
     EpLayout L{};
     u64 at = 0;
@@ -52,7 +52,7 @@ EpLayout make_layout(const b200moe_shape& s, u32 world, u32 rows) {
     L.sums = at; at = up256(at + n * (s.hidden / 32) * 4);
     L.ids = at; at = up256(at + n * s.top_k * 4);
     L.wts = at; at = up256(at + n * s.top_k * 4);
-    L.parts = at; at = up256(at + n * s.hidden * 4);
+    L.parts = at; at = up256(at + u64(fold) * rows * s.hidden * 4);  // [fold][rows][hidden]: sum p of every home row
     L.half = at;
     L.total = kFlagBytes + 2 * L.half;
     return L;
@@ -62,6 +62,7 @@ struct Ep {
     b200moe_shape shape;
     b200moe_route_policy policy;
     u32 world, rank, rows, per;
+    u32 fold, ranges;   // expert ranges of the fold; ranges = fold / world of them belong to this rank
     unsigned char* win[kMaxWorld];
     EpLayout lay;
     float** yblocks[2];  // device arrays [world]: block `rank` of every home rank's parts, per parity
@@ -199,9 +200,11 @@ using namespace b200moe;
 
 extern "C" {
 
-uint64_t b200moe_ep_window_bytes(const b200moe_shape* shape, uint32_t world, uint32_t rows_per_rank) {
+uint64_t b200moe_ep_window_bytes(const b200moe_shape* shape, uint32_t world, uint32_t rows_per_rank, uint32_t fold_parts) {
     if (!shape || world == 0 || world > kMaxWorld || rows_per_rank == 0) return 0;
-    return make_layout(*shape, world, rows_per_rank).total;
+    const u32 fold = fold_parts ? fold_parts : world;
+    if (fold % world || fold > 64) return 0;
+    return make_layout(*shape, world, rows_per_rank, fold).total;
 }
 
 int b200moe_ep_create(const b200moe_ep_desc* desc, void** out) {
@@ -212,6 +215,8 @@ int b200moe_ep_create(const b200moe_ep_desc* desc, void** out) {
     B200_REQUIRE(desc->rows_per_rank >= 1 && u64(desc->rows_per_rank) * desc->world * s.top_k <= (1u << 20), "ep_create: rows_per_rank is 0 or the window is too large");
     B200_REQUIRE(s.hidden % 128 == 0, "ep_create: hidden %u must be a multiple of 128 (the A8 records move as 16-byte pieces)", s.hidden);
     B200_REQUIRE(desc->policy.experts == s.experts && desc->policy.top_k == s.top_k, "ep_create: the route policy and the shape disagree");
+    B200_REQUIRE(desc->fold_parts == 0 || (desc->fold_parts % desc->world == 0 && desc->fold_parts <= 64 && s.experts % desc->fold_parts == 0),
+                 "ep_create: fold_parts must be a multiple of world that divides experts (at most 64)");
     B200_REQUIRE(desc->windows, "ep_create: windows is null");
     for (u32 r = 0; r < desc->world; ++r) B200_REQUIRE(desc->windows[r] && aligned(desc->windows[r], 256), "ep_create: window %u is null or not 256-byte aligned", r);
     if (b200moe_layer_workspace_bytes(&s, desc->world * desc->rows_per_rank) == 0) return B200MOE_ERR_INVALID_ARGUMENT;  // the shape check's message stands
@@ -219,7 +224,9 @@ int b200moe_ep_create(const b200moe_ep_desc* desc, void** out) {
     Ep* ep = new Ep{};
     ep->shape = s; ep->policy = desc->policy; ep->world = desc->world; ep->rank = desc->rank; ep->rows = desc->rows_per_rank;
     ep->per = s.experts / desc->world;
-    ep->lay = make_layout(s, ep->world, ep->rows);
+    ep->fold = desc->fold_parts ? desc->fold_parts : desc->world;
+    ep->ranges = ep->fold / ep->world;
+    ep->lay = make_layout(s, ep->world, ep->rows, ep->fold);
     ep->wait_polls = desc->wait_polls ? desc->wait_polls : kDefaultWaitPolls;
     for (u32 r = 0; r < ep->world; ++r) ep->win[r] = static_cast<unsigned char*>(desc->windows[r]);
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ep->counters), 256);
@@ -227,7 +234,7 @@ int b200moe_ep_create(const b200moe_ep_desc* desc, void** out) {
     for (u32 p = 0; p < 2 && e == cudaSuccess; ++p) {
         float* host[kMaxWorld];
         for (u32 h = 0; h < ep->world; ++h)
-            host[h] = reinterpret_cast<float*>(ep->win[h] + kFlagBytes + p * ep->lay.half + ep->lay.parts) + u64(ep->rank) * ep->rows * s.hidden;
+            host[h] = reinterpret_cast<float*>(ep->win[h] + kFlagBytes + p * ep->lay.half + ep->lay.parts) + u64(ep->rank) * ep->ranges * ep->rows * s.hidden;
         e = cudaMalloc(reinterpret_cast<void**>(&ep->yblocks[p]), sizeof(float*) * kMaxWorld);
         if (e == cudaSuccess) e = cudaMemcpy(ep->yblocks[p], host, sizeof(float*) * ep->world, cudaMemcpyHostToDevice);
     }
@@ -311,7 +318,8 @@ int b200moe_ep_ffn(void* handle, const b200moe_ep_step_view* v, void* stream) {
     lv.ids = reinterpret_cast<const u32*>(half + ep->lay.ids);
     lv.route_weights = reinterpret_cast<const float*>(half + ep->lay.wts);
     lv.first = ep->rank * ep->per; lv.end = lv.first + ep->per; lv.base = lv.first;
-    lv.combine_form = B200MOE_COMBINE_PARTS; lv.parts = ep->world; lv.part_experts = ep->per; lv.only_part = static_cast<int>(ep->rank);
+    lv.combine_form = B200MOE_COMBINE_PARTS; lv.parts = ep->fold; lv.part_experts = s.experts / ep->fold; lv.only_part = static_cast<int>(ep->rank * ep->ranges);
+    lv.only_part_count = ep->ranges; lv.part_stride = u64(ep->rows) * s.hidden;
     lv.y_blocks = ep->yblocks[parity]; lv.y_block_rows = ep->rows;
     lv.workspace = W.layer; lv.workspace_bytes = W.layer_bytes; lv.capacity = lv.rows; lv.grouped_min_rows = v->grouped_min_rows;
     lv.summary = summary; lv.stage_events = v->stage_events;
@@ -324,7 +332,7 @@ int b200moe_ep_ffn(void* handle, const b200moe_ep_step_view* v, void* stream) {
     if (int rc = after_launch("ep_wait_return")) return rc;
     const u64 count = u64(v->rows) * s.hidden;
     const float* parts = reinterpret_cast<const float*>(half + ep->lay.parts);
-    ep_fold_kernel<<<static_cast<u32>((count + 255) / 256), 256, 0, st>>>(parts, ep->world, u64(ep->rows) * s.hidden, v->shared, count, v->y, v->y_bf16, summary);
+    ep_fold_kernel<<<static_cast<u32>((count + 255) / 256), 256, 0, st>>>(parts, ep->fold, u64(ep->rows) * s.hidden, v->shared, count, v->y, v->y_bf16, summary);
     return after_launch("ep_fold");
 }
 

@@ -110,7 +110,7 @@ class OracleDenseKernels:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["ep_parts", "ep_parts_peer", "ep_fma", "ep_c_abi", "tp", "tp_allreduce"])
+    ap.add_argument("--case", required=True, choices=["ep_parts", "ep_parts_peer", "ep_fma", "ep_c_abi", "tp", "tp_allreduce", "tp_c_abi", "tp_c_abi_bf16"])
     ap.add_argument("--backend", default="gloo")
     ap.add_argument("--out", required=True)
     a = ap.parse_args()
@@ -164,6 +164,18 @@ def main():
         gate, up, down, x = tp_inputs()
         start, size = tp.tp_shares(DI, world)[rank]
         gs, us, ds = tp_slices(gate, up, down, start, size)
+        if a.case.startswith("tp_c_abi"):   # share + exchange + rank-ordered fold behind b200moe_tp_dense (no collective on the path)
+            layer = tp.PeerTpDense(ops.make_shape(DH, size, 1, 1, 12, 12), put(gs), put(us), put(ds), DROWS, payload_bf16=a.case.endswith("bf16"))
+            summary = torch.zeros(1, dtype=torch.int32, device=dev)
+            for step in range(4):
+                y = layer(put(x * np.float32(1.0 + 0.5 * step)), summary=summary).clone()
+            torch.cuda.synchronize()
+            assert int(summary.item()) == 0, f"job summary {int(summary.item()):#x}"
+            layer.close()
+            np.save(os.path.join(a.out, f"rank{rank}.npy"), y.cpu().numpy())
+            dist.barrier()
+            dist.destroy_process_group()
+            return
         if gpu:
             k = tp.DeviceDenseKernels(ops.make_shape(DH, size, 1, 1, 12, 12), put(gs), put(us), put(ds))
         else:

@@ -776,19 +776,21 @@ def test_ep_entry_point_single_rank(gpu, oracle):
     gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
     rw = synth.router_weight(rng, E, H)
     sh, osh = shape_pair(H, I, E, K, 12, 12)
-    layer = ep.PeerEpFfn(sh, ops.softmax_policy(E, K), dv(rw, gpu), dv(gate, gpu), dv(up, gpu), dv(down, gpu), rows)
-    summary = torch.zeros(1, dtype=torch.int32, device=gpu)
-    try:
-        for step in range(5):
-            x = synth.bf16_round(synth.activations(rng, rows, H))
-            shared = rng.standard_normal((rows, H), dtype=np.float32)
-            want = oracle.ffn(osh, O.softmax_policy(E, K), gate, up, down, rw, x, O.COMBINE_PARTS, parts=1, part_experts=E, shared=shared)
-            gx = dv(x, gpu).to(torch.bfloat16) if step % 2 else dv(x, gpu)
-            y = layer(gx, dv(shared, gpu), summary=summary)
-            assert same(host(y), want["y"]), step
-            assert host(summary)[0] == 0
-    finally:
-        layer.close()
+    for fold in (0, 4):   # 0: one expert range per rank; 4: the rank returns the sums of four ranges, folded in order
+        layer = ep.PeerEpFfn(sh, ops.softmax_policy(E, K), dv(rw, gpu), dv(gate, gpu), dv(up, gpu), dv(down, gpu), rows, fold_parts=fold)
+        summary = torch.zeros(1, dtype=torch.int32, device=gpu)
+        try:
+            for step in range(5):
+                x = synth.bf16_round(synth.activations(rng, rows, H))
+                shared = rng.standard_normal((rows, H), dtype=np.float32)
+                want = oracle.ffn(osh, O.softmax_policy(E, K), gate, up, down, rw, x, O.COMBINE_PARTS, parts=max(fold, 1), part_experts=E // max(fold, 1),
+                                  shared=shared)
+                gx = dv(x, gpu).to(torch.bfloat16) if step % 2 else dv(x, gpu)
+                y = layer(gx, dv(shared, gpu), summary=summary)
+                assert same(host(y), want["y"]), (fold, step)
+                assert host(summary)[0] == 0
+        finally:
+            layer.close()
 
 
 def test_ep_wait_for_a_silent_peer_is_bounded(gpu, oracle):
@@ -814,6 +816,42 @@ def test_ep_wait_for_a_silent_peer_is_bounded(gpu, oracle):
     finally:
         layer.close()
     test_quantize_a8(gpu, oracle)   # the context is intact
+
+
+def test_tp_entry_point_single_rank(gpu, oracle):
+    """b200moe_tp_dense with one rank (the kernels of the N-GPU path: share, scatter into the rank's own window, flag
+    wait, fold): FP32 payload = the dense block's bits, bfloat16 payload = its bfloat16 rounding widened; four steps."""
+    from b200moe import ops, synth, tp
+    rng = np.random.default_rng(43)
+    H, I, rows = 512, 768, 3
+    gate, up, down = synth.expert_tensors(rng, 1, H, I, 12, 12)
+    sh, osh = shape_pair(H, I, 1, 1, 12, 12)
+    for bf16 in (False, True):
+        layer = tp.PeerTpDense(sh, dv(gate, gpu), dv(up, gpu), dv(down, gpu), rows, payload_bf16=bf16)
+        summary = torch.zeros(1, dtype=torch.int32, device=gpu)
+        try:
+            for step in range(4):
+                x = rng.standard_normal((rows, H), dtype=np.float32)
+                codes, deltas, sums = oracle.quantize_a8(x)
+                want = oracle.experts(osh, gate, up, down, np.zeros((rows, 1), np.uint32), codes, deltas, sums)["raw"]
+                if bf16:
+                    want = (synth.bf16_bits(want).astype(np.uint32) << 16).view(np.float32)
+                y = layer(dv(x, gpu), summary=summary)
+                assert same(host(y), want), (bf16, step)
+                assert host(summary)[0] == 0
+        finally:
+            layer.close()
+    # a silent second rank: the fold's bounded wait runs out, y is not written, the status says so
+    layer = tp.PeerTpDense(sh, dv(gate, gpu), dv(up, gpu), dv(down, gpu), rows, wait_polls=2000, extra_windows=1)
+    try:
+        summary = torch.zeros(1, dtype=torch.int32, device=gpu)
+        y = torch.full((rows, H), 3.0, device=gpu)
+        layer(dv(rng.standard_normal((rows, H), dtype=np.float32), gpu), summary=summary, y=y)
+        torch.cuda.synchronize()
+        import b200moe
+        assert u32(summary)[0] & b200moe.JOB_WAIT_ABORTED and (host(y) == 3.0).all()
+    finally:
+        layer.close()
 
 
 def test_dense_ffn_tensor_parallel_split(gpu, oracle):

@@ -65,14 +65,18 @@ def ep_expected(oracle, form, world, x_scale=1.0):
                       shared=shared)["y"]
 
 
-def tp_expected(oracle, world):
+def tp_expected(oracle, world, x_scale=1.0, bf16=False):
+    from b200moe import synth
     gate, up, down, x = W.tp_inputs()
-    codes, deltas, sums = oracle.quantize_a8(x)
+    codes, deltas, sums = oracle.quantize_a8(x * np.float32(x_scale))
     ids = np.zeros((W.DROWS, 1), np.uint32)
     acc = np.zeros((W.DROWS, W.DH), np.float32)
     for start, size in __import__("b200moe").tp.tp_shares(W.DI, world):
         gs, us, ds = W.tp_slices(gate, up, down, start, size)
-        acc = (acc + oracle.experts(O.Shape(W.DH, size, 1, 1, 12, 12, float("inf")), gs, us, ds, ids, codes, deltas, sums)["raw"]).astype(np.float32)
+        part = oracle.experts(O.Shape(W.DH, size, 1, 1, 12, 12, float("inf")), gs, us, ds, ids, codes, deltas, sums)["raw"]
+        if bf16:   # the payload crosses the link as bfloat16 (RNE) and is widened before the FP32 fold
+            part = (synth.bf16_bits(part).astype(np.uint32) << 16).view(np.float32)
+        acc = (acc + part).astype(np.float32)
     return acc
 
 
@@ -130,6 +134,20 @@ def test_expert_parallel_two_gpus_c_abi(oracle):
     want = ep_expected(oracle, 0, world, x_scale=2.0)   # step 4 of the worker: x * (1 + 0.25 * 4)
     assert max_rel(got, want) <= REL_TOL
     assert np.array_equal(bits(got), bits(want))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case,bf16", [("tp_c_abi", False), ("tp_c_abi_bf16", True)])
+def test_tensor_parallel_two_gpus_c_abi(oracle, case, bf16):
+    """b200moe_tp_dense on two GPUs: the partials cross NVLink by the library's peer stores (FP32 or bfloat16), both ranks
+    fold them in rank order; the fourth step against the oracle's rank-ordered sum of the shares' partials, bit for bit."""
+    if not _two_gpus():
+        pytest.skip("needs 2 CUDA devices")
+    ys = run_ranks(case, "nccl", 2)
+    want = tp_expected(oracle, 2, x_scale=2.5, bf16=bf16)
+    assert np.array_equal(bits(ys[0]), bits(ys[1]))
+    assert max_rel(ys[0], want) <= REL_TOL
+    assert np.array_equal(bits(ys[0]), bits(want))
 
 
 @pytest.mark.gpu
