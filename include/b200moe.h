@@ -318,6 +318,9 @@ typedef struct b200moe_combine_view {
      * the destination of sum 0 plus i * part_stride floats (a rank that owns n consecutive expert ranges of the fold). */
     uint32_t only_part_count;  /* 0 or 1: one sum */
     uint64_t part_stride;
+    /* PARTS with parts = 2, as strix::ds41::cuda::MoeCombineView gives it (include/strix/cuda/ds41_moe.hpp:113-131): the
+     * first low_counts[row] slots of the row's order are the low part, the others the high part. When set, ids is not read. */
+    const uint32_t* low_counts;
 } b200moe_combine_view;
 int b200moe_combine(const b200moe_combine_view* view, void* stream);
 

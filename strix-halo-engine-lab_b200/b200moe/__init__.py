@@ -96,7 +96,7 @@ class CombineView(C.Structure):
     _fields_ = [("raw", vp), ("shared", vp), ("weights", vp), ("ids", vp), ("order", vp), ("rows", u32), ("top_k", u32),
                 ("hidden", u32), ("form", u32), ("parts", u32), ("part_experts", u32), ("only_part", i32), ("y", vp),
                 ("y_bf16", vp), ("row_status", vp), ("y_blocks", vp), ("y_block_rows", u32), ("summary", vp), ("only_part_count", u32),
-                ("part_stride", u64)]
+                ("part_stride", u64), ("low_counts", vp)]
 
 
 class LayerView(C.Structure):

@@ -50,6 +50,12 @@ bool device_ready() {
     return ok;
 }
 
+int device_sm_count() {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+}
+
 int ensure_dynamic_smem(const void* kernel, u32 bytes) {
     if (bytes <= 48u * 1024u) return B200MOE_OK;
     static std::mutex m;
@@ -341,7 +347,9 @@ int b200moe_router(const b200moe_router_view* v, void* stream) {
 
 uint64_t b200moe_routes_scratch_words(uint32_t rows, uint32_t top_k, uint32_t experts) { return routes_scratch_words(rows, top_k, experts); }
 
-int b200moe_build_routes(const b200moe_routes_view* v, void* stream) {
+}  // extern "C"
+namespace b200moe {
+int b200moe_check_routes_view(const b200moe_routes_view* v) {
     B200_REQUIRE(v, "null view");
     B200_REQUIRE(v->rows && v->top_k && v->ids, "routes need rows * top_k expert ids");
     B200_REQUIRE(v->experts && v->experts <= kMaxExperts && v->top_k <= kMaxTopK && v->top_k <= v->experts, "routes: need top_k <= 32, top_k <= experts <= 1024");
@@ -349,6 +357,13 @@ int b200moe_build_routes(const b200moe_routes_view* v, void* stream) {
     if (int rc = check_routes(v->out)) return rc;
     B200_REQUIRE(v->out.order && v->out.low_counts, "routes: order / low_counts are null");
     B200_REQUIRE(u64(v->rows) * v->top_k <= 1024 || v->scratch, "routes: more than 1024 slots need scratch");
+    return B200MOE_OK;
+}
+}  // namespace b200moe
+extern "C" {
+
+int b200moe_build_routes(const b200moe_routes_view* v, void* stream) {
+    if (int rc = b200moe_check_routes_view(v)) return rc;
     if (!device_ready()) return B200MOE_ERR_CUDA;
     return launch_routes(*v, as_stream(stream));
 }
@@ -383,8 +398,9 @@ int b200moe_combine(const b200moe_combine_view* v, void* stream) {
     B200_REQUIRE(v->top_k && v->top_k <= kMaxTopK && v->hidden, "combine: need 0 < top_k <= 32 and hidden > 0");
     B200_REQUIRE(v->form <= B200MOE_COMBINE_FMA_SLOTS, "combine: unknown form %u", v->form);
     if (v->form == B200MOE_COMBINE_PARTS) {
-        B200_REQUIRE(v->ids && v->order, "combine(parts): ids / order are null");
-        B200_REQUIRE(v->parts && v->part_experts && v->only_part < static_cast<int>(v->parts), "combine(parts): parts / part_experts / only_part are inconsistent");
+        B200_REQUIRE((v->ids || v->low_counts) && v->order, "combine(parts): ids (or low_counts) / order are null");
+        B200_REQUIRE(!v->low_counts || v->parts == 2, "combine(parts): low_counts describes a two-part split (parts must be 2)");
+        B200_REQUIRE(v->parts && (v->part_experts || v->low_counts) && v->only_part < static_cast<int>(v->parts), "combine(parts): parts / part_experts / only_part are inconsistent");
         B200_REQUIRE(v->only_part_count <= 1 || (v->only_part >= 0 && v->only_part + v->only_part_count <= v->parts && v->part_stride && !v->y_bf16),
                      "combine(parts): only_part_count needs only_part >= 0, a part_stride and no y_bf16");
     }

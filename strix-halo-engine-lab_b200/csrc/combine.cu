@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(256) combine_kernel(b200moe_combine_view v) {
                 const u32 slot = v.order[row * v.top_k + k];
                 s_slot[k] = slot;
                 s_w[k] = v.weights[slot];
-                s_part[k] = min(v.ids[slot] / v.part_experts, v.parts - 1);
+                s_part[k] = v.low_counts ? (k < v.low_counts[row] ? 0u : 1u) : min(v.ids[slot] / v.part_experts, v.parts - 1);
             } else {
                 s_slot[k] = row * v.top_k + k;
                 s_w[k] = v.weights[row * v.top_k + k];

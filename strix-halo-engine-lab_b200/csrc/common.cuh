@@ -37,6 +37,8 @@ bool device_ready();
 int ensure_dynamic_smem(const void* kernel, u32 bytes);
 // Asks for the largest shared-memory carve-out for a kernel that itself needs little (see api.cu).
 int prefer_max_shared(const void* kernel);
+// Multiprocessors of the current device (148 on a B200; queried, not assumed).
+int device_sm_count();
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 inline bool aligned(const void* p, std::size_t a) { return (reinterpret_cast<std::uintptr_t>(p) % a) == 0; }

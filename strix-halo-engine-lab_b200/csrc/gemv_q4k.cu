@@ -388,7 +388,7 @@ int launch_down_q4k(const b200moe_down_view& v, cudaStream_t stream) {
     if (v.max_union == 0) return B200MOE_OK;
     const u32 smem = kR * (I + I / 32 * 8);
     u32 rpc = 64;  // rows per CTA: halved while the grid would not give every SM two CTAs (H is a multiple of 256)
-    while (rpc > 8 && u64(H / rpc) * v.max_union < 2u * 148u) rpc /= 2;
+    while (rpc > 8 && u64(H / rpc) * v.max_union < 2u * static_cast<u32>(device_sm_count())) rpc /= 2;  // at least two CTAs per SM
     const dim3 grid(H / rpc, v.max_union);
 #define B200_DN(L)                                                     \
     {                                                                  \

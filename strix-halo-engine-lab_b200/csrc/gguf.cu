@@ -129,7 +129,7 @@ struct Parser {
         if (!sb) return fail_("unknown metadata value type");
         unsigned char b[8] = {};
         if (!bytes(b, sb)) return false;
-        if (t == 0 || t == 2 || t == 4 || t == 10 || t == 1 || t == 3 || t == 5 || t == 11) {
+        if (t == 0 || t == 2 || t == 4 || t == 10) {  // the unsigned integer types (uint8 / 16 / 32 / 64)
             u64 x = 0;
             for (u64 i = 0; i < sb; ++i) x |= u64(b[i]) << (8 * i);
             *is_int = true;
@@ -138,6 +138,19 @@ struct Parser {
         return true;
     }
 };
+
+// Metadata keys (src/gguf_reader.cpp:131-135, :297-313): at most 65,535 bytes of [a-z0-9_.], no leading, trailing or
+// doubled dot.
+bool valid_key(const std::string& key) {
+    if (key.empty() || key.size() > 65535 || key.front() == '.' || key.back() == '.') return false;
+    bool previous_dot = false;
+    for (const char c : key) {
+        const bool ok = (c >= 'a' && c <= 'z') || (c >= '0' && c <= '9') || c == '_' || c == '.';
+        if (!ok || (c == '.' && previous_dot)) return false;
+        previous_dot = c == '.';
+    }
+    return true;
+}
 
 bool mul_ok(u64 a, u64 b, u64* out) {
     if (a != 0 && b > std::numeric_limits<u64>::max() / a) return false;
@@ -170,11 +183,14 @@ int parse(const char* path, File* out) {
         std::string key;
         u32 t;
         if (!p.str(&key) || !p.num(&t)) return bad("truncated metadata");
+        if (!valid_key(key)) return bad("invalid GGUF metadata key");
         if (!keys.insert(key).second) return bad("duplicate GGUF metadata key");
         bool is_int; u64 v = 0;
         if (!p.value(t, 0, &total_elements, &is_int, &v)) return bad("bad metadata value");
         if (key == "general.alignment") {
-            if (!is_int || v == 0 || (v & (v - 1)) != 0) return bad("general.alignment must be a power of two");
+            // src/gguf_reader.cpp:271-282: an unsigned integer, a non-zero multiple of 8
+            if (!is_int) return bad("general.alignment must be an unsigned integer");
+            if (v == 0 || v % 8 != 0) return bad("general.alignment must be a non-zero multiple of 8");
             out->alignment = v;
         }
     }
@@ -277,8 +293,10 @@ int b200moe_gguf_find_moe_layer(const void* file, uint32_t layer, b200moe_gguf_m
     B200_REQUIRE(d.dims[0] == g.dims[1] && d.dims[1] == g.dims[0] && d.dims[2] == g.dims[2],
                  "gguf layer %u: down is not [inter, hidden, experts] of gate's [hidden, inter, experts]", layer);
     B200_REQUIRE(r.ggml_type == 0 && r.dims[0] == g.dims[0] && r.dims[1] == g.dims[2], "gguf layer %u: the router must be F32 [hidden, experts]", layer);
-    B200_REQUIRE((g.ggml_type == B200MOE_TYPE_Q8_0 || g.ggml_type == B200MOE_TYPE_Q4_K) && (d.ggml_type == B200MOE_TYPE_Q8_0 || d.ggml_type == B200MOE_TYPE_Q4_K),
-                 "gguf layer %u: expert tensors must be Q8_0 or Q4_K (types %u / %u)", layer, g.ggml_type, d.ggml_type);
+    B200_REQUIRE((g.ggml_type == B200MOE_TYPE_Q8_0 || g.ggml_type == B200MOE_TYPE_Q4_K || g.ggml_type == B200MOE_TYPE_Q5_K) &&
+                     (d.ggml_type == B200MOE_TYPE_Q8_0 || d.ggml_type == B200MOE_TYPE_Q4_K || d.ggml_type == B200MOE_TYPE_Q5_1),
+                 "gguf layer %u: gate / up must be Q8_0, Q4_K or Q5_K and down Q8_0, Q4_K or Q5_1 (types %u / %u)", layer, g.ggml_type, d.ggml_type);
+    B200_REQUIRE(g.dims[0] <= 0xffffffffull && g.dims[1] <= 0xffffffffull && g.dims[2] <= 0xffffffffull, "gguf layer %u: a dimension exceeds 32 bits", layer);
     out->shape.hidden = static_cast<u32>(g.dims[0]);
     out->shape.inter = static_cast<u32>(g.dims[1]);
     out->shape.experts = static_cast<u32>(g.dims[2]);

@@ -2,7 +2,7 @@
 // tensor cores (tcgen05.mma kind::i8, accumulators in tensor memory), everything after the dots is the same declared
 // FP32 arithmetic as the decode kernels, so the results are bit for bit those of gemv_q4k.cu / gemv_q4k_stream.cu
 // (contract: src/cpu/core/routed_expert.hpp:9-15, row rule routed_expert.cpp:73-108; the reference's own tensor-core
-// form is project_kernel / down_kernel over IMMA tiles, src/cuda/moe_a8.cuh:76-206, :225-341).
+// form is project_kernel / down_kernel over IMMA tiles, src/cuda/core/moe_a8.cuh:76-206, :225-341).
 //
 // Why one MMA per 32-wide group: the contract scales every group's EXACT integer dot by its own FP32 factors and adds
 // the terms in a fixed order, so the tensor core may only produce dot_g, never a sum over groups. kind::i8 has K = 32:

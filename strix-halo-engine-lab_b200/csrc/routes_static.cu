@@ -41,6 +41,8 @@ int static_scratch(u32** out) {
 }  // namespace
 }  // namespace b200moe
 
+namespace b200moe { int b200moe_check_routes_view(const b200moe_routes_view* v); }  // api.cu: the argument checks of b200moe_build_routes
+
 extern "C" {
 
 uint64_t b200moe_routes_static_max_words(void) { return b200moe::kStaticRoutesWords; }
@@ -58,6 +60,10 @@ int b200moe_build_routes_static(const b200moe_routes_view* v, void* stream) {
     b200moe_routes_view w = *v;
     w.scratch = nullptr;
     if (u64(v->rows) * v->top_k > 1024) {  // the one-block form of small windows uses no scratch at all
+        // argument errors come before the device is touched: the shared validation runs first, on a placeholder scratch
+        static u32 placeholder;
+        w.scratch = &placeholder;
+        if (int rc = b200moe_check_routes_view(&w)) return rc;
         if (!device_ready()) return B200MOE_ERR_CUDA;
         if (int rc = static_scratch(&w.scratch)) return rc;
     }

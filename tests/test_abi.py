@@ -110,3 +110,27 @@ def test_graft_entry_build_runs():
     """build() compiles (incrementally) the library and the oracle and checks exports and ABI version: what the build check runs."""
     import __graft_entry__ as entry
     entry.build()
+
+
+REFERENCE_INCLUDE = os.environ.get("STRIX_REFERENCE_INCLUDE", "/root/reference/include")
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE_INCLUDE, "strix", "cuda", "ds41_moe.hpp")),
+                    reason="the reference checkout is absent: the adapters are compiled against its headers")
+@pytest.mark.parametrize("source,compiler", [("strix_ds41_b200.cpp", "g++"), ("strix_qwen_b200.cpp", "nvcc")])
+def test_adapters_compile_against_the_reference_headers(tmp_path, source, compiler):
+    """adapter/*.cpp re-expose the C ABI under the reference's operator names; compiling them against the reference's
+    own headers is what shows that every view maps field for field (types included). The DS41 operator header is plain
+    C++ (g++ -fsyntax-only); the Qwen header pulls in a .cuh with device intrinsics and needs nvcc."""
+    import shutil
+    path = os.path.join(ROOT, "adapter", source)
+    inc = ["-I" + REFERENCE_INCLUDE, "-I" + os.path.join(ROOT, "include")]
+    if compiler == "g++":
+        cmd = ["g++", "-std=c++20", "-fsyntax-only", "-Wall", "-I/usr/local/cuda/include"] + inc + [path]
+    else:
+        nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+        if not os.path.exists(nvcc):
+            pytest.skip("nvcc not found")
+        cmd = [nvcc, "-x", "cu", "-std=c++20", "-arch=sm_100a"] + inc + ["-c", path, "-o", str(tmp_path / "adapter.o")]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]

@@ -54,7 +54,7 @@ def test_reads_layers_and_offsets(tmp_path):
 
 
 @pytest.mark.parametrize("kind", ["magic", "version", "truncated_header", "truncated_data", "unaligned", "overlap", "duplicate_name",
-                                  "duplicate_key", "padding", "block", "alignment", "rank"])
+                                  "duplicate_key", "padding", "block", "alignment", "alignment_signed", "bad_key", "rank"])
 def test_rejects_malformed_files(tmp_path, kind):
     rng = np.random.default_rng(61)
     ts, _ = moe_tensors(rng, 0, 2, 256, 256, 12, 12)
@@ -81,13 +81,29 @@ def test_rejects_malformed_files(tmp_path, kind):
         kw["pad_byte"] = 1
     elif kind == "block":
         ts[0] = (ts[0][0], [250, 256, 2], 12, ts[0][3])
-    elif kind == "alignment":
-        meta[1] = ("general.alignment", "u32", 48)
+    elif kind == "alignment":       # a non-zero multiple of 8 is required (the reference reader's rule): 12 is not
+        meta[1] = ("general.alignment", "u32", 12)
+    elif kind == "alignment_signed":  # ... and an unsigned integer type
+        meta[1] = ("general.alignment", "i32", 64)
+    elif kind == "bad_key":
+        meta.append(("Synthetic.Upper", "u32", 1))
     elif kind == "rank":
         ts[3] = (ts[3][0], [256, 2, 1, 1, 1], 0, ts[3][3])
     W.write(path, meta, ts, alignment=64, **kw)
     with pytest.raises(b200moe.B200MoeError):
         gguf.GgufFile(path)
+
+
+def test_alignment_rule_is_the_reference_readers(tmp_path):
+    """general.alignment: any non-zero multiple of 8 is admitted - 24 is, although it is no power of two."""
+    rng = np.random.default_rng(63)
+    ts, _ = moe_tensors(rng, 0, 2, 256, 256, 12, 12)
+    meta = list(META)
+    meta[1] = ("general.alignment", "u32", 24)
+    path = tmp_path / "a24.gguf"
+    base, _ = W.write(path, meta, ts, alignment=24)
+    with gguf.GgufFile(path) as f:
+        assert f.alignment == 24 and f.data_offset == base
 
 
 def test_missing_file():

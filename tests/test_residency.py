@@ -42,11 +42,12 @@ def test_choose_victims_rejects_bad_table():
 
 
 @pytest.mark.gpu
-def test_residency_equals_all_resident(gpu):
-    """16 experts, 6 slots: every window's output equals the all-resident layer's bit for bit (FMA_SLOTS form), across
-    misses, hits and evictions; an oversubscribed window is refused with the state unchanged; an id out of range stays
-    invalid."""
+def test_residency_equals_all_resident(gpu, oracle):
+    """16 experts, 6 slots: every window's output equals the CPU oracle's (experts + slot-order merge on the full tensors)
+    and the all-resident layer's, bit for bit (FMA_SLOTS form), across misses, hits and evictions; an oversubscribed window
+    is refused with the state unchanged; an id out of range stays invalid."""
     import torch
+    from oracle import loader as O
     from b200moe import ops, synth
     rng = np.random.default_rng(61)
     E, S, H, I, K, rows = 16, 6, 512, 256, 2, 2
@@ -70,6 +71,11 @@ def test_residency_equals_all_resident(gpu):
             y_full = full(xa, ids_d, w_d)
             y_part = part(xa, slot_ids, w_d)
             assert np.array_equal(y_full.cpu().numpy().view(np.uint32), y_part.cpu().numpy().view(np.uint32)), (gt, dt, step)
+            codes, deltas, sums = oracle.quantize_a8(x)
+            osh = O.Shape(H, I, E, K, gt, dt, float("inf"))
+            raw = oracle.experts(osh, gate, up, down, ids.astype(np.uint32), codes, deltas, sums)["raw"]
+            want = oracle.combine(O.COMBINE_FMA_SLOTS, raw, w, ids.astype(np.uint32))
+            assert np.array_equal(y_part.cpu().numpy().view(np.uint32), want.view(np.uint32)), (gt, dt, step)
         st = res.stats()
         assert st["windows"] == 14 and st["misses"] > S and st["evictions"] > 0 and st["hits"] > 0
         assert (res.table() >= 0).sum() == S

@@ -51,6 +51,18 @@ def test_static_routes_match_on_two_calls_in_a_row():
     got = ops.enqueue_moe_routes_static(ids, 128, 64, out=got)
     torch.cuda.synchronize()
     _same(want, got, 3000, 8)
+    # the point of the entry: calls made after the per-device set-up take no device memory - neither from the driver
+    # (cudaMemGetInfo) nor from torch's allocator - with every output preallocated by the caller
+    L = b200moe.lib()
+    v = b200moe.RoutesView(b200moe.ptr(ids), 3000, 8, 128, 64, 0, 0, 0, None, None, got.struct())
+    torch.cuda.synchronize()
+    free0, stats0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    reserved0 = torch.cuda.memory_reserved()
+    for _ in range(20):
+        assert L.b200moe_build_routes_static(C.byref(v), b200moe.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == stats0 and torch.cuda.memory_reserved() == reserved0
+    _same(want, got, 3000, 8)
 
 
 def test_static_routes_refuse_windows_beyond_the_array():
