@@ -66,7 +66,7 @@ struct Ep {
     unsigned char* win[kMaxWorld];
     EpLayout lay;
     float** yblocks[2];  // device arrays [world]: block `rank` of every home rank's parts, per parity
-    u32* counters;       // device: [0] step, [1] dispatch ticket, [2] abort seen by the dispatch wait
+    u32* counters;       // device: [0] completed steps, [1] dispatch ticket, [2] the dispatch wait gave up, [3] fold ticket, [4] prologue ticket
     u32 calls;
     u32 wait_polls;
 };
@@ -110,11 +110,9 @@ struct EpDev {  // what the exchange kernels need, by value
     u64 codes, deltas, sums, ids, wts;
 };
 
-__global__ void ep_begin_kernel(u32* counters) {
-    counters[0] += 1;
-    counters[1] = 0;
-    counters[2] = 0;
-}
+// Step numbers: counters[0] holds the number of COMPLETED steps; every kernel of a step uses counters[0] + 1 and the
+// step's last kernel (the fold) increments it, so a replayed graph keeps counting without a host-side argument.
+__device__ __forceinline__ u32 current_step(const u32* counters) { return *reinterpret_cast<const volatile u32*>(&counters[0]) + 1u; }
 
 // One block per home row: the row's A8 record to every rank that owns one of its experts, its ids and weights to all.
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDev d, b200moe_a8_rows x, const u32* __restrict__ ids, const float* __restrict__ wts,
@@ -156,35 +154,60 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDev d, b200moe_a8_ro
     __syncthreads();
     if (!s_last) return;
     __threadfence_system();
-    const u32 step = *reinterpret_cast<volatile u32*>(&counters[0]);
+    const u32 step = current_step(counters);
     if (tid < d.world) *reinterpret_cast<volatile u32*>(d.win[tid] + 4u * d.rank) = step;
 }
 
-// After the combine kernel's peer stores (a launch boundary orders them before this kernel): the return flags.
-__global__ void ep_signal_kernel(EpDev d, u32* counters, u32* summary) {
-    __threadfence_system();
-    const u32 step = *reinterpret_cast<volatile u32*>(&counters[0]);
-    if (threadIdx.x < d.world) *reinterpret_cast<volatile u32*>(d.win[threadIdx.x] + 128u + 4u * d.rank) = step;
-    if (threadIdx.x == 0 && counters[2] && summary) atomicOr(summary, B200MOE_JOB_WAIT_ABORTED);  // the dispatch wait gave up
-}
-
-// Waits until every source's flag word holds at least the current step; bounded. On a timeout: note_word (the layer
-// clears the job summary after the dispatch wait, so that wait reports through the counters) or the summary itself.
-__global__ void ep_wait_kernel(const unsigned char* flags, u32 world, const u32* counters, u32 polls, u32* note_word, u32* summary) {
-    const u32 step = counters[0];
+// Waits until every source's dispatch flag holds at least the current step; bounded. On a timeout it notes it in
+// counters[2] (the layer clears the job summary after this kernel, so the fold reports it). Also resets the dispatch ticket.
+__global__ void ep_wait_dispatch_kernel(const unsigned char* flags, u32 world, u32* counters, u32 polls) {
+    const u32 step = current_step(counters);
+    if (threadIdx.x == 0) { counters[1] = 0; counters[2] = 0; }
+    __syncthreads();
     if (threadIdx.x >= world) return;
     const volatile u32* f = reinterpret_cast<const volatile u32*>(flags) + threadIdx.x;
     for (u32 i = 0; i < polls; ++i) {
         if (static_cast<int>(*f - step) >= 0) { __threadfence_system(); return; }
         __nanosleep(200);
     }
-    if (note_word) *note_word = 1u;
-    if (summary) atomicOr(summary, B200MOE_JOB_WAIT_ABORTED);
+    counters[2] = 1u;
 }
 
-__global__ void __launch_bounds__(256) ep_fold_kernel(const float* __restrict__ parts, u32 n_parts, u64 part_stride, const float* __restrict__ shared,
-                                                      u64 count, float* __restrict__ y, u16* __restrict__ y_bf16, const u32* summary) {
-    if (summary && (*summary & B200MOE_JOB_WAIT_ABORTED)) return;  // fail closed: a piece never arrived
+// The last kernel of a step, after the combine kernel's peer stores (a launch boundary orders them before this kernel):
+// block 0 raises this rank's return flag on every rank; every block then waits (bounded) for all W return flags and
+// folds y = (((shared + S_0) + S_1) + ...) + S_{F-1}. Block 0 closes the step (counters[0] += 1), aborted or not.
+__global__ void __launch_bounds__(256) ep_fold_kernel(EpDev d, const unsigned char* window, const float* __restrict__ parts, u32 n_parts, u64 part_stride,
+                                                      const float* __restrict__ shared, u64 count, float* __restrict__ y, u16* __restrict__ y_bf16,
+                                                      u32* counters, u32 polls, u32* summary) {
+    __shared__ u32 s_ok;
+    const u32 step = current_step(counters);
+    if (threadIdx.x == 0) s_ok = 1;
+    if (blockIdx.x == 0) {
+        __threadfence_system();
+        if (threadIdx.x < d.world) *reinterpret_cast<volatile u32*>(d.win[threadIdx.x] + 128u + 4u * d.rank) = step;
+    }
+    __syncthreads();
+    if (threadIdx.x < d.world) {
+        const volatile u32* f = reinterpret_cast<const volatile u32*>(window + 128) + threadIdx.x;
+        bool seen = false;
+        for (u32 i = 0; i < polls && !seen; ++i) {
+            seen = static_cast<int>(*f - step) >= 0;
+            if (!seen) __nanosleep(200);
+        }
+        if (!seen || counters[2]) s_ok = 0;  // a return never arrived, or the dispatch wait had given up
+        __threadfence_system();
+    }
+    __syncthreads();
+    const bool ok = s_ok != 0 && !(summary && (*summary & B200MOE_JOB_WAIT_ABORTED));
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        if (!s_ok && summary) atomicOr(summary, B200MOE_JOB_WAIT_ABORTED);
+    }
+    // the step is closed by the last block to get here (every block has read the step number by then)
+    __shared__ u32 s_last;
+    if (threadIdx.x == 0) s_last = atomicAdd(&counters[3], 1u) == gridDim.x - 1u ? 1u : 0u;
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) { counters[3] = 0; __threadfence(); counters[0] = step; }
+    if (!ok) return;  // fail closed: a piece never arrived
     const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= count) return;
     float acc = shared ? shared[i] : 0.0f;
@@ -278,9 +301,6 @@ int b200moe_ep_ffn(void* handle, const b200moe_ep_step_view* v, void* stream) {
     const u64 half_base = kFlagBytes + parity * ep->lay.half;
     unsigned char* mine = ep->win[ep->rank];
 
-    ep_begin_kernel<<<1, 1, 0, st>>>(ep->counters);
-    if (int rc = after_launch("ep_begin")) return rc;
-
     // 1. route the home rows
     const float* x32 = static_cast<const float*>(v->x);
     if (v->x_is_bf16) {
@@ -293,8 +313,14 @@ int b200moe_ep_ffn(void* handle, const b200moe_ep_step_view* v, void* stream) {
     r.x = x32; r.x_stride = s.hidden; r.rows = v->rows; r.hidden = s.hidden;
     r.weight = v->router_weight; r.logit_bias = v->logit_bias; r.bias = v->select_bias; r.policy = ep->policy;
     r.logits = W.logits; r.scores = W.logits; r.ids = W.ids; r.weights = W.wts;
-    if (int rc = launch_router_logits(r, st, &q)) return rc;
-    if (int rc = launch_router_select(r, st)) return rc;
+    if (prologue_fusable(r, s.top_k)) {  // decode windows: A8 + logits + selection in one launch (no local routes: null outputs)
+        b200moe_routes_view none{};
+        none.rows = v->rows; none.top_k = s.top_k; none.experts = s.experts;
+        if (int rc = launch_prologue(r, q, none, ep->counters + 4, st)) return rc;
+    } else {
+        if (int rc = launch_router_logits(r, st, &q)) return rc;
+        if (int rc = launch_router_select(r, st)) return rc;
+    }
 
     // 2. dispatch, then wait for every rank's rows
     EpDev d{};
@@ -303,7 +329,7 @@ int b200moe_ep_ffn(void* handle, const b200moe_ep_step_view* v, void* stream) {
     d.half_base = half_base; d.codes = ep->lay.codes; d.deltas = ep->lay.deltas; d.sums = ep->lay.sums; d.ids = ep->lay.ids; d.wts = ep->lay.wts;
     ep_dispatch_kernel<<<v->rows, 256, 0, st>>>(d, W.x, W.ids, W.wts, ep->counters);
     if (int rc = after_launch("ep_dispatch")) return rc;
-    ep_wait_kernel<<<1, 32, 0, st>>>(mine, ep->world, ep->counters, ep->wait_polls, ep->counters + 2, nullptr);
+    ep_wait_dispatch_kernel<<<1, 32, 0, st>>>(mine, ep->world, ep->counters, ep->wait_polls);
     if (int rc = after_launch("ep_wait_dispatch")) return rc;
 
     // 3. the local experts over the global window; the combine stores S_rank of every row into its home rank's window
@@ -325,14 +351,11 @@ int b200moe_ep_ffn(void* handle, const b200moe_ep_step_view* v, void* stream) {
     lv.summary = summary; lv.stage_events = v->stage_events;
     if (int rc = b200moe_layer(&lv, stream)) return rc;
 
-    // 4. return flags, wait for every rank's partial sums, fold
-    ep_signal_kernel<<<1, 32, 0, st>>>(d, ep->counters, summary);
-    if (int rc = after_launch("ep_signal")) return rc;
-    ep_wait_kernel<<<1, 32, 0, st>>>(mine + 128, ep->world, ep->counters, ep->wait_polls, nullptr, summary);
-    if (int rc = after_launch("ep_wait_return")) return rc;
+    // 4. return flags, the wait for every rank's partial sums and the fold: one launch
     const u64 count = u64(v->rows) * s.hidden;
     const float* parts = reinterpret_cast<const float*>(half + ep->lay.parts);
-    ep_fold_kernel<<<static_cast<u32>((count + 255) / 256), 256, 0, st>>>(parts, ep->fold, u64(ep->rows) * s.hidden, v->shared, count, v->y, v->y_bf16, summary);
+    ep_fold_kernel<<<static_cast<u32>((count + 255) / 256), 256, 0, st>>>(d, mine, parts, ep->fold, u64(ep->rows) * s.hidden, v->shared, count, v->y, v->y_bf16,
+                                                                          ep->counters, ep->wait_polls, summary);
     return after_launch("ep_fold");
 }
 

@@ -32,9 +32,11 @@
 // job summary and the kernel returns - the host reads a status, the GPU never hangs.
 //
 // Roofline: HBM. Algorithmic bytes per item = 64 rows x K / 256 x 144 (+ the entries' A8 bytes).
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <type_traits>
 
 #include "q4k_row.cuh"
 
@@ -92,6 +94,21 @@ struct VExpert {  // one word: expert index (10 bits, experts <= 1024), first en
     __host__ __device__ u32 ne() const { return bits >> 24; }
 };
 
+// Stage geometry for S super-blocks per stage, as compile-time constants: the kernels are bound by issue slots, and
+// address arithmetic on run-time strides was a measurable part of them.
+constexpr u32 x_entry_bytes_of(u32 S) {  // codes, deltas, sums of one entry over a stage, padded so that entries lie 8 or 24
+    u32 b = S * 320u;                     // (mod 32) words apart: the mma form reads 8 bytes per lane at (entry, k slice) and
+    while ((b / 4) % 32 != 8 && (b / 4) % 32 != 24) b += 16;  // four entries then cover all banks once
+    return b;
+}
+template <u32 S_>
+struct Geo {
+    static constexpr u32 S = S_;
+    static constexpr u32 row_seg_bytes = S * kQ4KBlock;
+    static constexpr u32 w_bytes = kItemRows * row_seg_bytes;
+    static constexpr u32 x_entry_bytes = x_entry_bytes_of(S);
+};
+
 __device__ __forceinline__ u32 warp_inclusive_scan(u32 v, u32 lane) {
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) { const u32 o = __shfl_up_sync(0xffffffffu, v, d); if (lane >= (u32)d) v += o; }
@@ -122,10 +139,12 @@ __device__ __forceinline__ float tree4(float a) {
 // One stage of one weight row (this lane's pair p of nbk super-blocks, ascending) against NR staged A8 rows. blk: the
 // row's first super-block of the stage; xs: entry 0's area of the stage ({codes[S * 256], deltas[S * 8], sums[S * 8]},
 // the next entry x_entry_bytes further). acc[r] is the lane's chain acc_p of entry r.
-template <int NR>
-__device__ __forceinline__ void stage_rows(const uint4* blk, u32 nbk, u32 p, const unsigned char* xs, u32 x_entry_bytes, u32 S, float* acc) {
-#pragma unroll 1
-    for (u32 b = 0; b < nbk; ++b, blk += kQ4KBlock / 16) {
+template <int NR, class G>
+__device__ __forceinline__ void stage_rows(const uint4* blk, u32 nbk, u32 p, const unsigned char* xs, float* acc) {
+    constexpr u32 x_entry_bytes = G::x_entry_bytes, S = G::S;
+#pragma unroll
+    for (u32 b = 0; b < S; ++b, blk += kQ4KBlock / 16) {
+        if (b >= nbk) break;
         const uint4 hdr = blk[0], q0 = blk[1 + 2 * p], q1 = blk[2 + 2 * p];
         const Factors f = q4k_factors(hdr, p);
         const Nibbles n = split_nibbles(q0, q1);
@@ -142,15 +161,6 @@ __device__ __forceinline__ void stage_rows(const uint4* blk, u32 nbk, u32 p, con
         }
     }
 }
-__device__ __forceinline__ void stage_rows_n(u32 nr, const uint4* blk, u32 nbk, u32 p, const unsigned char* xs, u32 xeb, u32 S, float* acc) {
-    switch (nr) {  // no per-entry branches inside the block loop
-        case 1: stage_rows<1>(blk, nbk, p, xs, xeb, S, acc); break;
-        case 2: stage_rows<2>(blk, nbk, p, xs, xeb, S, acc); break;
-        case 3: stage_rows<3>(blk, nbk, p, xs, xeb, S, acc); break;
-        default: stage_rows<4>(blk, nbk, p, xs, xeb, S, acc); break;
-    }
-}
-
 // ---- the mma form of one stage ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_s8u8(int& c0, int& c1, u32 a0, u32 a2, u32 b0, u32 b1) {
     // D (16 x 8, s32) = A (16 x 32, s8, row) * B (32 x 8, u8, col); rows 8 .. 15 of A are zero (at most 8 entries).
@@ -168,15 +178,16 @@ __device__ __forceinline__ float pair_from_dots(float Dl, float DMl, float Dh, f
 // One stage of the warp's 8 weight rows against up to 8 staged A8 rows with tensor-core dots. w8: the warp's first row of
 // the stage (rows row_seg_bytes apart); fac: the warp's scratch. Lane = (e = lane >> 2, t = lane & 3): acc[4 * i + p] is the
 // chain acc_p of (row 2t + i, entry e). Lanes of absent entries compute on stale shared memory and are never stored.
-__device__ __forceinline__ void stage_rows_mma(const unsigned char* w8, u32 row_seg_bytes, u32 nbk, u32 lane, const unsigned char* xs,
-                                               u32 x_entry_bytes, u32 S, float* fac, float* acc) {
+template <class G>
+__device__ __forceinline__ void stage_rows_mma(const unsigned char* w8, u32 nbk, u32 lane, const unsigned char* xs, float* fac, float* acc) {
+    constexpr u32 row_seg_bytes = G::row_seg_bytes, x_entry_bytes = G::x_entry_bytes, S = G::S;
     const u32 p = lane >> 3, rr = lane & 7u;   // factor decode: lane = (pair, row), as in the dp4a form
     const u32 e = lane >> 2, t = lane & 3u;    // mma fragments: lane = (entry or weight row, k slice)
     const unsigned char* xe = xs + e * x_entry_bytes;
     const unsigned char* wdec = w8 + rr * row_seg_bytes;
     const unsigned char* wfrag = w8 + e * row_seg_bytes + 16u + 8u * t;   // B fragment: weight row n = lane >> 2
 #pragma unroll 1
-    for (u32 b = 0; b < nbk; ++b) {
+    for (u32 b = 0; b < nbk; ++b) {  // rolled: the body is long, and the form runs where the instruction cache matters
         const uint4 hdr = *reinterpret_cast<const uint4*>(wdec + kQ4KBlock * b);
         const Factors f = q4k_factors(hdr, p);
         __syncwarp();   // the previous block's readers are done with the scratch
@@ -204,16 +215,19 @@ __device__ __forceinline__ void stage_rows_mma(const unsigned char* w8, u32 row_
     }
 }
 
-template <bool DOWN>
+// 18 warps: two of the SM's four register partitions (16 K registers each) hold five warps, which caps a thread at
+// 16384 / (5 x 32) = 102 registers, 96 after rounding - what this launch bound gives (112 was tried: the launch is refused).
+template <bool DOWN, u32 S_>
 __global__ void __launch_bounds__(kThreads, 1)
 q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, WideArgs a, WidePlan plan) {
+    using G = Geo<S_>;
     extern __shared__ __align__(128) unsigned char smem[];
     if (DOWN && a.summary && *a.summary) return;  // a failed or aborted projection skips the whole stage (routed_expert.hpp:17-19)
     u32 n_union = a.routes.counts[0];
     if (n_union == 0) return;
     if (n_union > plan.max_union) n_union = plan.max_union;
 
-    unsigned char* at = smem + u64(kGroups) * plan.stages * plan.stage_bytes;
+    unsigned char* at = smem + kGroups * plan.stages * plan.stage_bytes;
     float* s_gu = reinterpret_cast<float*>(at);  // [group][buffer][gate | up][entry][32]
     if (!DOWN) at += kGroups * 2 * 2 * kKE * 32 * 4;
     VExpert* table = reinterpret_cast<VExpert*>(at);
@@ -281,10 +295,10 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
         u64* g_full = full + g * plan.stages;
         u64* g_empty = empty + g * plan.stages;
         u32* g_item = slot_item + g * plan.stages;
-        unsigned char* g_stage = smem + u64(g) * plan.stages * plan.stage_bytes;
+        unsigned char* g_stage = smem + g * plan.stages * plan.stage_bytes;
         const u32 e = lane / 3u, part = lane - 3u * e;  // lanes 0 .. 3 * ne - 1 copy one piece of one entry each
         const u32 in_stride = a.in.stride ? a.in.stride : a.in.width, in_gs = in_stride / 32;
-        u32 t = 0;
+        u32 t = 0, slot = 0, use = 0;  // stage count, ring position, lap
         bool ok = true;
         for (;;) {
             u32 k = 0;
@@ -303,8 +317,8 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
             u32 r = 0;
             if (e < ve_ne) r = __ldg((DOWN ? a.routes.slots : a.routes.rows) + ve.begin() + e);
             const u32 nsegs = end ? 1u : plan.nseg;
-            for (u32 s = 0; s < nsegs; ++s, ++t) {
-                const u32 slot = t % plan.stages, use = t / plan.stages;
+            for (u32 s = 0; s < nsegs; ++s, ++t, ++slot) {
+                if (slot == plan.stages) { slot = 0; ++use; }
                 if (use) ok = mbar_wait(&g_empty[slot], (use - 1u) & 1u, plan.wait_limit, abort_flag);  // the slot's previous use is done
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -314,28 +328,28 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
                     if (lane == 0) { g_item[slot] = kEndItem; mbar_arrive(&g_full[slot]); }
                     continue;
                 }
-                const u32 nbk = min(plan.S, plan.nb - s * plan.S);
-                unsigned char* dst = g_stage + u64(slot) * plan.stage_bytes;
+                const u32 nbk = min(G::S, plan.nb - s * G::S);
+                unsigned char* dst = g_stage + slot * plan.stage_bytes;
                 if (lane == 0) {
                     g_item[slot] = item;
-                    mbar_expect_tx(&g_full[slot], plan.w_bytes + ve_ne * nbk * 320u);
+                    mbar_expect_tx(&g_full[slot], G::w_bytes + ve_ne * nbk * 320u);
                 }
                 __syncwarp();
                 if (lane == 0) {
-                    const u32 x = s * plan.S * (kQ4KBlock / 4);  // 32-bit elements: a multiple of 36, i.e. of 144 bytes
+                    const u32 x = s * G::S * (kQ4KBlock / 4);  // 32-bit elements: a multiple of 36, i.e. of 144 bytes
                     if (DOWN) {
                         tma_2d(dst, &tm0, x, ve.expert() * a.rows_per_expert + kItemRows * chunk, &g_full[slot]);
                     } else {
                         const u32 y = ve.expert() * a.rows_per_expert + 32u * chunk;
                         tma_2d(dst, &tm0, x, y, &g_full[slot]);
-                        tma_2d(dst + 32u * plan.row_seg_bytes, &tm1, x, y, &g_full[slot]);
+                        tma_2d(dst + 32u * G::row_seg_bytes, &tm1, x, y, &g_full[slot]);
                     }
                 }
                 if (e < ve_ne) {
-                    unsigned char* xd = dst + plan.w_bytes + e * plan.x_entry_bytes;
-                    if (part == 0) bulk_g2s(xd, a.in.codes + u64(r) * in_stride + u64(s) * plan.S * 256u, nbk * 256u, &g_full[slot]);
-                    else if (part == 1) bulk_g2s(xd + 256u * plan.S, a.in.deltas + u64(r) * in_gs + u64(s) * plan.S * 8u, nbk * 32u, &g_full[slot]);
-                    else bulk_g2s(xd + 288u * plan.S, a.in.sums + u64(r) * in_gs + u64(s) * plan.S * 8u, nbk * 32u, &g_full[slot]);
+                    unsigned char* xd = dst + G::w_bytes + e * G::x_entry_bytes;
+                    if (part == 0) bulk_g2s(xd, a.in.codes + u64(r) * in_stride + u64(s) * G::S * 256u, nbk * 256u, &g_full[slot]);
+                    else if (part == 1) bulk_g2s(xd + 256u * G::S, a.in.deltas + u64(r) * in_gs + u64(s) * G::S * 8u, nbk * 32u, &g_full[slot]);
+                    else bulk_g2s(xd + 288u * G::S, a.in.sums + u64(r) * in_gs + u64(s) * G::S * 8u, nbk * 32u, &g_full[slot]);
                 }
             }
             if (!ok || end) break;
@@ -355,13 +369,12 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
     u64* g_full = full + g * plan.stages;
     u64* g_empty = empty + g * plan.stages;
     const u32* g_item = slot_item + g * plan.stages;
-    const unsigned char* g_stage = smem + u64(g) * plan.stages * plan.stage_bytes;
+    const unsigned char* g_stage = smem + g * plan.stages * plan.stage_bytes;
     const u32 act_stride = DOWN ? 0u : (a.act.stride ? a.act.stride : a.act.width);
-    u32 t = 0, kl = 0;
+    u32 slot = 0, phase = 0, kl = 0;  // ring position of the group's next stage, kept incrementally (no divisions in the loop)
     bool ok = true;
     for (;;) {
-        u32 slot = t % plan.stages;
-        ok = mbar_wait(&g_full[slot], (t / plan.stages) & 1u, plan.wait_limit, abort_flag);
+        ok = mbar_wait(&g_full[slot], phase, plan.wait_limit, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const u32 item = g_item[slot];
@@ -373,21 +386,30 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
         float acc[kKE];
 #pragma unroll
         for (int r = 0; r < (int)kKE; ++r) acc[r] = 0.0f;
-        for (u32 s = 0; s < plan.nseg; ++s, ++t) {
-            if (s) {
-                slot = t % plan.stages;
-                ok = mbar_wait(&g_full[slot], (t / plan.stages) & 1u, plan.wait_limit, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+        // the item's stages, with the form and the entry count fixed at compile time inside the loop (NR = 0: the mma form)
+        auto run = [&](auto tag) {
+            constexpr int NR = decltype(tag)::value;
+            for (u32 s = 0; s < plan.nseg; ++s) {
+                if (s) {
+                    ok = mbar_wait(&g_full[slot], phase, plan.wait_limit, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) return;
+                }
+                const unsigned char* st = g_stage + slot * plan.stage_bytes;
+                const u32 nbk = min(G::S, plan.nb - s * G::S);
+                if constexpr (NR == 0) stage_rows_mma<G>(st + 8u * w * G::row_seg_bytes, nbk, lane, st + G::w_bytes, fac, acc);
+                else stage_rows<NR, G>(reinterpret_cast<const uint4*>(st + (8u * w + rr) * G::row_seg_bytes), nbk, p, st + G::w_bytes, acc);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&g_empty[slot]);  // the stage is free for the producer
+                if (++slot == plan.stages) { slot = 0; phase ^= 1u; }
             }
-            const unsigned char* st = g_stage + u64(slot) * plan.stage_bytes;
-            const uint4* blk = reinterpret_cast<const uint4*>(st + (8u * w + rr) * plan.row_seg_bytes);
-            const unsigned char* xs = st + plan.w_bytes;
-            const u32 nbk = min(plan.S, plan.nb - s * plan.S);
-            if (mma) stage_rows_mma(st + 8u * w * plan.row_seg_bytes, plan.row_seg_bytes, nbk, lane, xs, plan.x_entry_bytes, plan.S, fac, acc);
-            else stage_rows_n(ne, blk, nbk, p, xs, plan.x_entry_bytes, plan.S, acc);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&g_empty[slot]);  // the stage is free for the producer
+        };
+        switch (mma ? 0u : ne) {
+            case 0: run(std::integral_constant<int, 0>{}); break;
+            case 1: run(std::integral_constant<int, 1>{}); break;
+            case 2: run(std::integral_constant<int, 2>{}); break;
+            case 3: run(std::integral_constant<int, 3>{}); break;
+            default: run(std::integral_constant<int, 4>{}); break;
         }
         if (!ok) break;
         // mma form: lane (e = lane >> 2, t = lane & 3) holds the four chains of rows 2t and 2t + 1 of entry e
@@ -513,16 +535,15 @@ bool make_plan(u32 K, u32 n_chunks, u32 max_union, u64 slots, bool down, WidePla
     p->nseg = (p->nb + p->S - 1) / p->S;
     p->row_seg_bytes = p->S * kQ4KBlock;
     p->w_bytes = kItemRows * p->row_seg_bytes;
-    // codes, deltas, sums of one entry over a stage, padded so that entries lie 8 (mod 32) words apart: the mma form reads
-    // 8 bytes per lane at (entry, k slice) and four entries then cover all banks once
-    p->x_entry_bytes = p->S * 320u;
-    while ((p->x_entry_bytes / 4) % 32 != 8 && (p->x_entry_bytes / 4) % 32 != 24) p->x_entry_bytes += 16;
-    p->stage_bytes = round_up(p->w_bytes + kKE * p->x_entry_bytes, 128);
+    p->x_entry_bytes = x_entry_bytes_of(p->S);
+    // a stage holds the A8 segments of as many entries as a virtual expert of this window can have: windows of fewer than
+    // kKE slots get smaller stages and with them a deeper ring
+    p->stage_bytes = round_up(p->w_bytes + static_cast<u32>(std::min<u64>(kKE, slots)) * p->x_entry_bytes, 128);
     p->n_chunks = n_chunks;
     p->max_union = max_union;
     p->vmax = max_union + static_cast<u32>(slots / kKE) + 1;
     if (u64(p->vmax) * n_chunks >= (1ull << 31)) return false;
-    for (p->stages = 4; p->stages >= 2; --p->stages)
+    for (p->stages = 5; p->stages >= 2; --p->stages)
         if (plan_smem(*p, down) <= kSmemBudget) break;
     if (p->stages < 2) return false;
     if ((2 * max_union + 2 + p->vmax) * 4 > kGroups * p->stages * p->stage_bytes) return false;  // the copied routes and the cost prefix borrow the stage area
@@ -570,8 +591,13 @@ int launch_gate_up_q4k_wide(const b200moe_gate_up_view& v, u32 rows, cudaStream_
     if (int rc = rows_map(v.weights.gate, rb, total_rows, p.S, 32, &tm0)) return rc;
     if (int rc = rows_map(v.weights.up, rb, total_rows, p.S, 32, &tm1)) return rc;
     const u32 smem = plan_smem(p, false);
-    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(q4k_wide_kernel<false>), smem)) return rc;
-    q4k_wide_kernel<false><<<sm_count(), kThreads, smem, stream>>>(tm0, tm1, a, p);
+    if (p.S == 3) {
+        if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(q4k_wide_kernel<false, 3>), smem)) return rc;
+        q4k_wide_kernel<false, 3><<<sm_count(), kThreads, smem, stream>>>(tm0, tm1, a, p);
+    } else {
+        if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(q4k_wide_kernel<false, 1>), smem)) return rc;
+        q4k_wide_kernel<false, 1><<<sm_count(), kThreads, smem, stream>>>(tm0, tm1, a, p);
+    }
     return after_launch("gate_up_q4k_wide");
 }
 
@@ -587,8 +613,13 @@ int launch_down_q4k_wide(const b200moe_down_view& v, u32 rows, cudaStream_t stre
     CUtensorMap tm0;
     if (int rc = rows_map(v.weights.down, u64(p.nb) * kQ4KBlock, u64(v.shape.experts) * v.shape.hidden, p.S, 64, &tm0)) return rc;
     const u32 smem = plan_smem(p, true);
-    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(q4k_wide_kernel<true>), smem)) return rc;
-    q4k_wide_kernel<true><<<sm_count(), kThreads, smem, stream>>>(tm0, tm0, a, p);
+    if (p.S == 3) {
+        if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(q4k_wide_kernel<true, 3>), smem)) return rc;
+        q4k_wide_kernel<true, 3><<<sm_count(), kThreads, smem, stream>>>(tm0, tm0, a, p);
+    } else {
+        if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(q4k_wide_kernel<true, 1>), smem)) return rc;
+        q4k_wide_kernel<true, 1><<<sm_count(), kThreads, smem, stream>>>(tm0, tm0, a, p);
+    }
     return after_launch("down_q4k_wide");
 }
 

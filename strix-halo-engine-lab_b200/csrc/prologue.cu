@@ -17,6 +17,9 @@
 namespace b200moe {
 namespace {
 
+// Eight experts (= warps) per logits block. Fewer experts per block spread the logits over more CTAs but every CTA stages the
+// window's activation rows itself: measured on B200 at config 2, batch 8, 4 and 2 experts per block cost 80.6 and 92.5 us per
+// step against 76.2 us with 8 (no difference at batch 1).
 constexpr u32 kRunElems = 2048, kWarps = 8;
 
 __device__ __forceinline__ u32 smem_addr(const void* p) { return static_cast<u32>(__cvta_generic_to_shared(p)); }
@@ -27,7 +30,7 @@ struct PrologueArgs {
     b200moe_routes_view routes;
     u32 routes_end;
     u32 logit_blocks;
-    u32* ticket;  // zeroed by the caller before the launch
+    u32* ticket;  // zero before the first launch; the block that finishes last puts it back to zero
 };
 
 template <int RT>
@@ -122,10 +125,11 @@ __global__ void __launch_bounds__(kWarps * 32) prologue_decode_kernel(PrologueAr
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    if (threadIdx.x == 0) *a.ticket = 0;  // every block has taken its ticket: ready for the next launch without a memset
     for (u32 row = warp; row < rows; row += kWarps)
         select_detail::select_row(rv.logits, rv.scores, rv.bias, rv.policy, row, lane, xs + warp * (2u * E + 32u), rv.ids, rv.weights);
     __syncthreads();  // the ids written above are read below by the whole block
-    routes_detail::routes_small_body(a.routes, a.routes_end);
+    if (a.routes.out.experts) routes_detail::routes_small_body(a.routes, a.routes_end);  // optional: a caller that routes elsewhere passes no outputs
 }
 
 }  // namespace
