@@ -442,7 +442,7 @@ class C4Model:
         from b200moe import synth
         self.cfg = cfg
         H, E, I = cfg["hidden"], cfg["experts"], cfg["inter"]
-        self.per = E // C4_PARTS
+        self.per = 32
         rng0 = np.random.default_rng(400)
         self.rw = synth.router_weight(rng0, E, H)
         self.bias = (rng0.standard_normal(E) * 0.1).astype(np.float32)
@@ -570,6 +570,9 @@ def large_arm(args, cfg, rank, world, dev):
 
     K, W = args.steps if args.steps != 2000 else 40, max(min(args.warmup, 20), 3)
     B = args.batch if args.batch != 8 else C4_GLOBAL_BATCH
+    if args.experts:
+        assert args.experts % 32 == 0 and world == 1, "--experts: a multiple of 32, one GPU"
+        cfg = dict(cfg, experts=args.experts, desc=cfg["desc"].replace("256 Q4_K experts", f"{args.experts} Q4_K experts (REDUCED layer for a profiler capture)"))
     assert B % world == 0 and cfg["experts"] % world == 0, "the global batch and the experts must split over the ranks"
     R = B // world
     H, E, TK, I = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["inter"]
@@ -580,7 +583,8 @@ def large_arm(args, cfg, rank, world, dev):
     policy = ops.sigmoid_group_policy(E, TK, 8, 4)
     rw, bias = torch.from_numpy(model.rw).to(dev), torch.from_numpy(model.bias).to(dev)
     sg, su, sd = (torch.from_numpy(a).to(dev) for a in model.shared)
-    slices = range(C4_PARTS) if world == 1 else range(rank * C4_PARTS // world, (rank + 1) * C4_PARTS // world)
+    n_slices = cfg["experts"] // model.per
+    slices = range(n_slices) if world == 1 else range(rank * C4_PARTS // world, (rank + 1) * C4_PARTS // world)
     parts = [model.slice_device(r, dev) for r in slices]
     gate, up, down = (torch.cat([p[t] for p in parts]) for t in range(3))
     del parts
@@ -595,7 +599,7 @@ def large_arm(args, cfg, rank, world, dev):
         layer = ep.PeerEpFfn(shape, policy, rw, gate, up, down, R, select_bias=bias, fold_parts=C4_PARTS)
         routed = lambda x, shared, y, ev=None: b200moe.check(b200moe.lib().b200moe_ep_ffn(layer.handle, C.byref(layer.view(x, y, shared, summary, ev)), b200moe.stream_ptr()))
     else:
-        ffn = ops.MoeFfn(shape, policy, gate, up, down, rw, capacity=B, combine_form=b200moe.COMBINE_PARTS, parts=C4_PARTS, select_bias=bias)
+        ffn = ops.MoeFfn(shape, policy, gate, up, down, rw, capacity=B, combine_form=b200moe.COMBINE_PARTS, parts=C4_PARTS, select_bias=bias)  # part_experts = E / 8
         routed = lambda x, shared, y, ev=None: b200moe.check(b200moe.lib().b200moe_ffn(C.byref(ffn._view(R, x, y, shared=shared, events=ev, summary=summary)), b200moe.stream_ptr()))
 
     def step(s, x=None, ev=None):
@@ -1054,6 +1058,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=4, help="distinct layers of weights rotated between steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=0,
+                    help="config 4: a reduced layer of this many routed experts (a multiple of 32; 0 = the config's 256) for profiler captures, "
+                         "which must hold only a few GB on the device; the line then says so in config.workload")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of one step with the CPU oracle (the `parity` key)")
     ap.add_argument("--no-extra", action="store_true", help="config 4 on one GPU: skip the config 2 batch 8 figures under extra.c2_b8")
     ap.add_argument("--no-graph", action="store_true", help="config 4 arm: launch every step eagerly instead of replaying a CUDA graph")

@@ -57,7 +57,9 @@ int device_sm_count() {
 }
 
 int ensure_dynamic_smem(const void* kernel, u32 bytes) {
-    if (bytes <= 48u * 1024u) return B200MOE_OK;
+    // The 48 KiB a launch gets without opting in cover static AND dynamic shared memory: kernels here declare up to a few
+    // KiB statically, so the opt-in starts below the limit.
+    if (bytes <= 40u * 1024u) return B200MOE_OK;
     static std::mutex m;
     static std::map<std::pair<int, const void*>, u32> granted;
     int dev = 0;
@@ -241,8 +243,15 @@ DecodeForm pick_decode_form(bool row_stream_fits, bool wide_fits, u32 rows, u32 
     if (wide_fits) return DecodeForm::wide;
     return row_stream_fits ? DecodeForm::row_stream : DecodeForm::block;
 }
+// The DS41 family (Q8_0 x A8): one weight row per warp up to kRowStreamRows rows, the token-block form of gemv_q8_wide.cu
+// above that (a lane there keeps the codes of four entries in registers over four weight rows).
+bool use_q8_wide(bool fits, u32 rows) {
+    const u32 forced = debug_value(B200MOE_DEBUG_DECODE_FORM);
+    if (!fits || forced == 3) return false;
+    return forced == 2 || rows > kRowStreamRows;
+}
 int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
-    if (!is_kquant(v.shape.gate_type)) return launch_gate_up_q8(v, st);
+    if (!is_kquant(v.shape.gate_type)) return use_q8_wide(q8_wide_gate_up_fits(v, rows), rows) ? launch_gate_up_q8_wide(v, rows, st) : launch_gate_up_q8(v, st);
     if (v.shape.gate_type == B200MOE_TYPE_Q5_K) return launch_gate_up_q4k(v, st);  // the per-block form reads both K-quant layouts
     if (use_grouped(v.shape, rows, grouped_min_rows, v.x.sums != nullptr)) return launch_gate_up_q4k_grouped(v, st);
     switch (pick_decode_form(stream_gate_up_fits(v, rows), wide_gate_up_fits(v, rows), rows, v.shape.hidden)) {
@@ -260,7 +269,8 @@ int enqueue_down(const b200moe_down_view& v, u32 rows, cudaStream_t st, u32 grou
             default: return launch_down_q4k(v, st);
         }
     }
-    return is_kquant(v.shape.gate_type) ? launch_down_q8_chain4(v, st) : launch_down_q8(v, st);  // chain4: Q8_0 and Q5_1 blocks
+    if (is_kquant(v.shape.gate_type)) return launch_down_q8_chain4(v, st);  // chain4: Q8_0 and Q5_1 blocks
+    return use_q8_wide(q8_wide_down_fits(v, rows), rows) ? launch_down_q8_wide(v, rows, st) : launch_down_q8(v, st);
 }
 
 }  // namespace

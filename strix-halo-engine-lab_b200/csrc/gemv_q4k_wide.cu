@@ -33,29 +33,19 @@
 //
 // Roofline: HBM. Algorithmic bytes per item = 64 rows x K / 256 x 144 (+ the entries' A8 bytes).
 #include <algorithm>
-#include <map>
-#include <mutex>
-#include <tuple>
 #include <type_traits>
 
-#include "q4k_row.cuh"
+#include "wide_common.cuh"
 
 namespace b200moe {
 
 namespace {
 using namespace q4k;
+using namespace wide;
 
-constexpr u32 kKE = 8;                                  // entries of a virtual expert
-constexpr u32 kGroups = 2, kGroupWarps = 8;
-constexpr u32 kConsumerWarps = kGroups * kGroupWarps;
-constexpr u32 kThreads = (kConsumerWarps + kGroups) * 32;  // one producer warp per group
 constexpr u32 kItemRows = 64;
-constexpr u32 kEndItem = 0xffffffffu;
-constexpr u32 kCostFixed = 4, kCostEntry = 3;           // estimated cost of an item: fixed + per entry
 constexpr u32 kMmaMinEntries = 5;                       // items with at least this many entries take the mma form
 constexpr u32 kFacFloats = 128;                         // per-warp scratch of the mma form: [D, DM, D', DM'][pair][row]
-constexpr u32 kSmemBudget = 227u * 1024u;
-constexpr u32 kDefaultWaitLimit = 1u << 22;
 
 struct WidePlan {
     u32 S;              // super-blocks per stage
@@ -86,14 +76,6 @@ struct WideArgs {
     u32 out_width;         // inter (gate/up) or hidden (down)
 };
 
-struct VExpert {  // one word: expert index (10 bits, experts <= 1024), first entry in the routes (14 bits, slots <= 8192), entries (4 bits)
-    u32 bits;
-    __host__ __device__ static VExpert make(u32 expert, u32 begin, u32 ne) { return VExpert{expert | (begin << 10) | (ne << 24)}; }
-    __host__ __device__ u32 expert() const { return bits & 0x3ffu; }
-    __host__ __device__ u32 begin() const { return (bits >> 10) & 0x3fffu; }
-    __host__ __device__ u32 ne() const { return bits >> 24; }
-};
-
 // Stage geometry for S super-blocks per stage, as compile-time constants: the kernels are bound by issue slots, and
 // address arithmetic on run-time strides was a measurable part of them.
 constexpr u32 x_entry_bytes_of(u32 S) {  // codes, deltas, sums of one entry over a stage, padded so that entries lie 8 or 24
@@ -108,27 +90,6 @@ struct Geo {
     static constexpr u32 w_bytes = kItemRows * row_seg_bytes;
     static constexpr u32 x_entry_bytes = x_entry_bytes_of(S);
 };
-
-__device__ __forceinline__ u32 warp_inclusive_scan(u32 v, u32 lane) {
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) { const u32 o = __shfl_up_sync(0xffffffffu, v, d); if (lane >= (u32)d) v += o; }
-    return v;
-}
-__device__ __forceinline__ u32 virtual_cost(u32 ne) { return kCostFixed + kCostEntry * ne; }
-
-// First item whose cumulative cost start is >= B (items: virtual expert major, chunks ascending; an item of virtual
-// expert jv costs virtual_cost(ne) and starts at cum[jv] * nc + chunk * cost). B >= total * nc gives n_virtual * nc.
-__device__ u32 item_at(const VExpert* table, const u32* cum, u32 n_virtual, u32 nc, u64 total_items_cost, u64 B) {
-    if (B >= total_items_cost) return n_virtual * nc;
-    u32 lo = 0, hi = n_virtual - 1;  // last jv with cum[jv] * nc <= B
-    while (lo < hi) {
-        const u32 mid = (lo + hi + 1) >> 1;
-        if (u64(cum[mid]) * nc <= B) lo = mid; else hi = mid - 1;
-    }
-    const u32 c = virtual_cost(table[lo].ne());
-    const u64 excl = u64(cum[lo]) * nc;
-    return lo * nc + static_cast<u32>((B - excl + c - 1) / c);
-}
 
 // (a0 + a1) + (a2 + a3) over the four pair lanes of a row (lane = 8 * p + row); every lane of the row gets the value.
 __device__ __forceinline__ float tree4(float a) {
@@ -250,42 +211,7 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
     if (tid < kGroups * plan.stages + kGroups) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 
     // ---- the virtual expert list (the stage area is free until the first copy is issued: it holds the copied routes)
-    u32* t_beg = reinterpret_cast<u32*>(smem);
-    u32* t_exp = t_beg + plan.max_union + 1;
-    u32* t_cum = t_exp + plan.max_union;  // exclusive cost prefix of every virtual expert: only the work split reads it
-    for (u32 j = tid; j <= n_union; j += kThreads) {
-        t_beg[j] = __ldg(a.routes.begins + j);
-        if (j < n_union) t_exp[j] = __ldg(a.routes.experts + j);
-    }
-    __syncthreads();
-    if (warp == 0) {
-        u32 n_virtual = 0, total = 0;
-        for (u32 j0 = 0; j0 < n_union; j0 += 32) {
-            const u32 j = j0 + lane;
-            const u32 eb = j < n_union ? t_beg[j] : 0u, ne = j < n_union ? t_beg[j + 1] - eb : 0u;
-            const u32 nv = (ne + kKE - 1) / kKE, cost = nv * kCostFixed + ne * kCostEntry;
-            const u32 iv = warp_inclusive_scan(nv, lane), ic = warp_inclusive_scan(cost, lane);
-            u32 pos = n_virtual + iv - nv, cum = total + ic - cost;
-            for (u32 k = 0; k < nv && pos < plan.vmax; ++k, ++pos) {
-                const u32 part = min(kKE, ne - k * kKE);
-                table[pos] = VExpert::make(t_exp[j], eb + k * kKE, part);
-                t_cum[pos] = cum;
-                cum += virtual_cost(part);
-            }
-            n_virtual += __shfl_sync(0xffffffffu, iv, 31);
-            total += __shfl_sync(0xffffffffu, ic, 31);
-        }
-        if (n_virtual > plan.vmax) n_virtual = plan.vmax;
-        __syncwarp();
-        if (lane == 0) {
-            const u64 all = u64(total) * plan.n_chunks;
-            const u32 lo = item_at(table, t_cum, n_virtual, plan.n_chunks, all, all * blockIdx.x / gridDim.x);
-            const u32 hi = item_at(table, t_cum, n_virtual, plan.n_chunks, all, all * (blockIdx.x + 1) / gridDim.x);
-            ctl[2] = lo;
-            ctl[3] = hi - lo;
-        }
-    }
-    __syncthreads();
+    build_work_list(a.routes, n_union, plan.max_union, plan.vmax, plan.n_chunks, reinterpret_cast<u32*>(smem), table, ctl);
     const u32 first_item = ctl[2], n_local = ctl[3];
     if (n_local == 0) return;
 
@@ -336,7 +262,7 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
                 }
                 __syncwarp();
                 if (lane == 0) {
-                    const u32 x = s * G::S * (kQ4KBlock / 4);  // 32-bit elements: a multiple of 36, i.e. of 144 bytes
+                    const u32 x = s * G::S * (kQ4KBlock / 8);  // 64-bit elements: a multiple of 18, i.e. of 144 bytes
                     if (DOWN) {
                         tma_2d(dst, &tm0, x, ve.expert() * a.rows_per_expert + kItemRows * chunk, &g_full[slot]);
                     } else {
@@ -479,46 +405,6 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
     if (!ok && lane == 0 && a.summary) atomicOr(a.summary, kAbortBit);
 }
 
-int sm_count() {
-    int dev = 0, v = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v;
-}
-
-// Tensor map of a [rows][row_bytes] tensor seen as 32-bit elements, boxes of (36 * S elements = S super-blocks) x box_rows
-// rows, no swizzle. The encoder is the driver's cuTensorMapEncodeTiled, looked up through the runtime (no link against
-// the driver library). Encoded maps are kept per (device, tensor, geometry): encoding is host work of a few microseconds
-// that a decode step would otherwise pay on every call.
-int rows_map(const u8* base, u64 row_bytes, u64 rows, u32 S, u32 box_rows, CUtensorMap* out) {
-    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static EncodeFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q{};
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
-        return reinterpret_cast<EncodeFn>(p);
-    }();
-    if (!fn) return fail(B200MOE_ERR_CUDA, "wide form: cuTensorMapEncodeTiled is not available from this driver");
-    static std::mutex m;
-    static std::map<std::tuple<int, const u8*, u64, u64, u32, u32>, CUtensorMap> cache;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const auto key = std::make_tuple(dev, base, row_bytes, rows, S, box_rows);
-    std::lock_guard<std::mutex> lock(m);
-    const auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return B200MOE_OK; }
-    const cuuint64_t dims[2] = {row_bytes / 4, rows};
-    const cuuint64_t strides[1] = {row_bytes};  // bytes between rows: a multiple of 16 (144 per super-block)
-    const cuuint32_t box[2] = {S * (kQ4KBlock / 4), box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<u8*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(B200MOE_ERR_CUDA, "wide form: cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
-    if (cache.size() >= 1024) cache.clear();
-    cache.emplace(key, *out);
-    return B200MOE_OK;
-}
-
 u32 round_up(u32 v, u32 a) { return (v + a - 1) / a * a; }
 
 u32 fixed_smem(const WidePlan& p, bool down) {
@@ -588,8 +474,8 @@ int launch_gate_up_q4k_wide(const b200moe_gate_up_view& v, u32 rows, cudaStream_
     a.row_status = v.row_status; a.summary = v.summary; a.rows_per_expert = v.shape.inter; a.out_width = v.shape.inter;
     CUtensorMap tm0, tm1;
     const u64 rb = u64(p.nb) * kQ4KBlock, total_rows = u64(v.shape.experts) * v.shape.inter;
-    if (int rc = rows_map(v.weights.gate, rb, total_rows, p.S, 32, &tm0)) return rc;
-    if (int rc = rows_map(v.weights.up, rb, total_rows, p.S, 32, &tm1)) return rc;
+    if (int rc = rows_map(v.weights.gate, rb, total_rows, p.S * kQ4KBlock, 32, &tm0)) return rc;
+    if (int rc = rows_map(v.weights.up, rb, total_rows, p.S * kQ4KBlock, 32, &tm1)) return rc;
     const u32 smem = plan_smem(p, false);
     if (p.S == 3) {
         if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(q4k_wide_kernel<false, 3>), smem)) return rc;
@@ -611,7 +497,7 @@ int launch_down_q4k_wide(const b200moe_down_view& v, u32 rows, cudaStream_t stre
     a.routes = v.routes; a.in = v.act; a.raw = v.raw; a.summary = const_cast<u32*>(v.summary);
     a.rows_per_expert = v.shape.hidden; a.out_width = v.shape.hidden;
     CUtensorMap tm0;
-    if (int rc = rows_map(v.weights.down, u64(p.nb) * kQ4KBlock, u64(v.shape.experts) * v.shape.hidden, p.S, 64, &tm0)) return rc;
+    if (int rc = rows_map(v.weights.down, u64(p.nb) * kQ4KBlock, u64(v.shape.experts) * v.shape.hidden, p.S * kQ4KBlock, 64, &tm0)) return rc;
     const u32 smem = plan_smem(p, true);
     if (p.S == 3) {
         if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(q4k_wide_kernel<true, 3>), smem)) return rc;

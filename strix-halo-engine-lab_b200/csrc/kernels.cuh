@@ -49,6 +49,11 @@ bool wide_gate_up_fits(const b200moe_gate_up_view& v, u32 rows);
 bool wide_down_fits(const b200moe_down_view& v, u32 rows);
 int launch_gate_up_q4k_wide(const b200moe_gate_up_view& v, u32 rows, cudaStream_t stream);
 int launch_down_q4k_wide(const b200moe_down_view& v, u32 rows, cudaStream_t stream);
+// gemv_q8_wide.cu: the Q8_0 x A8 lane-class contract in the same streaming skeleton, for windows of many rows.
+bool q8_wide_gate_up_fits(const b200moe_gate_up_view& v, u32 rows);
+bool q8_wide_down_fits(const b200moe_down_view& v, u32 rows);
+int launch_gate_up_q8_wide(const b200moe_gate_up_view& v, u32 rows, cudaStream_t stream);
+int launch_down_q8_wide(const b200moe_down_view& v, u32 rows, cudaStream_t stream);
 // value of a B200MOE_DEBUG_* hook (api.cu)
 u32 debug_value(u32 key);
 

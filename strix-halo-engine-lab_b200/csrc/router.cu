@@ -87,7 +87,10 @@ int launch_router_logits(const b200moe_router_view& v, cudaStream_t stream, cons
     if (v.rows == 1) B200_LOGITS(1, 1);
     else if (v.rows == 2) B200_LOGITS(2, 1);
     else if (v.rows <= 4) B200_LOGITS(4, 1);
-    else if (v.rows <= 16) B200_LOGITS(8, 1);
+    // 8 x 4 tiles read the router matrix a quarter as often, but only pay when they still leave every SM a dozen warps
+    // (token blocks); a 64-row window over 256 experts is 512 such tiles - 3.5 warps per SM, latency bound (117 us
+    // measured against 8 x 1 tiles on the same window)
+    else if (v.rows <= 16 || u64((E + 3) / 4) * ((v.rows + 7) / 8) < 148u * 12u) B200_LOGITS(8, 1);
     else B200_LOGITS(8, 4);
 #undef B200_LOGITS
     return after_launch("router_logits");
