@@ -257,7 +257,8 @@ def test_router_policies(gpu, oracle):
     from b200moe import ops, synth
     rng = np.random.default_rng(13)
     # logits in the declared dot order, every config's router shape
-    for experts, top_k, hidden, rows in ((64, 4, 2048, 1), (128, 8, 2048, 8), (256, 8, 7168, 5), (128, 8, 2048, 37), (32, 2, 96, 3)):
+    for experts, top_k, hidden, rows in ((64, 4, 2048, 1), (128, 8, 2048, 8), (256, 8, 7168, 5), (128, 8, 2048, 37), (32, 2, 96, 3),
+                                        (256, 8, 7168, 64), (40, 3, 1100, 21), (24, 2, 100, 17), (16, 2, 98, 18)):
         x = rng.standard_normal((rows, hidden), dtype=np.float32)
         w = synth.router_weight(rng, experts, hidden)
         lb = synth.zipf_logit_bias(rng, experts)
