@@ -315,7 +315,10 @@ def dense_arm(args, cfg, rank, world, dev):
     start, size = tp.tp_shares(I, world)[rank]
     shape = ops.make_shape(H, size, 1, 1, 12, 12)
     rank_bytes = 3 * (size // 256) * 144 * H                     # gate + up rows of the share, down K-share of every row
-    layers = max(2, min(32, -(-2 * L2_BYTES // rank_bytes) + 1))
+    # shares differ by one super-block when the blocks do not divide: every rank must build the SAME number of layers (each
+    # one hands its window round collectively), so the count comes from rank 0's share, the largest
+    largest = 3 * (tp.tp_shares(I, world)[0][1] // 256) * 144 * H
+    layers = max(2, min(32, -(-2 * L2_BYTES // largest) + 1))
     kernels = []
     for layer in range(layers):
         gate, up, down = synth.expert_tensors(np.random.default_rng(900 + layer), 1, H, I, 12, 12)
