@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(128) router_logits_kernel(const float* __restr
         }
 }
 
-// Windows of more than 16 rows: a CTA owns 8 rows x 16 experts and walks the hidden width in chunks of 512 columns that
+// Windows of more than 4 rows: a CTA owns 8 rows x 16 experts and walks the hidden width in chunks of 512 columns that
 // all 128 threads stage into shared memory with 16-byte asynchronous copies, three chunks in flight; a warp keeps an
 // 8 x 4 tile of lane-class sums. The x tile is then read from HBM / L2 once per 16 experts instead of once per expert (a
 // 64-row window over 256 experts of width 7168 pulled 470 MB through L2 in the form above), and the copies of two chunks
@@ -160,13 +160,13 @@ int launch_router_logits(const b200moe_router_view& v, cudaStream_t stream, cons
     if (v.rows == 1) B200_LOGITS(1, 1);
     else if (v.rows == 2) B200_LOGITS(2, 1);
     else if (v.rows <= 4) B200_LOGITS(4, 1);
-    else if (v.rows <= 16) B200_LOGITS(8, 1);
     else if (aligned(v.x, 16) && aligned(v.weight, 16) && xs % 4 == 0 && v.hidden % 4 == 0) {
         constexpr u32 smem = kTileStages * kTileStageFloats * sizeof(float);
         if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(router_logits_tile_kernel), smem)) return rc;
         router_logits_tile_kernel<<<dim3((E + kTileExperts - 1) / kTileExperts, (v.rows + kTileRows - 1) / kTileRows), 128, smem, stream>>>(
             v.x, xs, v.rows, v.hidden, v.weight, E, v.logit_bias, v.logits);
-    } else B200_LOGITS(8, 4);
+    } else if (v.rows <= 16) B200_LOGITS(8, 1);
+    else B200_LOGITS(8, 4);
 #undef B200_LOGITS
     return after_launch("router_logits");
 }

@@ -66,6 +66,17 @@ __device__ __forceinline__ u32 k_pass(u32 key, const float* c, u32 n, u32 lane, 
     return pick;
 }
 
+// Warp arg-max of (value, id) pairs under the order of beats(); kNone = no candidate. Rolled: these selections run once
+// per step in one warp per row on cold instruction caches, where a fetched line costs more than the instructions in it.
+__device__ __forceinline__ void warp_best(u32 key, u32& pick, float& best) {
+#pragma unroll 1
+    for (int d = 16; d; d >>= 1) {
+        const u32 op = __shfl_xor_sync(0xffffffffu, pick, d);
+        const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+        if (op != kNone && (pick == kNone || beats(key, ob, op, best, pick))) { pick = op; best = ob; }
+    }
+}
+
 // Fast path of one row, one warp: the row's choices live in registers (EPL per lane), no group limit, and no NaN among
 // the choices (then the serial scan of the contract is plain "largest choice, lowest id on ties", so a warp arg-max
 // per pass gives the same picks). Returns false - having written nothing - when the row needs the general path.
@@ -126,13 +137,8 @@ __device__ __forceinline__ bool select_row_fast(const float* logits, float* scor
             const u32 e = lane + 32u * j;
             if (e < E && !((taken >> j) & 1u) && (pick == kNone || beats(p.key, c[j], e, best, pick))) { pick = e; best = c[j]; }
         }
-#pragma unroll
-        for (int d = 16; d; d >>= 1) {
-            const u32 op = __shfl_xor_sync(0xffffffffu, pick, d);
-            const float ob = __shfl_xor_sync(0xffffffffu, best, d);
-            if (op != kNone && (pick == kNone || beats(p.key, ob, op, best, pick))) { pick = op; best = ob; }
-        }
-        if ((pick & 31u) == lane) taken |= 1u << (pick >> 5);
+        warp_best(p.key, pick, best);
+        if (pick != kNone && (pick & 31u) == lane) taken |= 1u << (pick >> 5);
         if (lane == k) my_id = pick;
     }
     if (p.order == B200MOE_ORDER_ASCENDING_ID) {
@@ -155,6 +161,30 @@ __device__ __forceinline__ bool select_row_fast(const float* logits, float* scor
         weights[u64(row) * p.top_k + lane] = __fmul_rn(renorm ? __fdiv_rn(my_s, den) : my_s, p.scale);
     }
     return true;
+}
+
+// Output order, weights and the stores of one row; lane k holds pick k in `my_id`, s[] the scores.
+__device__ __forceinline__ void finish_row(const b200moe_route_policy& p, u32 row, u32 lane, const float* s, u32 my_id,
+                                        u32* __restrict__ ids, float* __restrict__ weights) {
+    if (p.order == B200MOE_ORDER_ASCENDING_ID) {  // rank sort of the (distinct) ids held one per lane
+        u32 rank = 0;
+        for (u32 k = 0; k < p.top_k; ++k) { const u32 o = __shfl_sync(0xffffffffu, my_id, k); rank += (o < my_id) ? 1u : 0u; }
+        u32 sorted = kNone;
+        for (u32 k = 0; k < p.top_k; ++k) {
+            const u32 o = __shfl_sync(0xffffffffu, my_id, k), orank = __shfl_sync(0xffffffffu, rank, k);
+            if (orank == lane) sorted = o;
+        }
+        my_id = sorted;
+    }
+    const float my_s = (lane < p.top_k && my_id != kNone) ? s[my_id] : 0.0f;
+    float sum = 0.0f;  // ((0 + s0) + s1) + ... in output order (route_policy.hpp:121-123)
+    for (u32 k = 0; k < p.top_k; ++k) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_s, k));
+    const bool renorm = p.renormalize && (p.top_k > 1 || p.renorm_single);
+    const float den = __fadd_rn(sum, p.renorm_eps);
+    if (lane < p.top_k) {
+        ids[u64(row) * p.top_k + lane] = my_id;
+        weights[u64(row) * p.top_k + lane] = __fmul_rn(renorm ? __fdiv_rn(my_s, den) : my_s, p.scale);
+    }
 }
 
 // One warp selects one row. `s` points to this warp's scratch of 2 * experts + 32 floats (shared memory).
@@ -192,6 +222,65 @@ __device__ __forceinline__ void select_row(const float* logits, float* scores_ou
     if (scores_out) for (u32 e = lane; e < E; e += 32) scores_out[u64(row) * E + e] = s[e];
 
     u32 allowed = 0xffffffffu, per = E;
+    if (p.n_group > 1 && (E / p.n_group) % 32 == 0 && p.n_group <= 32) {
+        // Groups of whole 32-expert runs and no NaN among the choices: every serial scan of the contract is then "largest
+        // choice, lowest id on ties", which a warp arg-max reproduces; bit j of `live` = this lane's candidate lane + 32 j
+        // is still to be had. Short rolled loops over shared memory keep the code small (see warp_best).
+        per = E / p.n_group;
+        bool bad = false;
+        for (u32 e = lane; e < E; e += 32) bad |= c[e] != c[e];
+        float my_gs = 0.0f;
+        if (!__any_sync(0xffffffffu, bad)) {
+#pragma unroll 1
+            for (u32 g = 0; g < p.n_group; ++g) {
+                u32 i0 = kNone, i1 = kNone;
+                float b0 = 0.0f, b1 = 0.0f;
+#pragma unroll 1
+                for (u32 e = g * per + lane; e < (g + 1) * per; e += 32) { const float v = c[e]; if (i0 == kNone || beats(p.key, v, e, b0, i0)) { i0 = e; b0 = v; } }
+                warp_best(p.key, i0, b0);
+#pragma unroll 1
+                for (u32 e = g * per + lane; e < (g + 1) * per; e += 32) { const float v = c[e]; if (e != i0 && (i1 == kNone || beats(p.key, v, e, b1, i1))) { i1 = e; b1 = v; } }
+                warp_best(p.key, i1, b1);
+                const float v = __fadd_rn(b0, b1);
+                bad |= v != v;
+                if (lane == g) my_gs = v;
+            }
+        }
+        if (!__any_sync(0xffffffffu, bad)) {
+            u32 gmask = 0;
+#pragma unroll 1
+            for (u32 k = 0; k < p.topk_group; ++k) {
+                u32 pick = (lane < p.n_group && !((gmask >> lane) & 1u)) ? lane : kNone;
+                float best = my_gs;
+                warp_best(p.key, pick, best);
+                if (pick != kNone) gmask |= 1u << pick;
+            }
+            const u32 m = per >> 5;
+            u32 live = 0;
+            for (u32 j = 0, g = 0, i = 0; lane + 32u * j < E; ++j) {  // register j belongs to group j / m
+                if ((gmask >> g) & 1u) live |= 1u << j;
+                if (++i == m) { i = 0; ++g; }
+            }
+            u32 my_id = kNone;
+#pragma unroll 1
+            for (u32 k = 0; k < p.top_k; ++k) {
+                u32 pick = kNone;
+                float best = 0.0f;
+#pragma unroll 1
+                for (u32 rest = live; rest; rest &= rest - 1u) {
+                    const u32 e = lane + 32u * (__ffs(rest) - 1u);
+                    const float v = c[e];
+                    if (pick == kNone || beats(p.key, v, e, best, pick)) { pick = e; best = v; }
+                }
+                warp_best(p.key, pick, best);
+                if (pick != kNone && (pick & 31u) == lane) live &= ~(1u << (pick >> 5));
+                if (lane == k) my_id = pick;
+            }
+            finish_row(p, row, lane, s, my_id, ids, weights);
+            return;
+        }
+        per = E;  // a NaN: the serial rules below decide
+    }
     if (p.n_group > 1) {  // group-limited extension (include/b200moe.h): group score = its two best choices summed
         per = E / p.n_group;
         if (lane < p.n_group) {
@@ -215,25 +304,7 @@ __device__ __forceinline__ void select_row(const float* logits, float* scores_ou
         const u32 pick = k_pass(p.key, c, E, lane, taken, allowed, per);
         if (lane == k) my_id = pick;
     }
-    if (p.order == B200MOE_ORDER_ASCENDING_ID) {  // rank sort of the (distinct) ids held one per lane
-        u32 rank = 0;
-        for (u32 k = 0; k < p.top_k; ++k) { const u32 o = __shfl_sync(0xffffffffu, my_id, k); rank += (o < my_id) ? 1u : 0u; }
-        u32 sorted = kNone;
-        for (u32 k = 0; k < p.top_k; ++k) {
-            const u32 o = __shfl_sync(0xffffffffu, my_id, k), orank = __shfl_sync(0xffffffffu, rank, k);
-            if (orank == lane) sorted = o;
-        }
-        my_id = sorted;
-    }
-    const float my_s = (lane < p.top_k && my_id != kNone) ? s[my_id] : 0.0f;
-    float sum = 0.0f;  // ((0 + s0) + s1) + ... in output order (route_policy.hpp:121-123)
-    for (u32 k = 0; k < p.top_k; ++k) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_s, k));
-    const bool renorm = p.renormalize && (p.top_k > 1 || p.renorm_single);
-    const float den = __fadd_rn(sum, p.renorm_eps);
-    if (lane < p.top_k) {
-        ids[u64(row) * p.top_k + lane] = my_id;
-        weights[u64(row) * p.top_k + lane] = __fmul_rn(renorm ? __fdiv_rn(my_s, den) : my_s, p.scale);
-    }
+    finish_row(p, row, lane, s, my_id, ids, weights);
 }
 
 
