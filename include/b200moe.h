@@ -193,7 +193,9 @@ int b200moe_router(const b200moe_router_view* view, void* stream);
  * build_window_routes + restrict_routes (src/ds41_moe.cpp:11-61): experts ascending, entries of an expert in
  * ascending row; slots[i] = row * top_k + k; order[row][k] = the row's slots in ascending expert id;
  * low_counts[row] = how many of them have id < split; counts[0] = union experts, counts[1] = most entries of one
- * expert, counts[2] = entries. Only experts in [first, end) get entries (end 0 = all); experts[] holds id - base.
+ * expert, counts[2] = entries, counts[3] = 0: a scratch word of the expert kernels (they deal their work items out through
+ * it and leave it zero; routes built by other means must provide it zeroed, and two launches that run at the same time
+ * must not share one routes object). Only experts in [first, end) get entries (end 0 = all); experts[] holds id - base.
  * Sizes: rows * top_k for experts / rows / slots / order, + 1 for begins, rows for low_counts, 4 for counts. */
 typedef struct b200moe_routes {
     uint32_t* experts;

@@ -187,6 +187,7 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
     u32 n_union = a.routes.counts[0];
     if (n_union == 0) return;
     if (n_union > plan.max_union) n_union = plan.max_union;
+    u32* claim = a.routes.counts + 3;  // the grid's claim word (wide_common.cuh)
 
     unsigned char* at = smem + kGroups * plan.stages * plan.stage_bytes;
     float* s_gu = reinterpret_cast<float*>(at);  // [group][buffer][gate | up][entry][32]
@@ -201,7 +202,7 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
     at += (2 * kGroups * plan.stages + kGroups) * 8;
     u32* slot_item = reinterpret_cast<u32*>(at);
     at += kGroups * plan.stages * 4;
-    u32* ctl = reinterpret_cast<u32*>(at);  // [0] abort flag, [1] next local item, [2] first item, [3] items of this CTA
+    u32* ctl = reinterpret_cast<u32*>(at);  // [0] abort flag, [1] producers that have retired, [2] virtual experts, [3] items
     volatile u32* abort_flag = ctl;
 
     const u32 tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -212,8 +213,8 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
 
     // ---- the virtual expert list (the stage area is free until the first copy is issued: it holds the copied routes)
     build_work_list(a.routes, n_union, plan.max_union, plan.vmax, plan.n_chunks, reinterpret_cast<u32*>(smem), table, ctl);
-    const u32 first_item = ctl[2], n_local = ctl[3];
-    if (n_local == 0) return;
+    const u32 n_items = ctl[3];
+    if (n_items == 0) return;  // every CTA alike: nobody claims, the claim word stays zero
 
     // ------------------------------------------------------------------------------------------ producer warps
     if (warp >= kConsumerWarps) {
@@ -225,13 +226,18 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
         const u32 e = lane / 3u, part = lane - 3u * e;  // lanes 0 .. 3 * ne - 1 copy one piece of one entry each
         const u32 in_stride = a.in.stride ? a.in.stride : a.in.width, in_gs = in_stride / 32;
         u32 t = 0, slot = 0, use = 0;  // stage count, ring position, lap
-        bool ok = true;
+        bool ok = true, first = true;
         for (;;) {
-            u32 k = 0;
-            if (lane == 0) k = atomicAdd(&ctl[1], 1u);
-            k = __shfl_sync(0xffffffffu, k, 0);
-            const bool end = k >= n_local;
-            const u32 item = first_item + k;
+            // A group's first item needs no round trip: group 0 of CTA b takes item b, group 1 item gridDim.x + b - so a
+            // launch with fewer items than groups runs one group per SM, which has the SM's issue slots to itself.
+            u32 k = g * gridDim.x + blockIdx.x;
+            if (!first) {
+                if (lane == 0) k = gridDim.x * kGroups + claim_item(claim);
+                k = __shfl_sync(0xffffffffu, k, 0);
+            }
+            first = false;
+            const bool end = k >= n_items;
+            const u32 item = k;
             VExpert ve{0};
             u32 chunk = 0;
             if (!end) {
@@ -285,6 +291,7 @@ q4k_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
                 for (u32 i = 0; i < (plan.wait_limit >> 4) + 64u; ++i)
                     if (mbar_try_wait(&g_full[n % plan.stages], (n / plan.stages) & 1u)) break;
         }
+        if (lane == 0) retire_claims(claim, ctl);
         return;
     }
 
@@ -428,11 +435,11 @@ bool make_plan(u32 K, u32 n_chunks, u32 max_union, u64 slots, bool down, WidePla
     p->n_chunks = n_chunks;
     p->max_union = max_union;
     p->vmax = max_union + static_cast<u32>(slots / kKE) + 1;
-    if (u64(p->vmax) * n_chunks >= (1ull << 31)) return false;
+    if (u64(p->vmax) * n_chunks + 4096 >= kClaimMask) return false;  // items and the groups' closing claims fit the claim word's count
     for (p->stages = 5; p->stages >= 2; --p->stages)
         if (plan_smem(*p, down) <= kSmemBudget) break;
     if (p->stages < 2) return false;
-    if ((2 * max_union + 2 + p->vmax) * 4 > kGroups * p->stages * p->stage_bytes) return false;  // the copied routes and the cost prefix borrow the stage area
+    if (work_list_scratch_words(max_union, p->vmax) * 4 > kGroups * p->stages * p->stage_bytes) return false;  // the work list is built in the stage area
     p->wait_limit = kDefaultWaitLimit;
     p->stall_stage = 0xffffffffu;
     return true;

@@ -58,6 +58,7 @@ struct Q8Args {
 __device__ __forceinline__ void q8_stage(const unsigned char* w4, u32 nb, u32 ne, u32 lane, const unsigned char* xs, float (*cls)[kKE]) {
     if (lane >= nb) return;
     const u32 w0 = (kQ8Block * lane) >> 2;
+    const u32 sel_scale = (lane & 1u) ? 0x4432u : 0x4410u, sel_quant = (lane & 1u) ? 0x7654u : 0x5432u;
 #pragma unroll 1
     for (u32 t0 = 0; t0 < ne; t0 += kPass) {
         uint4 c0[kPass], c1[kPass];
@@ -72,20 +73,14 @@ __device__ __forceinline__ void q8_stage(const unsigned char* w4, u32 nb, u32 ne
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             const u32* row = reinterpret_cast<const u32*>(w4 + r * kRunBytes);
-            u32 q[8];
-            float scale;
-            if (lane & 1u) {  // block at byte 34 * lane: odd lanes start on a halfword
-                scale = half_bits_to_float(row[w0] >> 16);
+            // The block lies at byte 34 * lane: on a word for even lanes, on a halfword for odd ones. Nine words cover it
+            // either way; a byte permute with a per-lane selector picks scale and quants without a divergent branch.
+            u32 w[9], q[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) q[i] = row[w0 + 1 + i];
-            } else {
-                u32 w[9];
+            for (int i = 0; i < 9; ++i) w[i] = row[w0 + i];
+            const float scale = half_bits_to_float(__byte_perm(w[0], 0u, sel_scale));
 #pragma unroll
-                for (int i = 0; i < 9; ++i) w[i] = row[w0 + i];
-                scale = half_bits_to_float(w[0] & 0xffffu);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) q[i] = __funnelshift_r(w[i], w[i + 1], 16);
-            }
+            for (int i = 0; i < 8; ++i) q[i] = __byte_perm(w[i], w[i + 1], sel_quant);
 #pragma unroll
             for (int t = 0; t < (int)kPass; ++t) {
                 int da = __dp4a((int)q[0], (int)c0[t].x, 0), db = __dp4a((int)q[1], (int)c0[t].y, 0);
@@ -111,6 +106,7 @@ q8_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ 
     u32 n_union = a.routes.counts[0];
     if (n_union == 0) return;
     if (n_union > plan.max_union) n_union = plan.max_union;
+    u32* claim = a.routes.counts + 3;  // the grid's claim word (wide_common.cuh)
 
     unsigned char* at = smem + kGroups * plan.stages * plan.stage_bytes;
     float* s_gu = reinterpret_cast<float*>(at);  // [group][buffer][gate | up][entry][32]
@@ -123,7 +119,7 @@ q8_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ 
     at += (2 * kGroups * plan.stages + kGroups) * 8;
     u32* slot_item = reinterpret_cast<u32*>(at);
     at += kGroups * plan.stages * 4;
-    u32* ctl = reinterpret_cast<u32*>(at);  // [0] abort flag, [1] next local item, [2] first item, [3] items of this CTA
+    u32* ctl = reinterpret_cast<u32*>(at);  // [0] abort flag, [1] producers that have retired, [2] virtual experts, [3] items
     volatile u32* abort_flag = ctl;
 
     const u32 tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -132,8 +128,8 @@ q8_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ 
     if (tid < 4) ctl[tid] = 0;
     if (tid < kGroups * plan.stages + kGroups) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     build_work_list(a.routes, n_union, plan.max_union, plan.vmax, plan.n_chunks, reinterpret_cast<u32*>(smem), table, ctl);
-    const u32 first_item = ctl[2], n_local = ctl[3];
-    if (n_local == 0) return;
+    const u32 n_items = ctl[3];
+    if (n_items == 0) return;  // every CTA alike: nobody claims, the claim word stays zero
     const u32 item_stages = (DOWN ? 1u : 2u) * plan.nruns;
 
     // ------------------------------------------------------------------------------------------ producer warps
@@ -146,13 +142,18 @@ q8_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ 
         const u32 e = lane >> 1, part = lane & 1u;  // lanes 0 .. 2 * ne - 1 copy the codes or the deltas of one entry
         const u32 in_stride = a.in.stride ? a.in.stride : a.in.width, in_gs = in_stride / 32;
         u32 t = 0, slot = 0, use = 0;
-        bool ok = true;
+        bool ok = true, first = true;
         for (;;) {
-            u32 k = 0;
-            if (lane == 0) k = atomicAdd(&ctl[1], 1u);
-            k = __shfl_sync(0xffffffffu, k, 0);
-            const bool end = k >= n_local;
-            const u32 item = first_item + k;
+            // A group's first item needs no round trip: group 0 of CTA b takes item b, group 1 item gridDim.x + b - so a
+            // launch with fewer items than groups runs one group per SM, which has the SM's issue slots to itself.
+            u32 k = g * gridDim.x + blockIdx.x;
+            if (!first) {
+                if (lane == 0) k = gridDim.x * kGroups + claim_item(claim);
+                k = __shfl_sync(0xffffffffu, k, 0);
+            }
+            first = false;
+            const bool end = k >= n_items;
+            const u32 item = k;
             VExpert ve{0};
             u32 chunk = 0;
             if (!end) {
@@ -197,6 +198,7 @@ q8_wide_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ 
                 for (u32 i = 0; i < (plan.wait_limit >> 4) + 64u; ++i)
                     if (mbar_try_wait(&g_full[n % plan.stages], (n / plan.stages) & 1u)) break;
         }
+        if (lane == 0) retire_claims(claim, ctl);
         return;
     }
 
@@ -295,11 +297,11 @@ bool make_plan(u32 K, u32 n_chunks, u32 max_union, u64 slots, bool down, Q8Plan*
     p->n_chunks = n_chunks;
     p->max_union = max_union;
     p->vmax = max_union + static_cast<u32>(slots / kKE) + 1;
-    if (u64(p->vmax) * n_chunks >= (1ull << 31)) return false;
+    if (u64(p->vmax) * n_chunks + 4096 >= kClaimMask) return false;  // items and the groups' closing claims fit the claim word's count
     for (p->stages = 4; p->stages >= 2; --p->stages)
         if (plan_smem(*p, down) <= kSmemBudget) break;
     if (p->stages < 2) return false;
-    if ((2 * max_union + 2 + p->vmax) * 4 > kGroups * p->stages * p->stage_bytes) return false;
+    if (work_list_scratch_words(max_union, p->vmax) * 4 > kGroups * p->stages * p->stage_bytes) return false;  // the work list is built in the stage area
     p->wait_limit = debug_value(B200MOE_DEBUG_WAIT_LIMIT) ? debug_value(B200MOE_DEBUG_WAIT_LIMIT) : kDefaultWaitLimit;
     return true;
 }

@@ -1,5 +1,5 @@
 // Skeleton shared by the segment-streaming kernels (gemv_q4k_wide.cu, gemv_q8_wide.cu): the virtual-expert work list a CTA
-// builds in shared memory from the window routes, the split of that list over the grid by estimated cost, and the host
+// builds in shared memory from the window routes, the claim word through which the grid deals the items out, and the host
 // helper that encodes a tensor map of weight rows. See gemv_q4k_wide.cu for the design.
 #pragma once
 #include <cuda.h>
@@ -18,7 +18,6 @@ constexpr u32 kGroups = 2, kGroupWarps = 8;
 constexpr u32 kConsumerWarps = kGroups * kGroupWarps;
 constexpr u32 kThreads = (kConsumerWarps + kGroups) * 32;  // one producer warp per group
 constexpr u32 kEndItem = 0xffffffffu;
-constexpr u32 kCostFixed = 4, kCostEntry = 3;           // estimated cost of an item: fixed + per entry
 constexpr u32 kSmemBudget = 227u * 1024u;
 constexpr u32 kDefaultWaitLimit = 1u << 22;
 
@@ -35,63 +34,72 @@ __device__ __forceinline__ u32 warp_inclusive_scan(u32 v, u32 lane) {
     for (int d = 1; d < 32; d <<= 1) { const u32 o = __shfl_up_sync(0xffffffffu, v, d); if (lane >= (u32)d) v += o; }
     return v;
 }
-__device__ __forceinline__ u32 virtual_cost(u32 ne) { return kCostFixed + kCostEntry * ne; }
-
-// First item whose cumulative cost start is >= B (items: virtual expert major, chunks ascending; an item of virtual
-// expert jv costs virtual_cost(ne) and starts at cum[jv] * nc + chunk * cost). B >= total * nc gives n_virtual * nc.
-__device__ inline u32 item_at(const VExpert* table, const u32* cum, u32 n_virtual, u32 nc, u64 total_items_cost, u64 B) {
-    if (B >= total_items_cost) return n_virtual * nc;
-    u32 lo = 0, hi = n_virtual - 1;  // last jv with cum[jv] * nc <= B
-    while (lo < hi) {
-        const u32 mid = (lo + hi + 1) >> 1;
-        if (u64(cum[mid]) * nc <= B) lo = mid; else hi = mid - 1;
-    }
-    const u32 c = virtual_cost(table[lo].ne());
-    const u64 excl = u64(cum[lo]) * nc;
-    return lo * nc + static_cast<u32>((B - excl + c - 1) / c);
+// ---- the grid's claim word -------------------------------------------------------------------------------------------
+// Items are dealt to the groups of all CTAs through ONE word of device memory, routes.counts[3] (zero between launches: the
+// routes builders write 0, and a launch leaves 0 behind): bits 0..21 count the claims, bits 22..31 the CTAs that have made
+// their last claim. The CTA that retires last puts the word back to zero, so the next launch (a graph replay included)
+// needs no memset. Why not a fixed share per CTA: the time of an item depends on its entries in a way a cost estimate only
+// approximates, and with a dozen items per group a mis-estimate leaves SMs idle for the last tenth of the kernel.
+constexpr u32 kClaimBits = 22, kClaimMask = (1u << kClaimBits) - 1u;
+__host__ __device__ constexpr u32 work_list_scratch_words(u32 max_union, u32 vmax) { return 2 * max_union + 2 + vmax + kKE; }
+__device__ __forceinline__ u32 claim_item(u32* claim) { return atomicAdd(claim, 1u) & kClaimMask; }
+// Called once per producer warp (lane 0) when it will claim no more; ctl[1] counts the CTA's producers that have finished.
+__device__ __forceinline__ void retire_claims(u32* claim, u32* ctl) {
+    if (atomicAdd(&ctl[1], 1u) != kGroups - 1u) return;
+    const u32 before = atomicAdd(claim, 1u << kClaimBits);
+    if ((before >> kClaimBits) == gridDim.x - 1u) atomicExch(claim, 0u);
 }
 
-// Builds the CTA's work list: `table` gets the virtual experts (an expert of the union with at most kKE of its entries; an
-// expert with more entries appears several times), ctl[2] / ctl[3] the first item and the item count of this CTA's run
-// (items = virtual expert major x n_chunks chunks, split over the grid by cumulative cost). `scratch` is shared memory that
-// is free until the first copy is issued ((2 * max_union + 2 + vmax) words). Every thread of the block calls it; it holds two
-// block barriers. n_union <= max_union.
+// Builds the work list: `table` gets the virtual experts (an expert of the union with at most kKE of its entries; an expert
+// with more entries appears several times) ORDERED BY ENTRIES, most first (stable within a count): items are claimed in
+// table order, so the long items start first and the kernel's tail is made of short ones. ctl[3] = items (virtual expert
+// major x n_chunks chunks). Every CTA builds the same list. `scratch` is shared memory that is free until the first copy is
+// issued (work_list_scratch_words(max_union, vmax) words). Every thread of the block calls it; it holds four block barriers.
+// n_union <= max_union.
 __device__ __forceinline__ void build_work_list(const b200moe_routes& routes, u32 n_union, u32 max_union, u32 vmax, u32 n_chunks, u32* scratch,
                                                 VExpert* table, u32* ctl) {
     const u32 tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     u32* t_beg = scratch;
     u32* t_exp = t_beg + max_union + 1;
-    u32* t_cum = t_exp + max_union;  // exclusive cost prefix of every virtual expert: only the work split reads it
+    VExpert* unsorted = reinterpret_cast<VExpert*>(t_exp + max_union);
+    u32* s_hist = reinterpret_cast<u32*>(unsorted + vmax);
     for (u32 j = tid; j <= n_union; j += blockDim.x) {
         t_beg[j] = __ldg(routes.begins + j);
         if (j < n_union) t_exp[j] = __ldg(routes.experts + j);
     }
     __syncthreads();
     if (warp == 0) {
-        u32 n_virtual = 0, total = 0;
+        u32 n_virtual = 0;
         for (u32 j0 = 0; j0 < n_union; j0 += 32) {
             const u32 j = j0 + lane;
             const u32 eb = j < n_union ? t_beg[j] : 0u, ne = j < n_union ? t_beg[j + 1] - eb : 0u;
-            const u32 nv = (ne + kKE - 1) / kKE, cost = nv * kCostFixed + ne * kCostEntry;
-            const u32 iv = warp_inclusive_scan(nv, lane), ic = warp_inclusive_scan(cost, lane);
-            u32 pos = n_virtual + iv - nv, cum = total + ic - cost;
-            for (u32 k = 0; k < nv && pos < vmax; ++k, ++pos) {
-                const u32 part = min(kKE, ne - k * kKE);
-                table[pos] = VExpert::make(t_exp[j], eb + k * kKE, part);
-                t_cum[pos] = cum;
-                cum += virtual_cost(part);
-            }
+            const u32 nv = (ne + kKE - 1) / kKE;
+            const u32 iv = warp_inclusive_scan(nv, lane);
+            u32 pos = n_virtual + iv - nv;
+            for (u32 k = 0; k < nv && pos < vmax; ++k, ++pos) unsorted[pos] = VExpert::make(t_exp[j], eb + k * kKE, min(kKE, ne - k * kKE));
             n_virtual += __shfl_sync(0xffffffffu, iv, 31);
-            total += __shfl_sync(0xffffffffu, ic, 31);
         }
         if (n_virtual > vmax) n_virtual = vmax;
-        __syncwarp();
-        if (lane == 0) {
-            const u64 all = u64(total) * n_chunks;
-            const u32 lo = item_at(table, t_cum, n_virtual, n_chunks, all, all * blockIdx.x / gridDim.x);
-            const u32 hi = item_at(table, t_cum, n_virtual, n_chunks, all, all * (blockIdx.x + 1) / gridDim.x);
-            ctl[2] = lo;
-            ctl[3] = hi - lo;
+        if (lane == 0) { ctl[2] = n_virtual; ctl[3] = n_virtual * n_chunks; }
+    }
+    __syncthreads();
+    // counting sort by entries, descending: warp b places the virtual experts of kKE - b entries
+    const u32 n_virtual = ctl[2];
+    const u32 want = kKE - warp;
+    if (warp < kKE) {
+        u32 n = 0;
+        for (u32 i0 = 0; i0 < n_virtual; i0 += 32) n += __popc(__ballot_sync(0xffffffffu, i0 + lane < n_virtual && unsorted[i0 + lane].ne() == want));
+        if (lane == 0) s_hist[warp] = n;
+    }
+    __syncthreads();
+    if (warp < kKE) {
+        u32 pos = 0;
+        for (u32 b = 0; b < warp; ++b) pos += s_hist[b];
+        for (u32 i0 = 0; i0 < n_virtual; i0 += 32) {
+            const bool mine = i0 + lane < n_virtual && unsorted[i0 + lane].ne() == want;
+            const u32 m = __ballot_sync(0xffffffffu, mine);
+            if (mine) table[pos + __popc(m & ((1u << lane) - 1u))] = unsorted[i0 + lane];
+            pos += __popc(m);
         }
     }
     __syncthreads();
