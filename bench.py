@@ -431,6 +431,17 @@ C4_PARTS = 8          # the fold always has 8 expert ranges: 1 GPU and 8 GPUs gi
 C4_GLOBAL_BATCH = 64
 
 
+def gate_up_kernel_name(cfg, rows, form):
+    """The routed gate/up kernel the library picks for a decode window of `rows` rows (csrc/api.cu: pick_decode_form,
+    use_q8_wide), or the one --form forces."""
+    if cfg["gate_type"] != 12:
+        return "q8_wide_kernel<gate/up>" if (form == 2 or (form == 0 and rows >= 8)) else "gate_up_q8_kernel"
+    if form == 3:
+        return "gate_up_q4k_kernel (per-block form)"
+    stream = form == 1 or (form == 0 and rows <= 2 and cfg["hidden"] <= 2048)
+    return "gate_up_q4k_stream_kernel" if stream else "q4k_wide_kernel<gate/up>"
+
+
 def c4_config(cfg, batch, world):
     """The `config` object both arms print (the driver compares them key by key)."""
     return {"workload": f"c4: {cfg['desc']}, decode, global batch {batch}",
@@ -1028,7 +1039,7 @@ def decode_arm(args, cfg, rank, world, dev):
         "e2e": {"value": tokens / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
                 "ms_per_step": host_ms / K},
         "gpu_launches": int(round(launches_per_step * K)),
-        "roofline": {"kernel": "gate_up_q4k_stream_kernel" if cfg["gate_type"] == 12 else "gate_up_q8_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "roofline": {"kernel": gate_up_kernel_name(cfg, B, args.form), "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy",
                      # dram read + write per launch from an ncu capture of this kernel on this workload: 1.00 of the algorithmic bytes
                      "traffic": algo_bytes * NCU_TRAFFIC_RATIO if cfg["gate_type"] == 12 else None,

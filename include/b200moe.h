@@ -75,8 +75,9 @@ uint64_t b200moe_launch_count(void);
 #define B200MOE_DEBUG_WAIT_LIMIT 0u  /* polls of every bounded wait in the streaming kernels; 0 = the default (2^22) */
 #define B200MOE_DEBUG_STALL_STAGE 1u /* n > 0: in every CTA of the segment-streaming kernels the first producer stops feeding
                                       * before its n-th stage (no copy of that stage is issued, none is left in flight); 0 = never */
-#define B200MOE_DEBUG_DECODE_FORM 2u /* Q4_K decode windows: 0 = chosen by the plan, 1 = row streaming, 2 = segment streaming,
-                                      * 3 = per-block (each only where it applies) */
+#define B200MOE_DEBUG_DECODE_FORM 2u /* decode windows: 0 = chosen by the plan, 1 = row streaming (Q4_K), 2 = segment streaming (Q4_K;
+                                      * Q8_0: the dp4a token-block form), 3 = per-block (Q8_0: one row per warp), 4 = the Q8_0
+                                      * tensor-core form (each only where it applies) */
 int b200moe_debug_set(uint32_t key, uint32_t value);
 
 /* ------------------------------------------------------------------------------------------------ A8 activations

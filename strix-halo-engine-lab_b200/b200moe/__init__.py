@@ -16,7 +16,7 @@ TYPE_Q8_0, TYPE_Q4_K = 8, 12
 ROW_INVALID_ROUTE, ROW_NONFINITE_ACTIVATION, ROW_INVALID_DELTA, ROW_PROJECTION_NONFINITE = 1, 2, 4, 8
 JOB_WAIT_ABORTED = 0x40000000
 DEBUG_WAIT_LIMIT, DEBUG_STALL_STAGE, DEBUG_DECODE_FORM = 0, 1, 2
-FORM_AUTO, FORM_ROW_STREAM, FORM_SEGMENT_STREAM, FORM_PER_BLOCK = 0, 1, 2, 3
+FORM_AUTO, FORM_ROW_STREAM, FORM_SEGMENT_STREAM, FORM_PER_BLOCK, FORM_TENSOR = 0, 1, 2, 3, 4
 SCORE_SOFTMAX, SCORE_SIGMOID, SCORE_SQRT_SOFTPLUS = 0, 1, 2
 KEY_FLOAT_SERIAL, KEY_ORDERED_BITS = 0, 1
 ORDER_SELECTION, ORDER_ASCENDING_ID = 0, 1

@@ -229,31 +229,46 @@ bool use_grouped(const b200moe_shape& s, u32 rows, u32 grouped_min_rows, bool ha
     const u32 least = grouped_min_rows ? grouped_min_rows : kGroupedDefaultRows;
     return rows >= least && grouped_fits(s, have_sums);
 }
-// Decode forms of the Q4_K GEMVs: windows of up to kRowStreamRows rows over rows of up to kRowStreamK weights (a ring of
-// whole rows then keeps all sixteen consumer warps fed) take the row-streaming form, everything else the segment-streaming
-// form (any row length), the per-block form being what is left. B200MOE_DEBUG_DECODE_FORM forces one of them where it applies.
-constexpr u32 kRowStreamRows = 8, kRowStreamK = 2048;
+// Decode forms of the Q4_K GEMVs: windows of one or two rows over rows of up to kRowStreamK weights take the row-streaming
+// form (a ring of whole rows, its work split fixed per CTA), everything else the segment-streaming form (any row length;
+// its items are dealt out dynamically), the per-block form being what is left. Measured on B200 at hidden 2048, 128
+// experts, top-8: one row 36.0 against 37.1 us per step, eight rows 76.5 against 70.4 us. B200MOE_DEBUG_DECODE_FORM forces
+// one of them where it applies.
+constexpr u32 kRowStreamRows = 8, kRowStreamMaxRows = 2, kRowStreamK = 2048;
 enum class DecodeForm { row_stream, wide, block };
 DecodeForm pick_decode_form(bool row_stream_fits, bool wide_fits, u32 rows, u32 K) {
     const u32 forced = debug_value(B200MOE_DEBUG_DECODE_FORM);
     if (forced == 1 && row_stream_fits) return DecodeForm::row_stream;
     if (forced == 2 && wide_fits) return DecodeForm::wide;
     if (forced == 3) return DecodeForm::block;
-    if (row_stream_fits && rows <= kRowStreamRows && (K <= kRowStreamK || !wide_fits)) return DecodeForm::row_stream;
+    if (row_stream_fits && ((rows <= kRowStreamMaxRows && K <= kRowStreamK) || (rows <= kRowStreamRows && !wide_fits))) return DecodeForm::row_stream;
     if (wide_fits) return DecodeForm::wide;
     return row_stream_fits ? DecodeForm::row_stream : DecodeForm::block;
 }
-// The DS41 family (Q8_0 x A8): one weight row per warp below kRowStreamRows rows, the token-block form of gemv_q8_wide.cu
-// from there on (a lane there keeps the codes of four entries in registers over four weight rows). Measured on B200: a
-// 7168 x 2048 dense block over 8 rows takes 49 + 18 us in the token-block form against 55 + 30 us; one row over four
-// experts of 2048 x 1024 is 2 us faster in the one-row-per-warp form.
-bool use_q8_wide(bool fits, u32 rows) {
+// The DS41 family (Q8_0 x A8): one weight row per warp below kRowStreamRows rows; from there on the tensor-core form of
+// gemv_q8_mma.cu (rows of 1024 to 7168 weights), else the dp4a token-block form of gemv_q8_wide.cu. Measured on B200: a
+// 7168 x 2048 dense block over 8 rows takes 49 + 18 us in the dp4a token-block form against 55 + 30 us with one row per
+// warp; one row over four experts of 2048 x 1024 is 2 us faster with one row per warp.
+enum class Q8Form { row_per_warp, wide, mma };
+Q8Form pick_q8_form(bool wide_fits, bool mma_fits, u32 rows) {
     const u32 forced = debug_value(B200MOE_DEBUG_DECODE_FORM);
-    if (!fits || forced == 3) return false;
-    return forced == 2 || rows >= kRowStreamRows;
+    if (forced == 3) return Q8Form::row_per_warp;
+    if (forced == 4 && mma_fits) return Q8Form::mma;
+    if (forced == 2 && wide_fits) return Q8Form::wide;
+    if (forced == 0 && rows >= kRowStreamRows) {
+        if (mma_fits) return Q8Form::mma;
+        if (wide_fits) return Q8Form::wide;
+    }
+    return Q8Form::row_per_warp;
 }
 int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
-    if (!is_kquant(v.shape.gate_type)) return use_q8_wide(q8_wide_gate_up_fits(v, rows), rows) ? launch_gate_up_q8_wide(v, rows, st) : launch_gate_up_q8(v, st);
+    if (!is_kquant(v.shape.gate_type)) {
+        switch (pick_q8_form(q8_wide_gate_up_fits(v, rows), q8_mma_gate_up_fits(v, rows), rows)) {
+            case Q8Form::mma: return launch_gate_up_q8_mma(v, rows, st);
+            case Q8Form::wide: return launch_gate_up_q8_wide(v, rows, st);
+            default: return launch_gate_up_q8(v, st);
+        }
+    }
     if (v.shape.gate_type == B200MOE_TYPE_Q5_K) return launch_gate_up_q4k(v, st);  // the per-block form reads both K-quant layouts
     if (use_grouped(v.shape, rows, grouped_min_rows, v.x.sums != nullptr)) return launch_gate_up_q4k_grouped(v, st);
     switch (pick_decode_form(stream_gate_up_fits(v, rows), wide_gate_up_fits(v, rows), rows, v.shape.hidden)) {
@@ -272,7 +287,11 @@ int enqueue_down(const b200moe_down_view& v, u32 rows, cudaStream_t st, u32 grou
         }
     }
     if (is_kquant(v.shape.gate_type)) return launch_down_q8_chain4(v, st);  // chain4: Q8_0 and Q5_1 blocks
-    return use_q8_wide(q8_wide_down_fits(v, rows), rows) ? launch_down_q8_wide(v, rows, st) : launch_down_q8(v, st);
+    switch (pick_q8_form(q8_wide_down_fits(v, rows), q8_mma_down_fits(v, rows), rows)) {
+        case Q8Form::mma: return launch_down_q8_mma(v, rows, st);
+        case Q8Form::wide: return launch_down_q8_wide(v, rows, st);
+        default: return launch_down_q8(v, st);
+    }
 }
 
 }  // namespace

@@ -54,6 +54,11 @@ bool q8_wide_gate_up_fits(const b200moe_gate_up_view& v, u32 rows);
 bool q8_wide_down_fits(const b200moe_down_view& v, u32 rows);
 int launch_gate_up_q8_wide(const b200moe_gate_up_view& v, u32 rows, cudaStream_t stream);
 int launch_down_q8_wide(const b200moe_down_view& v, u32 rows, cudaStream_t stream);
+// gemv_q8_mma.cu: the same contract with the integer dots on the tensor cores (mma.sync s8 x s8), lane classes shared out over the warps.
+bool q8_mma_gate_up_fits(const b200moe_gate_up_view& v, u32 rows);
+bool q8_mma_down_fits(const b200moe_down_view& v, u32 rows);
+int launch_gate_up_q8_mma(const b200moe_gate_up_view& v, u32 rows, cudaStream_t stream);
+int launch_down_q8_mma(const b200moe_down_view& v, u32 rows, cudaStream_t stream);
 // value of a B200MOE_DEBUG_* hook (api.cu)
 u32 debug_value(u32 key);
 

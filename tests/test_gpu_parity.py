@@ -414,15 +414,16 @@ def test_experts_q8_0_ds41_family(gpu, oracle):
     from b200moe import synth
     rng = np.random.default_rng(16)
     for E, H, I, K, rows, limit in ((8, 256, 128, 3, 5, 10.0), (16, 512, 256, 4, 1, math.inf), (6, 2048, 1024, 2, 19, math.inf),
-                                    (4, 1280, 768, 2, 70, 7.0), (3, 256, 1536, 1, 33, math.inf)):
+                                    (4, 1280, 768, 2, 70, 7.0), (3, 256, 1536, 1, 33, math.inf), (2, 2304, 1024, 2, 9, math.inf)):
         gate, up, down = synth.expert_tensors(rng, E, H, I, 8, 8)
         x = rng.standard_normal((rows, H), dtype=np.float32)
         ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
         wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
         shared = rng.standard_normal((rows, H), dtype=np.float32)
         sh, osh = shape_pair(H, I, E, K, 8, 8, limit)
-        # the one-row-per-warp form and the token-block form (where the shape admits it; runs of 32 blocks, the last one partial)
-        for form in (b200moe.FORM_AUTO, b200moe.FORM_SEGMENT_STREAM, b200moe.FORM_PER_BLOCK):
+        # one row per warp, the dp4a token-block form and the tensor-core form (each where the shape admits it; runs of 32
+        # blocks, the last one partial)
+        for form in (b200moe.FORM_AUTO, b200moe.FORM_SEGMENT_STREAM, b200moe.FORM_PER_BLOCK, b200moe.FORM_TENSOR):
             b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, form)
             try:
                 run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_PARTS, shared=shared)
