@@ -599,6 +599,33 @@ int b200moe_residency_table(const void* residency, int32_t* table_host);
 int b200moe_residency_choose_victims(const int32_t* slot_expert, uint32_t slots, const double* score, const uint8_t* used,
                                      uint32_t experts, const uint32_t* missing, uint32_t n_missing, uint32_t* victims);
 
+/* ------------------------------------------------------------------------------------------------ the launch-record seam
+ * The reference dispatches its weight kernels through a registry of {schema, revision, sizeof, alignof, launch} rows and a
+ * checked, typed launch-record envelope instead of an untyped pointer (strix::weight::KernelArguments and
+ * strix::weight::enqueue, include/strix/weight/resolve.hpp:67-76; Registration / enqueue_registered,
+ * src/cuda/weight/registry.hpp:53-65). The same seam over this library's sites: b200moe_registry lists one row per
+ * enqueue entry point, b200moe_enqueue takes an envelope, checks it against the row (known schema, this ABI revision,
+ * bytes == sizeof of the site's view, data aligned for it) before anything is touched, and forwards to the site. */
+enum {
+    B200MOE_SITE_QUANTIZE_A8 = 1, B200MOE_SITE_RMSNORM_A8 = 2, B200MOE_SITE_Q8_0_A8 = 3, B200MOE_SITE_ROUTER = 4,
+    B200MOE_SITE_ROUTES = 5, B200MOE_SITE_ROUTES_STATIC = 6, B200MOE_SITE_GATE_UP = 7, B200MOE_SITE_DOWN = 8,
+    B200MOE_SITE_COMBINE = 9, B200MOE_SITE_LAYER = 10, B200MOE_SITE_FFN = 11, B200MOE_SITE_DENSE_FFN = 12
+};
+typedef struct b200moe_kernel_arguments {
+    uint32_t schema;        /* B200MOE_SITE_* */
+    uint32_t abi_revision;  /* B200MOE_ABI_VERSION the caller was compiled against */
+    const void* data;       /* the site's view */
+    uint64_t bytes;         /* sizeof of that view in the caller's build */
+} b200moe_kernel_arguments;
+typedef struct b200moe_registration {
+    uint32_t schema, revision;
+    uint64_t bytes, alignment;  /* sizeof / alignof of the site's view in this build */
+    const char* name;           /* the entry point's name */
+} b200moe_registration;
+/* Rows of the registry (static storage); returns how many. */
+uint32_t b200moe_registry(const b200moe_registration** rows);
+int b200moe_enqueue(const b200moe_kernel_arguments* arguments, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

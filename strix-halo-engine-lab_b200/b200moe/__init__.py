@@ -160,6 +160,33 @@ class ResidencyStats(C.Structure):
 ABI_VERSION = 3  # B200MOE_ABI_VERSION of include/b200moe.h: the layout of the views mirrored above
 
 # every symbol include/b200moe.h declares (tests check that the library exports each of them)
+class KernelArguments(C.Structure):
+    """The checked launch-record envelope (b200moe_kernel_arguments)."""
+    _fields_ = [("schema", u32), ("abi_revision", u32), ("data", vp), ("bytes", u64)]
+
+
+class Registration(C.Structure):
+    _fields_ = [("schema", u32), ("revision", u32), ("bytes", u64), ("alignment", u64), ("name", C.c_char_p)]
+
+
+(SITE_QUANTIZE_A8, SITE_RMSNORM_A8, SITE_Q8_0_A8, SITE_ROUTER, SITE_ROUTES, SITE_ROUTES_STATIC, SITE_GATE_UP, SITE_DOWN, SITE_COMBINE,
+ SITE_LAYER, SITE_FFN, SITE_DENSE_FFN) = range(1, 13)
+
+
+def registry():
+    """The library's registry rows as {schema: Registration}."""
+    rows = C.POINTER(Registration)()
+    n = lib().b200moe_registry(C.byref(rows))
+    return {rows[i].schema: rows[i] for i in range(n)}
+
+
+def enqueue(schema, view, stream=None, abi_revision=None, nbytes=None):
+    """A site through the launch-record seam: the view travels as a typed, size-checked envelope."""
+    a = KernelArguments(schema, ABI_VERSION if abi_revision is None else abi_revision, C.cast(C.pointer(view), C.c_void_p),
+                        C.sizeof(view) if nbytes is None else nbytes)
+    return lib().b200moe_enqueue(C.byref(a), stream)
+
+
 EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", "b200moe_debug_set", "b200moe_quantize_a8", "b200moe_rmsnorm_a8", "b200moe_q8_0_a8",
            "b200moe_router", "b200moe_routes_scratch_words", "b200moe_build_routes", "b200moe_routes_static_max_words",
            "b200moe_build_routes_static", "b200moe_gate_row_bytes",
@@ -172,7 +199,7 @@ EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", 
            "b200moe_residency_create", "b200moe_residency_destroy", "b200moe_residency_map",
            "b200moe_residency_get_stats", "b200moe_residency_table", "b200moe_residency_choose_victims",
            "b200moe_gguf_tensor_count", "b200moe_gguf_data_offset", "b200moe_gguf_alignment", "b200moe_gguf_tensor_at", "b200moe_gguf_find",
-           "b200moe_gguf_find_moe_layer"]
+           "b200moe_gguf_find_moe_layer", "b200moe_registry", "b200moe_enqueue"]
 
 _lib = None
 

@@ -671,3 +671,55 @@ int b200moe_dense_ffn(const b200moe_dense_view* v, void* stream) {
 }
 
 }  // extern "C"
+
+// ---- the launch-record seam (include/strix/weight/resolve.hpp:67-76, src/cuda/weight/registry.hpp:53-65) ----------------
+namespace {
+using SiteLaunch = int (*)(const void*, void*);
+struct SiteRow { b200moe_registration reg; SiteLaunch launch; };
+template <class View, int (*Fn)(const View*, void*)>
+int site_thunk(const void* view, void* stream) { return Fn(static_cast<const View*>(view), stream); }
+#define B200_SITE(id, View, fn) SiteRow{{id, B200MOE_ABI_VERSION, sizeof(View), alignof(View), #fn}, &site_thunk<View, fn>}
+const SiteRow kSites[] = {
+    B200_SITE(B200MOE_SITE_QUANTIZE_A8, b200moe_quantize_a8_view, b200moe_quantize_a8),
+    B200_SITE(B200MOE_SITE_RMSNORM_A8, b200moe_rmsnorm_view, b200moe_rmsnorm_a8),
+    B200_SITE(B200MOE_SITE_Q8_0_A8, b200moe_q8a8_view, b200moe_q8_0_a8),
+    B200_SITE(B200MOE_SITE_ROUTER, b200moe_router_view, b200moe_router),
+    B200_SITE(B200MOE_SITE_ROUTES, b200moe_routes_view, b200moe_build_routes),
+    B200_SITE(B200MOE_SITE_ROUTES_STATIC, b200moe_routes_view, b200moe_build_routes_static),
+    B200_SITE(B200MOE_SITE_GATE_UP, b200moe_gate_up_view, b200moe_gate_up),
+    B200_SITE(B200MOE_SITE_DOWN, b200moe_down_view, b200moe_down),
+    B200_SITE(B200MOE_SITE_COMBINE, b200moe_combine_view, b200moe_combine),
+    B200_SITE(B200MOE_SITE_LAYER, b200moe_layer_view, b200moe_layer),
+    B200_SITE(B200MOE_SITE_FFN, b200moe_ffn_view, b200moe_ffn),
+    B200_SITE(B200MOE_SITE_DENSE_FFN, b200moe_dense_view, b200moe_dense_ffn),
+};
+#undef B200_SITE
+constexpr uint32_t kSiteCount = sizeof(kSites) / sizeof(kSites[0]);
+}  // namespace
+
+extern "C" {
+
+uint32_t b200moe_registry(const b200moe_registration** rows) {
+    static b200moe_registration table[kSiteCount];
+    static const bool filled = [] { for (uint32_t i = 0; i < kSiteCount; ++i) table[i] = kSites[i].reg; return true; }();
+    (void)filled;
+    if (rows) *rows = table;
+    return kSiteCount;
+}
+
+int b200moe_enqueue(const b200moe_kernel_arguments* a, void* stream) {
+    B200_REQUIRE(a, "enqueue: null launch record");
+    for (const SiteRow& row : kSites) {
+        if (row.reg.schema != a->schema) continue;
+        B200_REQUIRE(a->abi_revision == row.reg.revision, "enqueue(%s): launch record of ABI revision %u, this build is revision %u", row.reg.name,
+                     a->abi_revision, row.reg.revision);
+        B200_REQUIRE(a->bytes == row.reg.bytes, "enqueue(%s): launch record of %llu bytes, the view has %llu", row.reg.name, (unsigned long long)a->bytes,
+                     (unsigned long long)row.reg.bytes);
+        B200_REQUIRE(a->data && reinterpret_cast<uintptr_t>(a->data) % row.reg.alignment == 0, "enqueue(%s): the view is null or not aligned to %llu bytes",
+                     row.reg.name, (unsigned long long)row.reg.alignment);
+        return row.launch(a->data, stream);
+    }
+    return fail(B200MOE_ERR_INVALID_ARGUMENT, "enqueue: unknown schema %u", a->schema);
+}
+
+}  // extern "C"

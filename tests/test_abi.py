@@ -45,7 +45,8 @@ def test_struct_layouts(tmp_path):
              "b200moe_layer_view": b200moe.LayerView, "b200moe_ffn_view": b200moe.FfnView,
              "b200moe_dense_view": b200moe.DenseView, "b200moe_rmsnorm_view": b200moe.RmsnormView,
              "b200moe_residency_desc": b200moe.ResidencyDesc, "b200moe_residency_stats": b200moe.ResidencyStats,
-             "b200moe_gguf_tensor_info": b200moe.GgufTensorInfo, "b200moe_gguf_moe_layer": b200moe.GgufMoeLayer}
+             "b200moe_gguf_tensor_info": b200moe.GgufTensorInfo, "b200moe_gguf_moe_layer": b200moe.GgufMoeLayer,
+             "b200moe_kernel_arguments": b200moe.KernelArguments, "b200moe_registration": b200moe.Registration}
     src = tmp_path / "sizes.c"
     body = "\n".join(f'    printf("{n} %zu\\n", sizeof({n}));' for n in names)
     src.write_text(f'#include <stdio.h>\n#include "{HEADER}"\nint main(void) {{\n{body}\n    return 0;\n}}\n')
@@ -87,6 +88,28 @@ def test_argument_errors_come_first(lib):
     assert lib.b200moe_layer(lv, None) == b200moe.ERR_INVALID_ARGUMENT and b"capacity" in lib.b200moe_last_error()
 
 
+def test_registry_rows_and_envelope_checks(lib):
+    """The launch-record seam: one registry row per enqueue site whose size equals the ctypes mirror of its view, and an
+    envelope with the wrong schema, revision or size is refused before the site sees it."""
+    import b200moe
+    views = {b200moe.SITE_QUANTIZE_A8: b200moe.QuantizeA8View, b200moe.SITE_RMSNORM_A8: b200moe.RmsnormView, b200moe.SITE_Q8_0_A8: b200moe.Q8A8View,
+             b200moe.SITE_ROUTER: b200moe.RouterView, b200moe.SITE_ROUTES: b200moe.RoutesView, b200moe.SITE_ROUTES_STATIC: b200moe.RoutesView,
+             b200moe.SITE_GATE_UP: b200moe.GateUpView, b200moe.SITE_DOWN: b200moe.DownView, b200moe.SITE_COMBINE: b200moe.CombineView,
+             b200moe.SITE_LAYER: b200moe.LayerView, b200moe.SITE_FFN: b200moe.FfnView, b200moe.SITE_DENSE_FFN: b200moe.DenseView}
+    rows = b200moe.registry()
+    assert set(rows) == set(views)
+    for schema, view in views.items():
+        assert rows[schema].revision == b200moe.ABI_VERSION and rows[schema].bytes == C.sizeof(view), rows[schema].name
+        assert rows[schema].alignment == C.alignment(view) and rows[schema].name.startswith(b"b200moe_")
+    v = b200moe.QuantizeA8View(1, 1, 31, 31, 0, b200moe.A8Rows(1, 1, 1, 1, 31, 32), None)
+    assert b200moe.enqueue(b200moe.SITE_QUANTIZE_A8, v) == b200moe.ERR_INVALID_ARGUMENT and b"multiple of 32" in lib.b200moe_last_error()  # reached the site
+    assert b200moe.enqueue(99, v) == b200moe.ERR_INVALID_ARGUMENT and b"unknown schema" in lib.b200moe_last_error()
+    assert b200moe.enqueue(b200moe.SITE_QUANTIZE_A8, v, abi_revision=b200moe.ABI_VERSION - 1) == b200moe.ERR_INVALID_ARGUMENT
+    assert b"revision" in lib.b200moe_last_error()
+    assert b200moe.enqueue(b200moe.SITE_ROUTER, v) == b200moe.ERR_INVALID_ARGUMENT and b"bytes" in lib.b200moe_last_error()
+    assert lib.b200moe_enqueue(None, None) == b200moe.ERR_INVALID_ARGUMENT
+
+
 def test_no_cpu_fallback(lib):
     """Without a usable sm_100 device a well-formed compute call fails with ERR_CUDA."""
     import torch
@@ -117,7 +140,7 @@ REFERENCE_INCLUDE = os.environ.get("STRIX_REFERENCE_INCLUDE", "/root/reference/i
 
 @pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE_INCLUDE, "strix", "cuda", "ds41_moe.hpp")),
                     reason="the reference checkout is absent: the adapters are compiled against its headers")
-@pytest.mark.parametrize("source,compiler", [("strix_ds41_b200.cpp", "g++"), ("strix_qwen_b200.cpp", "nvcc")])
+@pytest.mark.parametrize("source,compiler", [("strix_ds41_b200.cpp", "g++"), ("strix_qwen_b200.cpp", "nvcc"), ("strix_weight_b200.cpp", "g++")])
 def test_adapters_compile_against_the_reference_headers(tmp_path, source, compiler):
     """adapter/*.cpp re-expose the C ABI under the reference's operator names; compiling them against the reference's
     own headers is what shows that every view maps field for field (types included). The DS41 operator header is plain

@@ -83,6 +83,24 @@ def test_quantize_a8(gpu, oracle):
         assert np.array_equal(host(c), wc) and same(host(d), wd) and np.array_equal(host(s), ws)
 
 
+def test_site_through_the_launch_record_seam(gpu, oracle):
+    """b200moe_enqueue forwards a checked envelope to the site: the A8 quantiser through it equals the oracle."""
+    import ctypes as C
+    import b200moe
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((6, 512), dtype=np.float32)
+    xd = dv(x, gpu)
+    codes = torch.empty((6, 512), dtype=torch.int8, device=gpu)
+    deltas = torch.empty((6, 16), dtype=torch.float32, device=gpu)
+    sums = torch.empty((6, 16), dtype=torch.int32, device=gpu)
+    v = b200moe.QuantizeA8View(b200moe.ptr(xd), 6, 512, 512, 0, b200moe.A8Rows(b200moe.ptr(codes), b200moe.ptr(deltas), b200moe.ptr(sums), 6, 512, 512), None)
+    b200moe.check(b200moe.enqueue(b200moe.SITE_QUANTIZE_A8, v, b200moe.stream_ptr()))
+    wc, wd, ws = oracle.quantize_a8(x)
+    assert np.array_equal(host(codes), wc) and same(host(deltas), wd) and np.array_equal(host(sums), ws)
+    with pytest.raises(b200moe.B200MoeError):
+        b200moe.check(b200moe.enqueue(b200moe.SITE_QUANTIZE_A8, v, b200moe.stream_ptr(), nbytes=C.sizeof(v) - 8))
+
+
 def test_quantize_a8_padding_and_rejection(gpu, oracle):
     """Padded output stride keeps the padding (cpu_backend_host_tests.cpp:119-149); a partial group is rejected with
     every output untouched (:65-92)."""
