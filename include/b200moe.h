@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 3
+#define B200MOE_ABI_VERSION 4
 
 /* Status codes (values follow strix::weight::Error's role, include/strix/weight/types.hpp:35-40). */
 enum {
@@ -598,6 +598,46 @@ int b200moe_residency_table(const void* residency, int32_t* table_host);
  * expert ascending). B200MOE_ERR_WORKSPACE when there are fewer such slots than missing experts (nothing written). */
 int b200moe_residency_choose_victims(const int32_t* slot_expert, uint32_t slots, const double* score, const uint8_t* used,
                                      uint32_t experts, const uint32_t* missing, uint32_t n_missing, uint32_t* victims);
+
+/* ------------------------------------------------------------------------------------------------ residency planner
+ * Which experts to bring into HBM slots AHEAD of need, under an upload budget per step: the host-side planner of
+ * strix::residency::Planner (include/strix/residency/expert_residency.hpp:102-147). Pure host code (no CUDA call).
+ * seed (optional prior) -> fill_from_seed (initial residency) -> per step: observe(layer, ids) ..., end_step, plan -> for
+ * every move the caller copies the expert into the slot (b200moe_residency_promote) and commits it. plan() is a pure
+ * function of the state: twice without a commit gives the same moves. */
+#define B200MOE_MOVE_NO_EVICTION 0xffffffffu
+typedef struct b200moe_planner_desc {
+    uint32_t layers, experts, top_k, slots;  /* slots per layer */
+    const uint64_t* expert_bytes;            /* [layers]: bytes of one expert (gate + up + down) of the layer */
+    double decay;                            /* 0 = 0.97 */
+    double margin_reuses;                    /* 0 = 1.5: a candidate replaces a victim only if its score leads by more */
+    uint64_t upload_bytes_per_step;          /* 0 = 64 MiB; one expert larger than the budget may still move alone */
+} b200moe_planner_desc;
+typedef struct b200moe_move {
+    uint32_t layer, slot;
+    uint32_t evict;   /* the expert leaving the slot, or B200MOE_MOVE_NO_EVICTION */
+    uint32_t expert;  /* the expert moving in */
+} b200moe_move;
+typedef struct b200moe_planner_receipt {
+    uint64_t active_bytes, hit_bytes, promoted_bytes, promotions, evictions, steps;
+} b200moe_planner_receipt;
+int b200moe_planner_create(const b200moe_planner_desc* desc, void** planner);
+void b200moe_planner_destroy(void* planner);
+int b200moe_planner_seed(void* planner, uint32_t layer, const uint32_t* counts);               /* counts [experts] */
+int b200moe_planner_observe(void* planner, uint32_t layer, const uint32_t* ids, uint32_t n);  /* one step's ids, duplicates allowed */
+int b200moe_planner_end_step(void* planner);
+/* moves [capacity] <- the step's moves, *count <- how many there are (more than capacity: enlarge the array and call again). */
+int b200moe_planner_plan(const void* planner, b200moe_move* moves, uint32_t capacity, uint32_t* count);
+int b200moe_planner_commit(void* planner, const b200moe_move* move);
+int b200moe_planner_fill_from_seed(void* planner);
+int b200moe_planner_table(const void* planner, uint32_t layer, int32_t* table);   /* [experts]: slot or -1 */
+int b200moe_planner_scores(const void* planner, uint32_t layer, double* scores);  /* [experts] */
+int b200moe_planner_get_receipt(const void* planner, b200moe_planner_receipt* out);
+/* Applies planner moves of ONE layer to its residency object: copies each move's expert from host memory into the slot on
+ * `stream` (a stream of the caller's choice - a side stream keeps the copies off the compute stream; the caller orders it
+ * before the next b200moe_residency_map, e.g. with an event) and updates the residency's table. Moves whose slot holds an
+ * expert other than `evict`, or whose expert is already resident, are refused before anything is copied. */
+int b200moe_residency_promote(void* residency, const b200moe_move* moves, uint32_t count, void* stream);
 
 /* ------------------------------------------------------------------------------------------------ the launch-record seam
  * The reference dispatches its weight kernels through a registry of {schema, revision, sizeof, alignof, launch} rows and a

@@ -457,6 +457,28 @@ class Ref:
                                              _p(out, f32p))
         return sec, out
 
+    def planner_trace(self, layers, experts, top_k, slots, expert_bytes, decay, margin, budget, ids, seed_counts=None, fill=False, max_moves=256):
+        """The reference's residency planner over a scripted trace (ids [steps][layers][n]); every planned move is committed.
+        Returns (moves per step as lists of (layer, slot, evict, expert), final tables [layers][experts], receipt dict)."""
+        ids = np.ascontiguousarray(ids, np.uint32)
+        steps, _, n = ids.shape
+        eb = np.ascontiguousarray(expert_bytes, np.uint64)
+        moves = np.zeros((steps, max_moves, 4), np.uint32)
+        counts = np.zeros(steps, np.uint32)
+        tables = np.zeros((layers, experts), np.int32)
+        receipt = np.zeros(6, np.uint64)
+        sc = np.ascontiguousarray(seed_counts, np.uint32) if seed_counts is not None else None
+        self.lib.ref_planner_trace.argtypes = [C.c_uint32] * 4 + [C.c_void_p, C.c_double, C.c_double, C.c_uint64, C.c_void_p, C.c_int, C.c_uint32, C.c_void_p,
+                                               C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        rc = self.lib.ref_planner_trace(layers, experts, top_k, slots, eb.ctypes.data, decay, margin, budget, sc.ctypes.data if sc is not None else None,
+                                        int(fill), steps, ids.ctypes.data, n, moves.ctypes.data, max_moves, counts.ctypes.data, tables.ctypes.data, None,
+                                        receipt.ctypes.data)
+        assert rc == 0, f"ref_planner_trace failed ({rc})"
+        assert int(counts.max(initial=0)) <= max_moves
+        per_step = [[tuple(int(v) for v in moves[s, i]) for i in range(int(counts[s]))] for s in range(steps)]
+        keys = ("active_bytes", "hit_bytes", "promoted_bytes", "promotions", "evictions", "steps")
+        return per_step, tables, dict(zip(keys, (int(v) for v in receipt)))
+
     def isa(self):
         """Row-kernel table of the routed-expert executor on this host."""
         return self.lib.ref_expert_isa().decode()

@@ -38,6 +38,7 @@
 #include "strix/moe_a8_down_contract.hpp"
 #include "strix/moe_plan.hpp"
 #include "strix/moe_q4k_a8_contract.hpp"
+#include "strix/residency/expert_residency.hpp"
 
 // src/moe_plan.cpp references this symbol from the GGUF reader (storage planning only, never on the routing path);
 // the reader itself drags in the whole weight library, so the link is closed with an empty answer.
@@ -298,6 +299,48 @@ int ref_combine(u32 form, u32 rows, u32 top_k, u32 width, const float* w, const 
                                 std::span<float>(y, n));
     } catch (const std::invalid_argument&) { return 1; }
     return 0;
+}
+
+// The reference's residency planner (include/strix/residency/expert_residency.hpp:102-147) driven over a scripted trace:
+// optional seed + fill_from_seed, then per step observe(layer, ids) for every layer, end_step, plan (twice: it must not
+// change the state), and commit of every planned move. Outputs: the moves of every step, the final tables and scores,
+// the receipt counters.
+int ref_planner_trace(u32 layers, u32 experts, u32 top_k, u32 slots, const std::uint64_t* expert_bytes, double decay, double margin,
+                      std::uint64_t budget, const u32* seed_counts, int fill, u32 steps, const u32* ids, u32 n_ids, u32* moves_out, u32 max_moves,
+                      u32* move_counts, i32* tables_out, double* scores_out, std::uint64_t* receipt_out) {
+    try {
+        strix::residency::ModelBytes m;
+        m.layers = layers; m.experts = experts; m.top_k = top_k;
+        m.expert_bytes.assign(expert_bytes, expert_bytes + layers);
+        strix::residency::PlannerConfig cfg;
+        cfg.decay = decay; cfg.margin_reuses = margin; cfg.upload_bytes_per_step = budget;
+        strix::residency::Planner planner(m, slots, cfg);
+        if (seed_counts)
+            for (u32 l = 0; l < layers; ++l) planner.seed(l, seed_counts + std::size_t(l) * experts);
+        if (fill) planner.fill_from_seed();
+        for (u32 s = 0; s < steps; ++s) {
+            for (u32 l = 0; l < layers; ++l) planner.observe(l, ids + (std::size_t(s) * layers + l) * n_ids, n_ids);
+            planner.end_step();
+            const auto first = planner.plan(), moves = planner.plan();
+            if (first.size() != moves.size()) return 2;
+            move_counts[s] = static_cast<u32>(moves.size());
+            for (std::size_t i = 0; i < moves.size(); ++i) {
+                if (i < max_moves) {
+                    u32* o = moves_out + (std::size_t(s) * max_moves + i) * 4;
+                    o[0] = moves[i].layer; o[1] = moves[i].slot; o[2] = moves[i].evict; o[3] = moves[i].expert;
+                }
+                planner.commit(moves[i]);
+            }
+        }
+        for (u32 l = 0; l < layers; ++l) std::copy(planner.table(l).begin(), planner.table(l).end(), tables_out + std::size_t(l) * experts);
+        (void)scores_out;  // the scores are private to the reference's class: the moves and tables are what they decide
+        const auto r = planner.receipt();
+        receipt_out[0] = r.active_bytes; receipt_out[1] = r.hit_bytes; receipt_out[2] = r.promoted_bytes;
+        receipt_out[3] = r.promotions; receipt_out[4] = r.evictions; receipt_out[5] = r.steps;
+        return 0;
+    } catch (const std::exception&) {
+        return 1;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------

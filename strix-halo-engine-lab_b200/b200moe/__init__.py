@@ -157,9 +157,25 @@ class ResidencyStats(C.Structure):
     _fields_ = [("windows", u64), ("hits", u64), ("misses", u64), ("evictions", u64), ("bytes_loaded", u64)]
 
 
-ABI_VERSION = 3  # B200MOE_ABI_VERSION of include/b200moe.h: the layout of the views mirrored above
+ABI_VERSION = 4  # B200MOE_ABI_VERSION of include/b200moe.h: the layout of the views mirrored above
 
 # every symbol include/b200moe.h declares (tests check that the library exports each of them)
+class PlannerDesc(C.Structure):
+    _fields_ = [("layers", u32), ("experts", u32), ("top_k", u32), ("slots", u32), ("expert_bytes", vp), ("decay", C.c_double),
+                ("margin_reuses", C.c_double), ("upload_bytes_per_step", u64)]
+
+
+class Move(C.Structure):
+    _fields_ = [("layer", u32), ("slot", u32), ("evict", u32), ("expert", u32)]
+
+
+class PlannerReceipt(C.Structure):
+    _fields_ = [("active_bytes", u64), ("hit_bytes", u64), ("promoted_bytes", u64), ("promotions", u64), ("evictions", u64), ("steps", u64)]
+
+
+MOVE_NO_EVICTION = 0xFFFFFFFF
+
+
 class KernelArguments(C.Structure):
     """The checked launch-record envelope (b200moe_kernel_arguments)."""
     _fields_ = [("schema", u32), ("abi_revision", u32), ("data", vp), ("bytes", u64)]
@@ -199,7 +215,10 @@ EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", 
            "b200moe_residency_create", "b200moe_residency_destroy", "b200moe_residency_map",
            "b200moe_residency_get_stats", "b200moe_residency_table", "b200moe_residency_choose_victims",
            "b200moe_gguf_tensor_count", "b200moe_gguf_data_offset", "b200moe_gguf_alignment", "b200moe_gguf_tensor_at", "b200moe_gguf_find",
-           "b200moe_gguf_find_moe_layer", "b200moe_registry", "b200moe_enqueue"]
+           "b200moe_gguf_find_moe_layer", "b200moe_registry", "b200moe_enqueue",
+           "b200moe_planner_create", "b200moe_planner_destroy", "b200moe_planner_seed", "b200moe_planner_observe", "b200moe_planner_end_step",
+           "b200moe_planner_plan", "b200moe_planner_commit", "b200moe_planner_fill_from_seed", "b200moe_planner_table", "b200moe_planner_scores",
+           "b200moe_planner_get_receipt", "b200moe_residency_promote"]
 
 _lib = None
 

@@ -41,6 +41,14 @@ class ExpertResidency:
         check(lib().b200moe_residency_map(self.handle, ptr(ids), ids.numel(), ptr(out), stream_ptr()))
         return out
 
+    def promote(self, moves, stream=None):
+        """Planner moves of this layer ((layer, slot, evict, expert) tuples): the experts are copied into their slots on
+        `stream` (an int handle; default: the current stream) and the table follows; the caller orders that stream before
+        the next map()."""
+        from . import Move
+        arr = (Move * len(moves))(*[Move(*m) for m in moves])
+        check(lib().b200moe_residency_promote(self.handle, arr, len(moves), stream if stream is not None else stream_ptr()))
+
     def stats(self):
         s = ResidencyStats()
         check(lib().b200moe_residency_get_stats(self.handle, C.byref(s)))
@@ -74,3 +82,73 @@ def choose_victims(slot_expert, score, used, missing):
     p = lambda a: a.ctypes.data_as(C.c_void_p)  # noqa: E731
     check(lib().b200moe_residency_choose_victims(p(slot_expert), len(slot_expert), p(score), p(used), len(score), p(missing), len(missing), p(victims)))
     return victims
+
+
+class Planner:
+    """b200moe_planner_*: which experts to bring into slots ahead of need under an upload budget per step (host code only;
+    the counterpart of strix::residency::Planner, include/strix/residency/expert_residency.hpp:102-147)."""
+
+    def __init__(self, layers, experts, top_k, slots, expert_bytes, decay=0.0, margin_reuses=0.0, upload_bytes_per_step=0):
+        from . import PlannerDesc
+        self.layers, self.experts, self.slots = layers, experts, slots
+        self._bytes = (C.c_uint64 * layers)(*[int(b) for b in expert_bytes])
+        desc = PlannerDesc(layers, experts, top_k, slots, C.cast(self._bytes, C.c_void_p), decay, margin_reuses, upload_bytes_per_step)
+        self.handle = C.c_void_p()
+        check(lib().b200moe_planner_create(C.byref(desc), C.byref(self.handle)))
+
+    def seed(self, layer, counts):
+        a = np.ascontiguousarray(counts, np.uint32)
+        check(lib().b200moe_planner_seed(self.handle, layer, a.ctypes.data_as(C.c_void_p)))
+
+    def observe(self, layer, ids):
+        a = np.ascontiguousarray(ids, np.uint32).reshape(-1)
+        check(lib().b200moe_planner_observe(self.handle, layer, a.ctypes.data_as(C.c_void_p), a.size))
+
+    def end_step(self):
+        check(lib().b200moe_planner_end_step(self.handle))
+
+    def plan(self):
+        """The step's moves as (layer, slot, evict, expert) tuples; evict is MOVE_NO_EVICTION for a free slot."""
+        from . import Move
+        n = C.c_uint32()
+        cap = 64
+        while True:
+            moves = (Move * cap)()
+            check(lib().b200moe_planner_plan(self.handle, moves, cap, C.byref(n)))
+            if n.value <= cap:
+                return [(m.layer, m.slot, m.evict, m.expert) for m in moves[:n.value]]
+            cap = n.value
+
+    def commit(self, move):
+        from . import Move
+        check(lib().b200moe_planner_commit(self.handle, C.byref(Move(*move))))
+
+    def fill_from_seed(self):
+        check(lib().b200moe_planner_fill_from_seed(self.handle))
+
+    def table(self, layer):
+        t = np.zeros(self.experts, np.int32)
+        check(lib().b200moe_planner_table(self.handle, layer, t.ctypes.data_as(C.c_void_p)))
+        return t
+
+    def scores(self, layer):
+        s = np.zeros(self.experts, np.float64)
+        check(lib().b200moe_planner_scores(self.handle, layer, s.ctypes.data_as(C.c_void_p)))
+        return s
+
+    def receipt(self):
+        from . import PlannerReceipt
+        r = PlannerReceipt()
+        check(lib().b200moe_planner_get_receipt(self.handle, C.byref(r)))
+        return {k: int(getattr(r, k)) for k, _ in PlannerReceipt._fields_}
+
+    def close(self):
+        if self.handle:
+            lib().b200moe_planner_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass

@@ -45,6 +45,8 @@ struct Residency {
     u32* marks_dev = nullptr;
     u32* marks_host = nullptr;             // pinned
     i32* table_host = nullptr;             // pinned staging of the table upload
+    i32* promote_host = nullptr;           // pinned staging of the table upload of b200moe_residency_promote
+    cudaEvent_t promote_done = nullptr;    // that upload has left promote_host
     int device = 0;
     double decay = 0.97;
     b200moe_residency_stats stats{};
@@ -110,6 +112,8 @@ int b200moe_residency_create(const b200moe_residency_desc* desc, void** out) {
     if (e == cudaSuccess) e = cudaMalloc(&r->marks_dev, sizeof(u32) * s.experts);
     if (e == cudaSuccess) e = cudaHostAlloc(&r->marks_host, sizeof(u32) * s.experts, cudaHostAllocDefault);
     if (e == cudaSuccess) e = cudaHostAlloc(&r->table_host, sizeof(i32) * s.experts, cudaHostAllocDefault);
+    if (e == cudaSuccess) e = cudaHostAlloc(&r->promote_host, sizeof(i32) * s.experts, cudaHostAllocDefault);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&r->promote_done, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaMemset(r->table_dev, 0xff, sizeof(i32) * s.experts);  // every expert absent (-1)
     if (e != cudaSuccess) {
         const int rc = fail(B200MOE_ERR_CUDA, "residency_create: %s", cudaGetErrorString(e));
@@ -127,6 +131,8 @@ void b200moe_residency_destroy(void* residency) {
     if (r->marks_dev) cudaFree(r->marks_dev);
     if (r->marks_host) cudaFreeHost(r->marks_host);
     if (r->table_host) cudaFreeHost(r->table_host);
+    if (r->promote_host) cudaFreeHost(r->promote_host);
+    if (r->promote_done) cudaEventDestroy(r->promote_done);
     delete r;
 }
 
@@ -195,6 +201,45 @@ int b200moe_residency_map(void* residency, const uint32_t* ids, uint32_t count, 
     if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "residency_map: table upload: %s", cudaGetErrorString(e));
     residency_map_kernel<<<blocks, 256, 0, st>>>(ids, count, r->table_dev, E, slot_ids, nullptr);
     return after_launch("residency_remap");
+}
+
+int b200moe_residency_promote(void* residency, const b200moe_move* moves, uint32_t count, void* stream) {
+    B200_REQUIRE(residency && (moves || !count), "residency_promote: null argument");
+    if (count == 0) return B200MOE_OK;
+    auto* r = static_cast<Residency*>(residency);
+    const u32 E = r->d.shape.experts, S = r->d.slots;
+    // every move is checked against the state the earlier moves leave, before anything is copied
+    std::vector<i32> slot_expert = r->slot_expert, table = r->table;
+    for (u32 i = 0; i < count; ++i) {
+        const b200moe_move& m = moves[i];
+        B200_REQUIRE(m.slot < S && m.expert < E, "residency_promote: move %u names slot %u / expert %u outside %u / %u", i, m.slot, m.expert, S, E);
+        B200_REQUIRE(table[m.expert] < 0, "residency_promote: move %u: expert %u is already resident", i, m.expert);
+        const i32 cur = slot_expert[m.slot];
+        B200_REQUIRE(cur < 0 ? m.evict == B200MOE_MOVE_NO_EVICTION : static_cast<u32>(cur) == m.evict,
+                     "residency_promote: move %u: slot %u holds expert %d, the move expects %d", i, m.slot, cur, static_cast<int>(m.evict));
+        if (cur >= 0) table[cur] = -1;
+        slot_expert[m.slot] = static_cast<i32>(m.expert);
+        table[m.expert] = static_cast<i32>(m.slot);
+    }
+    cudaStream_t st = as_stream(stream);
+    cudaError_t e = cudaEventSynchronize(r->promote_done);  // the previous promotion's table has left the staging buffer
+    for (u32 i = 0; i < count && e == cudaSuccess; ++i) {
+        const u32 x = moves[i].expert, s = moves[i].slot;
+        e = cudaMemcpyAsync(r->d.gate_slots + u64(s) * r->gate_bytes, r->d.gate_host + u64(x) * r->gate_bytes, r->gate_bytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(r->d.up_slots + u64(s) * r->gate_bytes, r->d.up_host + u64(x) * r->gate_bytes, r->gate_bytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(r->d.down_slots + u64(s) * r->down_bytes, r->d.down_host + u64(x) * r->down_bytes, r->down_bytes, cudaMemcpyHostToDevice, st);
+        if (moves[i].evict != B200MOE_MOVE_NO_EVICTION) r->stats.evictions += 1;
+        r->stats.bytes_loaded += 2 * r->gate_bytes + r->down_bytes;
+    }
+    if (e == cudaSuccess) {
+        std::copy(table.begin(), table.end(), r->promote_host);
+        e = cudaMemcpyAsync(r->table_dev, r->promote_host, sizeof(i32) * E, cudaMemcpyHostToDevice, st);
+    }
+    if (e == cudaSuccess) e = cudaEventRecord(r->promote_done, st);
+    if (e != cudaSuccess) return fail(B200MOE_ERR_CUDA, "residency_promote: %s", cudaGetErrorString(e));
+    r->slot_expert.swap(slot_expert);
+    r->table.swap(table);
+    return B200MOE_OK;
 }
 
 }  // extern "C"

@@ -3,7 +3,7 @@ the reference checkout by oracle/Makefile). Run where the reference checkout exi
 
     make -C oracle && python tests/golden/make_golden.py
 
-norm_golden.npz (the RMSNorm in front of the FFN) is written by the same run; `--norm-only` writes just that file; formats_golden.npz (Q5_K / Q5_1 tensors) likewise with `--formats-only`.
+norm_golden.npz (the RMSNorm in front of the FFN) is written by the same run; `--norm-only` writes just that file; formats_golden.npz (Q5_K / Q5_1 tensors) likewise with `--formats-only`, planner_golden.npz (the residency planner's traces) with `--planner-only`.
 The vectors are small seeded cases of every contract on the path; tests/test_oracle_pins.py::test_golden_vectors
 replays them against the restated oracle wherever the reference itself is absent (e.g. on the GPU box).
 """
@@ -116,10 +116,32 @@ def format_vectors():
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+
+def planner_vectors():
+    """planner_golden.npz: the reference Planner's moves, tables and receipt on the traces of tests/test_planner.py."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import test_planner as tp
+    ref = Ref()
+    out = {}
+    for k, case in enumerate(tp.CASES):
+        layers, experts, top_k, slots, eb, decay, margin, budget, steps, n, seeded, _ = case
+        ids, seed_counts = tp.trace_of(case, 100 + k)
+        moves, tables, receipt = ref.planner_trace(layers, experts, top_k, slots, eb, decay, margin, budget, ids, seed_counts, fill=seeded)
+        out[f"moves_{k}"] = np.array([m for step in moves for m in step], np.uint32).reshape(-1, 4)
+        out[f"counts_{k}"] = np.array([len(s) for s in moves])
+        out[f"tables_{k}"] = tables
+        out[f"receipt_{k}"] = np.array(list(receipt.values()), np.uint64)
+    np.savez_compressed(os.path.join(ROOT, "tests", "golden", "planner_golden.npz"), **out)
+    print("planner_golden.npz:", sum(int(v.sum()) for k, v in out.items() if k.startswith("counts_")), "moves")
+
+
 if __name__ == "__main__":
-    if "--norm-only" not in sys.argv and "--formats-only" not in sys.argv:
+    only = [a for a in sys.argv[1:] if a.endswith("-only")]
+    if not only:
         main()
-    if "--formats-only" not in sys.argv:
+    if not only or "--norm-only" in only:
         norm_vectors()
-    if "--norm-only" not in sys.argv:
+    if not only or "--formats-only" in only:
         format_vectors()
+    if not only or "--planner-only" in only:
+        planner_vectors()

@@ -89,3 +89,78 @@ def test_residency_equals_all_resident(gpu, oracle):
         out = res.map(bad).cpu().numpy().view(np.uint32)
         assert out[1] == 0xFFFFFFFF and out[0] == before.max()
         res.close()
+
+
+@pytest.mark.gpu
+def test_planned_promotions_ahead_of_need(gpu, oracle):
+    """The planner's moves applied by b200moe_residency_promote on a side stream: the initial residency comes from a seed,
+    every step's moves stay inside the upload budget, the window after them equals the CPU oracle bit for bit, and windows
+    inside the hot set stop missing once the promotions are in. Moves that contradict the table are refused unchanged."""
+    import torch
+    from oracle import loader as O
+    from b200moe import ops, synth
+    rng = np.random.default_rng(62)
+    E, S, H, I, K, rows = 16, 6, 512, 256, 2, 2
+    gate, up, down = synth.expert_tensors(rng, E, H, I, 12, 12)
+    shape = ops.make_shape(H, I, E, K, 12, 12)
+    expert_bytes = int(b200moe.lib().b200moe_expert_bytes(shape))
+    hosts = [torch.from_numpy(a).pin_memory() for a in (gate, up, down)]
+    res = residency.ExpertResidency(shape, *hosts, slots=S, device=gpu)
+    part = ops.MoeLayer(res.slot_shape, res.gate, res.up, res.down, rows, b200moe.COMBINE_FMA_SLOTS)
+    pl = residency.Planner(1, E, K, S, [expert_bytes], decay=0.9, margin_reuses=0.5, upload_bytes_per_step=2 * expert_bytes)
+    prior = np.zeros(E, np.uint32)
+    prior[[3, 7, 9, 12]] = (40, 30, 20, 10)
+    pl.seed(0, prior)
+    pl.fill_from_seed()
+    side = torch.cuda.Stream(device=gpu)
+    first = [(0, int(s), b200moe.MOVE_NO_EVICTION, int(e)) for e, s in enumerate(pl.table(0)) if s >= 0]
+    res.promote(first, stream=side.cuda_stream)
+    torch.cuda.current_stream().wait_stream(side)
+    assert np.array_equal(res.table(), pl.table(0))
+    hot = np.array([1, 2, 3, 4, 5])
+    late_misses = 0
+    for step in range(16):
+        ids = np.stack([rng.permutation(hot)[:K] for _ in range(rows)]).astype(np.int32)
+        x = rng.standard_normal((rows, H), dtype=np.float32)
+        w = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
+        before = res.stats()["misses"]
+        xa = ops.enqueue_quantize_a8(torch.from_numpy(x).to(gpu))
+        ids_d, w_d = torch.from_numpy(ids).to(gpu), torch.from_numpy(w).to(gpu)
+        y = part(xa, res.map(ids_d), w_d)
+        if step >= 8:
+            late_misses += res.stats()["misses"] - before
+        codes, deltas, sums = oracle.quantize_a8(x)
+        raw = oracle.experts(O.Shape(H, I, E, K, 12, 12, float("inf")), gate, up, down, ids.astype(np.uint32), codes, deltas, sums)["raw"]
+        want = oracle.combine(O.COMBINE_FMA_SLOTS, raw, w, ids.astype(np.uint32))
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), want.view(np.uint32)), step
+        # the planner sees the step, plans inside its budget; the copies run on the side stream, ordered before the next window.
+        # Experts that the demand path loaded meanwhile are resident in the residency object but not in the planner's table:
+        # the planner's table is brought in line first (its commit is the record of a copy that is in).
+        pl.observe(0, ids)
+        pl.end_step()
+        table, mine = res.table(), pl.table(0)
+        for e in range(E):
+            if table[e] >= 0 and mine[e] != table[e]:
+                holder = int(np.where(mine == table[e])[0][0]) if (mine == table[e]).any() else b200moe.MOVE_NO_EVICTION
+                pl.commit((0, int(table[e]), holder, e))
+                mine = pl.table(0)
+        moves = pl.plan()
+        assert len(moves) <= 2
+        side.wait_stream(torch.cuda.current_stream())
+        res.promote(moves, stream=side.cuda_stream)
+        for m in moves:
+            pl.commit(m)
+        torch.cuda.current_stream().wait_stream(side)
+        assert np.array_equal(res.table(), pl.table(0))
+    assert late_misses == 0                       # the hot set is resident: no demand load after the promotions
+    # contradicting moves: refused, nothing changes
+    table = res.table().copy()
+    resident, absent = int(np.argmax(table >= 0)), int(np.argmax(table < 0))
+    for bad in ((0, int(table[resident]), b200moe.MOVE_NO_EVICTION, absent),       # the slot is not free
+                (0, 0, int(np.where(table == 0)[0][0]), resident),                   # the expert is already resident
+                (0, S, b200moe.MOVE_NO_EVICTION, absent)):                           # no such slot
+        with pytest.raises(b200moe.InvalidArgument):
+            res.promote([bad])
+        assert np.array_equal(res.table(), table)
+    res.close()
+    pl.close()
