@@ -1,20 +1,22 @@
 #!/usr/bin/env python
 """Benchmark of the block-quantized MoE FFN hot path on B200.
 
-A step = one MoE layer call (router -> A8 -> routes -> Q4_K gate/up + SwiGLU -> Q4_K down -> combine) over one
-batch of synthetic tokens. Default workload = BASELINE.json configs[1]: hidden 2048, 128 experts, top-8, inter 768,
-Q4_K experts, FP32 N(0,1) activations, batch 8 (the largest of the config's 1 / 4 / 8). Between steps the call
-rotates over several layers' worth of distinct expert weights (well over twice the 126 MB L2), so weight bytes come
-from HBM, not L2.
+Default workload (`--workload c4`): the large routed layer in decode at a FIXED global batch of 64 rows - hidden 7168, 256
+Q4_K routed experts behind a sigmoid + bias, group-limited top-8 router, one Q8_0 shared expert, inter 2048. One GPU holds
+every expert (b200moe_ffn); N GPUs run expert parallelism (b200moe_ep_ffn: 256 / N experts and 64 / N home rows per rank),
+so the total work is the same at every N ("scaling": "strong"). A step reads the realised distinct experts' bytes - about
+2.7 GB, far beyond the 126 MB L2. Other workloads: c1 (Q8_0 decode, batch 1), c2 (Q4_K decode, hidden 2048, batch 1 - 8;
+its batch-8 line is repeated under `extra.c2_b8` of the default run), c3 (Q4_K prefill, 4096 tokens), c5 (dense Q4_K block;
+tensor parallelism at N > 1). Smaller layers rotate over several layers' worth of distinct weights (over twice the L2).
 
 One JSON line on stdout (rank 0):
   value     whole-job tokens/s with inputs resident in HBM, steps replayed from a CUDA graph (device-timed, max over
-            ranks); `ms_per_step` likewise
-  e2e       the same metric through the host-buffer C-ABI call (pinned host activations in, host outputs back,
-            copies and the stream wait inside the timed region)
-  roofline  the dominant kernel (Q4_K gate/up GEMV): algorithmic bytes / its CUDA-event duration, against the
-            measured HBM copy peak
-  cpu_baseline  the reference's own CPU code (oracle/_ref) or the oracle port, on the host cores, bounded sample
+            ranks, repeated until the timed region is at least a quarter of a second); `ms_per_step` likewise
+  e2e       the same metric through the C ABI with pinned host rows in and the result back on the host every step
+  roofline  the dominant kernel (routed Q4_K gate/up GEMV): algorithmic bytes / its CUDA-event duration, against the
+            measured HBM copy peak; `traffic` = DRAM bytes per launch (ncu capture, see the note in the line)
+  parity    one step against the CPU oracle, outside the timed regions
+  cpu_baseline  the reference's own CPU row kernels (oracle/_ref) or the oracle port, on the host cores, bounded sample
 `--impl reference` times that CPU arm alone on the same config and prints the same line shape.
 """
 import argparse
@@ -306,8 +308,9 @@ def prefill_arm(args, cfg, rank, world, dev):
 def dense_arm(args, cfg, rank, world, dev):
     """Config 5: the dense Q4_K FFN block (hidden 5120, inter 17408), `--batch` rows (1..8). One GPU holds the whole
     block; N GPUs run tensor parallelism (b200moe.tp): whole-super-block shares of inter per rank, every rank sees the
-    same rows, the partial sums are all-gathered and folded in rank order. A step = A8 of x + gate/up + SwiGLU + A8 of h +
-    down (+ all-gather + fold). Enough distinct layers are rotated that one rotation exceeds twice the L2."""
+    same rows, the partial sums are exchanged by the library's peer stores and folded in rank order on every rank
+    (b200moe_tp_dense: one C call per step). A step = A8 of x + gate/up + SwiGLU + A8 of h + down (+ exchange + fold).
+    Enough distinct layers are rotated that one rotation exceeds twice the L2."""
     import torch
     import torch.distributed as dist
     import b200moe

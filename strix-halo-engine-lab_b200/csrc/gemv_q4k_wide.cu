@@ -7,14 +7,15 @@
 //
 //  * Work item = (virtual expert, 64 weight rows): 32 gate + 32 up rows of one output group, or 64 down rows. A virtual
 //    expert is an expert of the window's union with at most kKE = 8 of its entries; an expert with more entries appears
-//    several times (its rows are then streamed again, out of L2). Every CTA builds the virtual list in shared memory from
-//    the routes (one warp scan) and takes a contiguous run of items of about equal estimated cost.
+//    several times (its rows are then streamed again, out of L2). Every CTA builds the same virtual list in shared memory
+//    from the routes, ordered by entry count (longest items first); the items are dealt out over the whole grid through a
+//    claim word in device memory (wide_common.cuh).
 //  * A stage = S = 3 super-blocks of the item's 64 rows (one or two tiled TMA copies of 432 bytes x 32 / 64 rows: the rows
 //    lie 432 bytes apart in shared memory, an odd count of 16-byte units, which keeps the 128-bit reads of eight rows
 //    conflict free) PLUS the same K range of the A8 rows of the item's entries (codes, deltas, sums: three bulk copies per
 //    entry), all counted on one mbarrier. The consumers therefore find everything a stage needs in shared memory.
-//  * Two groups of eight consumer warps share a CTA, each with its own ring of stages and its own producer warp; a group
-//    takes the next unclaimed item of the CTA's run (a shared-memory counter), so the groups finish together. Lane =
+//  * Two groups of eight consumer warps share a CTA, each with its own ring of stages and its own producer warp; a group's
+//    producer claims the next item of the grid while its consumers still work on the stages in the ring. Lane =
 //    (pair p, row): a lane walks its row's super-blocks in ascending order across the item's stages, the serial chains
 //    acc_p += pair_p never leave their lane, and (a0 + a1) + (a2 + a3) is two xor-shuffles at the end of the item.
 //  * gate/up: the group meets on an mbarrier once per item and eight warps run SwiGLU + the A8 rule of one entry each.
@@ -24,8 +25,8 @@
 //    bytes, high nibbles left in place as 16 q; the k order inside a group is permuted the same way on both sides, which
 //    an exact integer sum does not see). The accumulator fragment gives lane (entry, t) the dots of rows 2t and 2t + 1,
 //    and the lane runs the same FP32 operation sequence on them with the rows' factors fetched from a per-warp scratch:
-//    the kernel is bound by issue slots (ncu: 76 % issue active at config 4), and this form needs about half the
-//    instructions of the dp4a form at 8 entries. Both forms produce the contract's bits.
+//    the kernel is bound by issue slots (ncu: three quarters of them busy at config 4), and this form needs about half
+//    the instructions of the dp4a form at 8 entries; from 3 or 4 entries on it was measured slower than dp4a. Both forms produce the contract's bits.
 //
 // Every wait is bounded (plan.wait_limit polls): a waiter that runs out raises the CTA's abort flag, every role leaves
 // its loops, the producers wait (bounded) for the copies they still have in flight, B200MOE_JOB_WAIT_ABORTED is set in the

@@ -16,7 +16,9 @@
 //    halfword, as in gemv_q8.cu.
 //  * gate/up: after the up rows the group meets on an mbarrier and eight warps run swiglu_clamped (declared_exp) + the A8
 //    rule of one entry each (src/ds41_moe.cpp:134-146).
-// Waits are bounded as in gemv_q4k_wide.cu (B200MOE_JOB_WAIT_ABORTED).
+// Items are dealt out through the grid's claim word and waits are bounded, both as in gemv_q4k_wide.cu
+// (B200MOE_JOB_WAIT_ABORTED). gemv_q8_mma.cu takes the same windows with the integer dots on the tensor cores and is the
+// library's choice where it applies (rows of 1024 to 7168 weights); this form is what is left: other row lengths.
 //
 // Roofline: the FP32 tail of the contract (convert, scale * delta, product, add per (row, entry, group)) bounds it, not
 // HBM: a 64-row window re-reads the shared expert's 46.8 MB out of L2.
