@@ -599,6 +599,20 @@ int b200moe_residency_table(const void* residency, int32_t* table_host);
 int b200moe_residency_choose_victims(const int32_t* slot_expert, uint32_t slots, const double* score, const uint8_t* used,
                                      uint32_t experts, const uint32_t* missing, uint32_t n_missing, uint32_t* victims);
 
+/* ------------------------------------------------------------------------------------------------ deferred first error
+ * strix::DeferredMoeFirstError (include/strix/deferred_moe_status.hpp:9-28): two words {domain, bits} in device memory
+ * that keep the COMPLETE first non-zero job summary of a stream of layers. The caller enqueues the merge after a layer
+ * with that layer's summary word; a later layer - failed or not - never overwrites the record. The publishers are
+ * serialised by the stream. b200moe_check_first_error reads a HOST copy of the record: B200MOE_OK for {0, 0},
+ * B200MOE_ERR_INVALID_ARGUMENT with the bits named in b200moe_last_error for a recorded failure,
+ * B200MOE_ERR_UNSUPPORTED for a malformed record (check_deferred_moe_status, :30-42). */
+enum { B200MOE_DOMAIN_NONE = 0, B200MOE_DOMAIN_LEGACY = 1, B200MOE_DOMAIN_Q4K_A8 = 2 };
+typedef struct b200moe_first_error {
+    uint32_t domain, bits;
+} b200moe_first_error;
+int b200moe_merge_first_error(b200moe_first_error* record, const uint32_t* summary, uint32_t domain, void* stream);
+int b200moe_check_first_error(const b200moe_first_error* record_host);
+
 /* ------------------------------------------------------------------------------------------------ residency planner
  * Which experts to bring into HBM slots AHEAD of need, under an upload budget per step: the host-side planner of
  * strix::residency::Planner (include/strix/residency/expert_residency.hpp:102-147). Pure host code (no CUDA call).

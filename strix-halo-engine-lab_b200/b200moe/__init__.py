@@ -176,6 +176,14 @@ class PlannerReceipt(C.Structure):
 MOVE_NO_EVICTION = 0xFFFFFFFF
 
 
+class FirstError(C.Structure):
+    """strix::DeferredMoeFirstError: {domain, bits}."""
+    _fields_ = [("domain", u32), ("bits", u32)]
+
+
+DOMAIN_NONE, DOMAIN_LEGACY, DOMAIN_Q4K_A8 = 0, 1, 2
+
+
 class KernelArguments(C.Structure):
     """The checked launch-record envelope (b200moe_kernel_arguments)."""
     _fields_ = [("schema", u32), ("abi_revision", u32), ("data", vp), ("bytes", u64)]
@@ -218,7 +226,7 @@ EXPORTS = ["b200moe_abi_version", "b200moe_last_error", "b200moe_launch_count", 
            "b200moe_gguf_find_moe_layer", "b200moe_registry", "b200moe_enqueue",
            "b200moe_planner_create", "b200moe_planner_destroy", "b200moe_planner_seed", "b200moe_planner_observe", "b200moe_planner_end_step",
            "b200moe_planner_plan", "b200moe_planner_commit", "b200moe_planner_fill_from_seed", "b200moe_planner_table", "b200moe_planner_scores",
-           "b200moe_planner_get_receipt", "b200moe_residency_promote"]
+           "b200moe_planner_get_receipt", "b200moe_residency_promote", "b200moe_merge_first_error", "b200moe_check_first_error"]
 
 _lib = None
 

@@ -723,3 +723,25 @@ int b200moe_enqueue(const b200moe_kernel_arguments* a, void* stream) {
 }
 
 }  // extern "C"
+
+extern "C" {
+
+int b200moe_merge_first_error(b200moe_first_error* record, const uint32_t* summary, uint32_t domain, void* stream) {
+    B200_REQUIRE(record && summary, "merge_first_error: record / summary are null");
+    B200_REQUIRE(domain == B200MOE_DOMAIN_LEGACY || domain == B200MOE_DOMAIN_Q4K_A8, "merge_first_error: domain %u is not one this library publishes", domain);
+    if (!device_ready()) return B200MOE_ERR_CUDA;
+    return launch_merge_first_error(record, summary, domain, as_stream(stream));
+}
+
+int b200moe_check_first_error(const b200moe_first_error* r) {
+    B200_REQUIRE(r, "check_first_error: null record");
+    if (r->domain == B200MOE_DOMAIN_NONE && r->bits == 0) return B200MOE_OK;
+    if (r->domain == B200MOE_DOMAIN_LEGACY && r->bits != 0)
+        return fail(B200MOE_ERR_INVALID_ARGUMENT, "routed experts rejected invalid routes or nonfinite weights (status bits %u)", r->bits);
+    if (r->domain == B200MOE_DOMAIN_Q4K_A8 && r->bits != 0)
+        return fail(B200MOE_ERR_INVALID_ARGUMENT, "Q4K A8 rejected status bits (route/weight=1,input=2,delta=4,pipeline=8%s): %u",
+                    (r->bits & B200MOE_JOB_WAIT_ABORTED) ? ", bounded wait ran out=0x40000000" : "", r->bits);
+    return fail(B200MOE_ERR_UNSUPPORTED, "deferred MoE completion record is malformed (domain %u, bits %u)", r->domain, r->bits);
+}
+
+}  // extern "C"

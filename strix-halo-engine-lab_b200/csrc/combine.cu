@@ -99,8 +99,21 @@ __global__ void __launch_bounds__(256) row_order_kernel(const u32* ids, u32 rows
     for (u32 k = 0; k < top_k; ++k) order[row * top_k + k] = slot[k];
 }
 
+// The complete first non-zero summary stays (include/strix/deferred_moe_status.hpp:19-28); one thread, stream ordered.
+__global__ void merge_first_error_kernel(b200moe_first_error* record, const u32* summary, u32 domain) {
+    const u32 bits = *summary;
+    if (bits != 0u && record->domain == 0u) {
+        record->bits = bits;
+        record->domain = domain;
+    }
+}
+
 }  // namespace
 
+int launch_merge_first_error(b200moe_first_error* record, const u32* summary, u32 domain, cudaStream_t stream) {
+    merge_first_error_kernel<<<1, 1, 0, stream>>>(record, summary, domain);
+    return after_launch("merge_first_error");
+}
 int launch_combine(const b200moe_combine_view& v, cudaStream_t stream) {
     if (v.rows == 0) return B200MOE_OK;
     if (int rc = prefer_max_shared(reinterpret_cast<const void*>(combine_kernel))) return rc;

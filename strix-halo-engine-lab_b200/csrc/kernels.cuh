@@ -68,6 +68,7 @@ int launch_prologue(const b200moe_router_view& r, const b200moe_quantize_a8_view
                     cudaStream_t stream);
 
 // combine.cu
+int launch_merge_first_error(b200moe_first_error* record, const u32* summary, u32 domain, cudaStream_t stream);
 int launch_combine(const b200moe_combine_view& v, cudaStream_t stream);
 int launch_canonical_sum(const float* a, const float* b, const float* c, u64 count, float* y, cudaStream_t stream);
 int launch_fill_u32(u32* p, u32 value, u64 count, cudaStream_t stream);

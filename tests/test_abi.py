@@ -46,7 +46,9 @@ def test_struct_layouts(tmp_path):
              "b200moe_dense_view": b200moe.DenseView, "b200moe_rmsnorm_view": b200moe.RmsnormView,
              "b200moe_residency_desc": b200moe.ResidencyDesc, "b200moe_residency_stats": b200moe.ResidencyStats,
              "b200moe_gguf_tensor_info": b200moe.GgufTensorInfo, "b200moe_gguf_moe_layer": b200moe.GgufMoeLayer,
-             "b200moe_kernel_arguments": b200moe.KernelArguments, "b200moe_registration": b200moe.Registration}
+             "b200moe_kernel_arguments": b200moe.KernelArguments, "b200moe_registration": b200moe.Registration,
+             "b200moe_first_error": b200moe.FirstError, "b200moe_move": b200moe.Move, "b200moe_planner_desc": b200moe.PlannerDesc,
+             "b200moe_planner_receipt": b200moe.PlannerReceipt}
     src = tmp_path / "sizes.c"
     body = "\n".join(f'    printf("{n} %zu\\n", sizeof({n}));' for n in names)
     src.write_text(f'#include <stdio.h>\n#include "{HEADER}"\nint main(void) {{\n{body}\n    return 0;\n}}\n')
@@ -108,6 +110,21 @@ def test_registry_rows_and_envelope_checks(lib):
     assert b"revision" in lib.b200moe_last_error()
     assert b200moe.enqueue(b200moe.SITE_ROUTER, v) == b200moe.ERR_INVALID_ARGUMENT and b"bytes" in lib.b200moe_last_error()
     assert lib.b200moe_enqueue(None, None) == b200moe.ERR_INVALID_ARGUMENT
+
+
+def test_first_error_record_check(lib):
+    """b200moe_check_first_error on host copies of the record: the cases of check_deferred_moe_status
+    (include/strix/deferred_moe_status.hpp:30-42)."""
+    import b200moe
+    assert lib.b200moe_check_first_error(C.byref(b200moe.FirstError(0, 0))) == b200moe.OK
+    assert lib.b200moe_check_first_error(C.byref(b200moe.FirstError(b200moe.DOMAIN_Q4K_A8, 9))) == b200moe.ERR_INVALID_ARGUMENT
+    assert b"route/weight=1" in lib.b200moe_last_error() and b": 9" in lib.b200moe_last_error()
+    assert lib.b200moe_check_first_error(C.byref(b200moe.FirstError(b200moe.DOMAIN_LEGACY, 1))) == b200moe.ERR_INVALID_ARGUMENT
+    assert b"invalid routes" in lib.b200moe_last_error()
+    for malformed in ((0, 5), (b200moe.DOMAIN_Q4K_A8, 0), (7, 1)):
+        assert lib.b200moe_check_first_error(C.byref(b200moe.FirstError(*malformed))) == b200moe.ERR_UNSUPPORTED
+        assert b"malformed" in lib.b200moe_last_error()
+    assert lib.b200moe_merge_first_error(None, None, 2, None) == b200moe.ERR_INVALID_ARGUMENT
 
 
 def test_no_cpu_fallback(lib):

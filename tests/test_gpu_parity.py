@@ -101,6 +101,32 @@ def test_site_through_the_launch_record_seam(gpu, oracle):
         b200moe.check(b200moe.enqueue(b200moe.SITE_QUANTIZE_A8, v, b200moe.stream_ptr(), nbytes=C.sizeof(v) - 8))
 
 
+def test_deferred_first_error_record(gpu):
+    """The record keeps the COMPLETE first non-zero summary of a stream of layers; a clean layer or a later failure never
+    overwrites it (include/strix/deferred_moe_status.hpp:16-28). The summaries are real ones: a window with an id out of
+    range sets INVALID_ROUTE in the routes' row status, folded into the word the merge reads."""
+    import ctypes as C
+    import b200moe
+    from b200moe import ops
+    L = b200moe.lib()
+    record = torch.zeros(2, dtype=torch.int32, device=gpu)
+    clean = torch.zeros(1, dtype=torch.int32, device=gpu)
+    ids = torch.tensor([[0, 1], [2, 900]], dtype=torch.int32, device=gpu)        # 900 >= 8 experts
+    status = torch.zeros(2, dtype=torch.int32, device=gpu)
+    ops.enqueue_moe_routes(ids, 8, 4, row_status=status)
+    first = status.max().reshape(1).contiguous()                                   # the job summary of that window
+    later = torch.tensor([b200moe.ROW_PROJECTION_NONFINITE], dtype=torch.int32, device=gpu)
+    st = b200moe.stream_ptr()
+    for summary, domain in ((clean, b200moe.DOMAIN_Q4K_A8), (first, b200moe.DOMAIN_Q4K_A8), (clean, b200moe.DOMAIN_LEGACY),
+                            (later, b200moe.DOMAIN_LEGACY)):
+        b200moe.check(L.b200moe_merge_first_error(b200moe.ptr(record), b200moe.ptr(summary), domain, st))
+    got = record.cpu().numpy().view(np.uint32)
+    assert int(first.item()) == b200moe.ROW_INVALID_ROUTE and got.tolist() == [b200moe.DOMAIN_Q4K_A8, b200moe.ROW_INVALID_ROUTE]
+    assert L.b200moe_check_first_error(C.byref(b200moe.FirstError(int(got[0]), int(got[1])))) == b200moe.ERR_INVALID_ARGUMENT
+    with pytest.raises(b200moe.B200MoeError):
+        b200moe.check(L.b200moe_merge_first_error(b200moe.ptr(record), b200moe.ptr(clean), 9, st))
+
+
 def test_quantize_a8_padding_and_rejection(gpu, oracle):
     """Padded output stride keeps the padding (cpu_backend_host_tests.cpp:119-149); a partial group is rejected with
     every output untouched (:65-92)."""
