@@ -47,6 +47,8 @@ enum {
 #define B200MOE_TYPE_Q5_1 7u  /* 24-byte blocks {fp16 d, fp16 m, 32 high bits, 16 B nibbles}: down tensors of the Qwen A8 family
                                * (strix::cpu::expert::DownFormat::q5_1, src/cpu/core/routed_expert.hpp:28) */
 #define B200MOE_TYPE_Q8_0 8u  /* 34-byte blocks {fp16 d, int8 q[32]} */
+#define B200MOE_TYPE_Q2_K 10u /* 84-byte super-blocks {16 B of (4-bit scale | 4-bit min << 4) per 16 weights, 64 B of 2-bit quants, fp16 d,
+                              * fp16 dmin}: gate / up / down tensors of the DS41 family (include/strix/ds41_formats.hpp:16-19) */
 #define B200MOE_TYPE_Q4_K 12u /* 144-byte super-blocks {fp16 d, fp16 dmin, 12 B 6-bit scales/mins, 128 B nibbles} */
 #define B200MOE_TYPE_Q5_K 13u /* 176-byte super-blocks {fp16 d, fp16 dmin, 12 B scales/mins, 32 B high bits, 128 B nibbles}: gate / up
                                * tensors (GateFormat::q5_k, routed_expert.hpp:27); the Q4_K row rule with 5-bit quants */

@@ -359,7 +359,8 @@ class Ref:
         r["union"], r["max_rows"] = rc, mx.value
         return r
 
-    def window_q8_0(self, gate, up, down, experts, hidden, inter, limit, x, ids, weights, shared, split, first=0, end=0):
+    def window_ds41(self, gate_type, down_type, gate, up, down, experts, hidden, inter, limit, x, ids, weights, shared, split, first=0, end=0):
+        """reference_window over Q8_0 (8) / Q2_K (10) tensors."""
         x = np.ascontiguousarray(x, np.float32)
         ids = np.ascontiguousarray(ids, np.uint32)
         weights = np.ascontiguousarray(weights, np.float32)
@@ -371,7 +372,7 @@ class Ref:
                    y=np.zeros((rows, hidden), np.float32))
         if shared is None:
             shared = np.zeros((rows, hidden), np.float32)
-        rc = self.lib.ref_window_q8_0(_p(gate, u8p), _p(up, u8p), _p(down, u8p), experts, hidden, inter, C.c_float(limit),
+        rc = self.lib.ref_window_ds41(gate_type, down_type, _p(gate, u8p), _p(up, u8p), _p(down, u8p), experts, hidden, inter, C.c_float(limit),
                                       _p(x, f32p), rows, _p(ids, u32p), _p(weights, f32p), _p(shared, f32p), K, split, first, end,
                                       _p(out["gate"], f32p), _p(out["up"], f32p), _p(out["act_codes"], i8p),
                                       _p(out["act_deltas"], f32p), _p(out["act_sums"], i32p), _p(out["raw"], f32p), _p(out["y"], f32p))
@@ -379,6 +380,9 @@ class Ref:
             raise ValueError("rejected")
         return out
 
+
+    def window_q8_0(self, gate, up, down, experts, hidden, inter, limit, x, ids, weights, shared, split, first=0, end=0):
+        return self.window_ds41(8, 8, gate, up, down, experts, hidden, inter, limit, x, ids, weights, shared, split, first, end)
     def half_sum(self, ids, split, weights, raw, half):
         ids = np.ascontiguousarray(ids, np.uint32)
         rows, K = ids.shape

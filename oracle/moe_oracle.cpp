@@ -93,6 +93,37 @@ float product_q8_0(const u8* row, const i8* codes, const float* deltas, size_t w
     return butterfly32(lanes);
 }
 
+// ---- Q2_K x A8 product, DS41 contract (src/ds41_formats.cpp:106-115 q2_k_group, :198-218 product_q2_k) ---------------
+// 84-byte super-blocks {scales[16], qs[64], fp16 d, fp16 dmin}; group g of a block: half = g / 4, 2-bit codes at bit
+// 2 * (g % 4) of qs[32 * half + l]; its two 16-weight halves carry (scale | min << 4) bytes 8 * half + 2 * (g % 4) + {0, 1}.
+float product_q2_k(const u8* row, const i8* codes, const float* deltas, size_t width) {
+    float lanes[32];
+    for (auto& l : lanes) l = 0.0f;
+    for (size_t g = 0; g < width / 32; ++g) {
+        const u8* blk = row + g / 8 * 84;
+        const unsigned within = (unsigned)(g % 8), half = within / 4, shift = 2 * (within % 4);
+        i32 a = 0, b = 0;
+        for (unsigned h = 0; h < 2; ++h) {
+            i32 qx = 0, sx = 0;
+            for (unsigned j = 16 * h; j < 16 * h + 16; ++j) {
+                const i32 q = (blk[16 + 32 * half + j] >> shift) & 3, x = codes[g * 32 + j];
+                qx += q * x;
+                sx += x;
+            }
+            const u8 sc = blk[8 * half + 2 * (within % 4) + h];
+            a += (i32)(sc & 15) * qx;
+            b += (i32)(sc >> 4) * sx;
+        }
+        const float scaled = half_f(ld16(blk + 80)) * (float)a;
+        const float offset = half_f(ld16(blk + 82)) * (float)b;
+        lanes[g % 32] = lanes[g % 32] + (scaled - offset) * deltas[g];
+    }
+    return butterfly32(lanes);
+}
+inline float product_ds41(u32 type, const u8* row, const i8* codes, const float* deltas, size_t width) {
+    return type == B200MOE_TYPE_Q2_K ? product_q2_k(row, codes, deltas, width) : product_q8_0(row, codes, deltas, width);
+}
+
 // ---- Q4_K 6-bit factors (src/cpu/core/routed_expert.cpp:65-71 == get_scale_min_k4, src/ggml_dequant.cpp:43-50) --
 inline void q4k_factors(const u8* blk, unsigned j, unsigned* sc, unsigned* mn) {
     const u8* p = blk + 4;
@@ -106,6 +137,7 @@ inline size_t row_bytes(u32 type, u32 width) {
         case B200MOE_TYPE_Q8_0: return (size_t)width / 32 * 34;
         case B200MOE_TYPE_Q5_1: return (size_t)width / 32 * 24;
         case B200MOE_TYPE_Q5_K: return (size_t)width / 256 * 176;
+        case B200MOE_TYPE_Q2_K: return (size_t)width / 256 * 84;
         default: return (size_t)width / 256 * 144;
     }
 }
@@ -491,10 +523,12 @@ int orc_experts(const b200moe_shape* sh, const u8* gate, const u8* up, const u8*
     if (end == 0) end = sh->experts;
     const bool q5k = sh->gate_type == B200MOE_TYPE_Q5_K;
     const bool q4k = sh->gate_type == B200MOE_TYPE_Q4_K || q5k;  // the K-quant (Qwen A8) family
-    if (!q4k && sh->gate_type != B200MOE_TYPE_Q8_0) return 1;
-    if (sh->down_type != B200MOE_TYPE_Q4_K && sh->down_type != B200MOE_TYPE_Q8_0 && sh->down_type != B200MOE_TYPE_Q5_1) return 1;
-    if (!q4k && sh->down_type != B200MOE_TYPE_Q8_0) return 1;
-    if (H % (q4k ? 256 : 32) || I % (sh->down_type == B200MOE_TYPE_Q4_K ? 256 : 32)) return 1;
+    const bool g2 = sh->gate_type == B200MOE_TYPE_Q2_K, d2 = sh->down_type == B200MOE_TYPE_Q2_K;
+    if (!q4k && sh->gate_type != B200MOE_TYPE_Q8_0 && !g2) return 1;
+    if (sh->down_type != B200MOE_TYPE_Q4_K && sh->down_type != B200MOE_TYPE_Q8_0 && sh->down_type != B200MOE_TYPE_Q5_1 && !d2) return 1;
+    if (!q4k && sh->down_type != B200MOE_TYPE_Q8_0 && !d2) return 1;
+    if (q4k && d2) return 1;
+    if (H % ((q4k || g2) ? 256 : 32) || I % ((sh->down_type == B200MOE_TYPE_Q4_K || d2) ? 256 : 32)) return 1;
     const size_t grow = row_bytes(sh->gate_type, H), drow = row_bytes(sh->down_type, I);
     const u32 slots = rows * K;
     std::vector<i8> hc((size_t)slots * I);
@@ -513,7 +547,7 @@ int orc_experts(const b200moe_shape* sh, const u8* gate, const u8* up, const u8*
             const u8* ur = up + ((size_t)e * I + o) * grow;
             float g, u;
             if (q4k) { g = row_kquant(gr, H / 256, xc, xd, xs, q5k); u = row_kquant(ur, H / 256, xc, xd, xs, q5k); }
-            else { g = product_q8_0(gr, xc, xd, H); u = product_q8_0(ur, xc, xd, H); }
+            else { g = product_ds41(sh->gate_type, gr, xc, xd, H); u = product_ds41(sh->gate_type, ur, xc, xd, H); }
             if (gate_out) gate_out[(size_t)s * I + o] = g;
             if (up_out) up_out[(size_t)s * I + o] = u;
             h[o] = q4k ? swiglu_qwen(g, u) : swiglu_ds41(g, u, sh->limit);
@@ -542,7 +576,7 @@ int orc_experts(const b200moe_shape* sh, const u8* gate, const u8* up, const u8*
             if (sh->down_type == B200MOE_TYPE_Q4_K) v = row_q4k(dr, I / 256, c, d, sm);
             else if (sh->down_type == B200MOE_TYPE_Q5_1) v = row_q5_1_chain4(dr, I / 32, c, d, sm);
             else if (q4k) v = row_q8_chain4(dr, I / 32, c, d);
-            else v = product_q8_0(dr, c, d, I);
+            else v = product_ds41(sh->down_type, dr, c, d, I);
             raw[(size_t)s * H + o] = v;
         }
     });

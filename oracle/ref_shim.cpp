@@ -195,16 +195,20 @@ int ref_window_routes(const u32* ids, u32 rows, u32 top_k, u32 split, u32 first,
 
 // strix::ds41::reference_window with Q8_0 tensors (src/ds41_moe.cpp:124-165). x: FP32 rows quantised with
 // ds41::quantize_a8. Outputs: gate / up [slot][inter], act codes [slot][inter] / deltas / sums, raw [slot][hidden], y.
-int ref_window_q8_0(const u8* gate, const u8* up, const u8* down, u32 experts, u32 hidden, u32 inter, float limit, const float* x,
-                    u32 rows, const u32* ids, const float* weights, const float* shared, u32 top_k, u32 split, u32 first, u32 end,
+// gate_type / down_type: ggml type ids 8 (Q8_0) or 10 (Q2_K), the two block types of the family that this build binds.
+int ref_window_ds41(u32 gate_type, u32 down_type, const u8* gate, const u8* up, const u8* down, u32 experts, u32 hidden, u32 inter, float limit,
+                    const float* x, u32 rows, const u32* ids, const float* weights, const float* shared, u32 top_k, u32 split, u32 first, u32 end,
                     float* gate_out, float* up_out, i8* act_codes, float* act_deltas, i32* act_sums, float* raw, float* y) {
     try {
+        const auto format_of = [](u32 t) { return t == 10 ? strix::ds41::WeightFormat::q2_k : strix::ds41::WeightFormat::q8_0; };
+        const auto row_bytes = [](u32 t, u32 width) { return t == 10 ? std::size_t(width / 256) * 84 : std::size_t(width / 32) * 34; };
         strix::ds41::ExpertTensors t;
-        t.gate_up_format = t.down_format = strix::ds41::WeightFormat::q8_0;
+        t.gate_up_format = format_of(gate_type);
+        t.down_format = format_of(down_type);
         t.hidden = hidden; t.inter = inter; t.limit = limit;
-        t.gate = std::span<const u8>(gate, (std::size_t)experts * inter * (hidden / 32 * 34));
+        t.gate = std::span<const u8>(gate, (std::size_t)experts * inter * row_bytes(gate_type, hidden));
         t.up = std::span<const u8>(up, t.gate.size());
-        t.down = std::span<const u8>(down, (std::size_t)experts * hidden * (inter / 32 * 34));
+        t.down = std::span<const u8>(down, (std::size_t)experts * hidden * row_bytes(down_type, inter));
         std::vector<strix::ds41::A8Activation> xa;
         for (u32 r = 0; r < rows; ++r) xa.push_back(strix::ds41::quantize_a8(std::span<const float>(x + (std::size_t)r * hidden, hidden)));
         auto routes = strix::ds41::build_window_routes(std::span<const u32>(ids, (std::size_t)rows * top_k), rows, top_k, split);
@@ -224,6 +228,12 @@ int ref_window_q8_0(const u8* gate, const u8* up, const u8* down, u32 experts, u
         if (y) std::memcpy(y, out.y.data(), (std::size_t)rows * hidden * 4);
     } catch (const std::invalid_argument&) { return 1; }
     return 0;
+}
+int ref_window_q8_0(const u8* gate, const u8* up, const u8* down, u32 experts, u32 hidden, u32 inter, float limit, const float* x,
+                    u32 rows, const u32* ids, const float* weights, const float* shared, u32 top_k, u32 split, u32 first, u32 end,
+                    float* gate_out, float* up_out, i8* act_codes, float* act_deltas, i32* act_sums, float* raw, float* y) {
+    return ref_window_ds41(8, 8, gate, up, down, experts, hidden, inter, limit, x, rows, ids, weights, shared, top_k, split, first, end, gate_out, up_out,
+                           act_codes, act_deltas, act_sums, raw, y);
 }
 // reference_half_sum (src/ds41_moe.cpp:99-115).
 int ref_half_sum(const u32* ids, u32 rows, u32 top_k, u32 split, const float* weights, const float* raw, u32 hidden, unsigned half, float* out) {

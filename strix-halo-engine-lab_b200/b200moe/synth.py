@@ -14,6 +14,7 @@ Q8_0_BLOCK = 34
 Q4_K_BLOCK = 144
 Q5_K_BLOCK = 176
 Q5_1_BLOCK = 24
+Q2_K_BLOCK = 84
 
 
 def q8_0_blocks(rng, nblocks, scale=0.01):
@@ -39,6 +40,15 @@ def q5_k_blocks(rng, nblocks, scale=0.01 / 64):
     out = rng.integers(0, 256, size=(nblocks, Q5_K_BLOCK), dtype=np.uint8)
     dd = (np.abs(rng.standard_normal((nblocks, 2), dtype=np.float32)) * scale).astype(np.float16)
     out[:, 0:4] = dd.view(np.uint8).reshape(nblocks, 4)
+    return out
+
+
+def q2_k_blocks(rng, nblocks, scale=0.01 / 8):
+    """84-byte super-blocks: 16 bytes of (4-bit scale | 4-bit min << 4), 64 bytes of 2-bit quants, fp16 d, fp16 dmin
+    (d, dmin = fp16(|N(0,1)| * scale)); every byte but the two factors uniform."""
+    out = rng.integers(0, 256, size=(nblocks, Q2_K_BLOCK), dtype=np.uint8)
+    dd = (np.abs(rng.standard_normal((nblocks, 2), dtype=np.float32)) * scale).astype(np.float16)
+    out[:, 80:84] = dd.view(np.uint8).reshape(nblocks, 4)
     return out
 
 
@@ -68,7 +78,7 @@ def pack_q4k_factors(scales, mins):
 
 
 def row_bytes(ggml_type, width):
-    return {7: width // 32 * Q5_1_BLOCK, 8: width // 32 * Q8_0_BLOCK, 13: width // 256 * Q5_K_BLOCK}.get(ggml_type, width // 256 * Q4_K_BLOCK)
+    return {7: width // 32 * Q5_1_BLOCK, 8: width // 32 * Q8_0_BLOCK, 10: width // 256 * Q2_K_BLOCK, 13: width // 256 * Q5_K_BLOCK}.get(ggml_type, width // 256 * Q4_K_BLOCK)
 
 
 def expert_tensors(rng, experts, hidden, inter, gate_type, down_type):
@@ -78,6 +88,8 @@ def expert_tensors(rng, experts, hidden, inter, gate_type, down_type):
             return q8_0_blocks(rng, experts * rows * (width // 32)).reshape(-1)
         if t == 7:
             return q5_1_blocks(rng, experts * rows * (width // 32)).reshape(-1)
+        if t == 10:
+            return q2_k_blocks(rng, experts * rows * (width // 256)).reshape(-1)
         if t == 13:
             return q5_k_blocks(rng, experts * rows * (width // 256)).reshape(-1)
         return q4_k_blocks(rng, experts * rows * (width // 256)).reshape(-1)

@@ -113,14 +113,15 @@ struct Carver {  // caller-owned workspace, 256-byte aligned sections
 };
 
 int check_shape(const b200moe_shape& s) {
-    B200_REQUIRE(s.gate_type == B200MOE_TYPE_Q8_0 || is_kquant(s.gate_type), "gate/up type %u is not bound (Q8_0 = 8, Q4_K = 12, Q5_K = 13)", s.gate_type);
-    B200_REQUIRE(s.down_type == B200MOE_TYPE_Q8_0 || s.down_type == B200MOE_TYPE_Q4_K || s.down_type == B200MOE_TYPE_Q5_1,
-                 "down type %u is not bound (Q5_1 = 7, Q8_0 = 8, Q4_K = 12)", s.down_type);
-    B200_REQUIRE(!(s.gate_type == B200MOE_TYPE_Q8_0 && s.down_type != B200MOE_TYPE_Q8_0), "Q8_0 gate/up with a down type other than Q8_0 has no declared contract");
+    B200_REQUIRE(is_ds41_type(s.gate_type) || is_kquant(s.gate_type), "gate/up type %u is not bound (Q8_0 = 8, Q2_K = 10, Q4_K = 12, Q5_K = 13)", s.gate_type);
+    B200_REQUIRE(is_ds41_type(s.down_type) || s.down_type == B200MOE_TYPE_Q4_K || s.down_type == B200MOE_TYPE_Q5_1,
+                 "down type %u is not bound (Q5_1 = 7, Q8_0 = 8, Q2_K = 10, Q4_K = 12)", s.down_type);
+    B200_REQUIRE(!(is_ds41_type(s.gate_type) && !is_ds41_type(s.down_type)), "Q8_0 / Q2_K gate/up with a down type other than Q8_0 / Q2_K has no declared contract");
+    B200_REQUIRE(!(is_kquant(s.gate_type) && s.down_type == B200MOE_TYPE_Q2_K), "Q2_K down tensors belong to the Q8_0 / Q2_K family");
     B200_REQUIRE(s.hidden && s.inter && s.experts && s.top_k, "shape has a zero dimension");
     B200_REQUIRE(s.experts <= kMaxExperts && s.top_k <= kMaxTopK && s.top_k <= s.experts, "need top_k <= 32, top_k <= experts <= 1024");
-    B200_REQUIRE(s.hidden % (is_kquant(s.gate_type) ? 256u : 32u) == 0, "hidden %u is not a whole number of gate/up blocks", s.hidden);
-    B200_REQUIRE(s.inter % (s.down_type == B200MOE_TYPE_Q4_K ? 256u : 32u) == 0, "inter %u is not a whole number of down blocks", s.inter);
+    B200_REQUIRE(s.hidden % ((is_kquant(s.gate_type) || s.gate_type == B200MOE_TYPE_Q2_K) ? 256u : 32u) == 0, "hidden %u is not a whole number of gate/up blocks", s.hidden);
+    B200_REQUIRE(s.inter % ((s.down_type == B200MOE_TYPE_Q4_K || s.down_type == B200MOE_TYPE_Q2_K) ? 256u : 32u) == 0, "inter %u is not a whole number of down blocks", s.inter);
     B200_REQUIRE(s.hidden % 64 == 0, "hidden %u must be a multiple of 64", s.hidden);
     return B200MOE_OK;
 }
@@ -262,6 +263,7 @@ Q8Form pick_q8_form(bool wide_fits, bool mma_fits, u32 rows) {
     return Q8Form::row_per_warp;
 }
 int enqueue_gate_up(const b200moe_gate_up_view& v, u32 rows, cudaStream_t st, u32 grouped_min_rows = 0) {
+    if (v.shape.gate_type == B200MOE_TYPE_Q2_K) return launch_gate_up_ds41_any(v, st);  // the generic form of the family reads every block type
     if (!is_kquant(v.shape.gate_type)) {
         switch (pick_q8_form(q8_wide_gate_up_fits(v, rows), q8_mma_gate_up_fits(v, rows), rows)) {
             case Q8Form::mma: return launch_gate_up_q8_mma(v, rows, st);
@@ -287,6 +289,7 @@ int enqueue_down(const b200moe_down_view& v, u32 rows, cudaStream_t st, u32 grou
         }
     }
     if (is_kquant(v.shape.gate_type)) return launch_down_q8_chain4(v, st);  // chain4: Q8_0 and Q5_1 blocks
+    if (v.shape.down_type == B200MOE_TYPE_Q2_K) return launch_down_ds41_any(v, st);
     switch (pick_q8_form(q8_wide_down_fits(v, rows), q8_mma_down_fits(v, rows), rows)) {
         case Q8Form::mma: return launch_down_q8_mma(v, rows, st);
         case Q8Form::wide: return launch_down_q8_wide(v, rows, st);

@@ -48,17 +48,20 @@ inline bool aligned(const void* p, std::size_t a) { return (reinterpret_cast<std
         if (!(cond)) return ::b200moe::fail(B200MOE_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
     } while (0)
 
-constexpr u32 kQ8Block = 34, kQ4KBlock = 144, kQ5KBlock = 176, kQ51Block = 24;
+constexpr u32 kQ8Block = 34, kQ4KBlock = 144, kQ5KBlock = 176, kQ51Block = 24, kQ2KBlock = 84;
 inline u64 row_bytes_of(u32 type, u32 width) {
     switch (type) {
         case B200MOE_TYPE_Q8_0: return u64(width / 32) * kQ8Block;
         case B200MOE_TYPE_Q5_1: return u64(width / 32) * kQ51Block;
         case B200MOE_TYPE_Q5_K: return u64(width / 256) * kQ5KBlock;
+        case B200MOE_TYPE_Q2_K: return u64(width / 256) * kQ2KBlock;
         default: return u64(width / 256) * kQ4KBlock;
     }
 }
 // gate / up of the Qwen A8 family (K-quant super-blocks, four-chain pair rule); down types whose term reads the code sums
 inline bool is_kquant(u32 type) { return type == B200MOE_TYPE_Q4_K || type == B200MOE_TYPE_Q5_K; }
+// tensors of the DS41 family (32 lane classes + butterfly, declared_exp SwiGLU with the clamp)
+inline bool is_ds41_type(u32 type) { return type == B200MOE_TYPE_Q8_0 || type == B200MOE_TYPE_Q2_K; }
 inline bool down_reads_sums(u32 type) { return type == B200MOE_TYPE_Q4_K || type == B200MOE_TYPE_Q5_1; }
 
 // ---- device helpers ------------------------------------------------------------------------------------------------

@@ -293,9 +293,9 @@ int b200moe_gguf_find_moe_layer(const void* file, uint32_t layer, b200moe_gguf_m
     B200_REQUIRE(d.dims[0] == g.dims[1] && d.dims[1] == g.dims[0] && d.dims[2] == g.dims[2],
                  "gguf layer %u: down is not [inter, hidden, experts] of gate's [hidden, inter, experts]", layer);
     B200_REQUIRE(r.ggml_type == 0 && r.dims[0] == g.dims[0] && r.dims[1] == g.dims[2], "gguf layer %u: the router must be F32 [hidden, experts]", layer);
-    B200_REQUIRE((g.ggml_type == B200MOE_TYPE_Q8_0 || g.ggml_type == B200MOE_TYPE_Q4_K || g.ggml_type == B200MOE_TYPE_Q5_K) &&
-                     (d.ggml_type == B200MOE_TYPE_Q8_0 || d.ggml_type == B200MOE_TYPE_Q4_K || d.ggml_type == B200MOE_TYPE_Q5_1),
-                 "gguf layer %u: gate / up must be Q8_0, Q4_K or Q5_K and down Q8_0, Q4_K or Q5_1 (types %u / %u)", layer, g.ggml_type, d.ggml_type);
+    B200_REQUIRE((g.ggml_type == B200MOE_TYPE_Q8_0 || g.ggml_type == B200MOE_TYPE_Q2_K || g.ggml_type == B200MOE_TYPE_Q4_K || g.ggml_type == B200MOE_TYPE_Q5_K) &&
+                     (d.ggml_type == B200MOE_TYPE_Q8_0 || d.ggml_type == B200MOE_TYPE_Q2_K || d.ggml_type == B200MOE_TYPE_Q4_K || d.ggml_type == B200MOE_TYPE_Q5_1),
+                 "gguf layer %u: gate / up must be Q8_0, Q2_K, Q4_K or Q5_K and down Q8_0, Q2_K, Q4_K or Q5_1 (types %u / %u)", layer, g.ggml_type, d.ggml_type);
     B200_REQUIRE(g.dims[0] <= 0xffffffffull && g.dims[1] <= 0xffffffffull && g.dims[2] <= 0xffffffffull, "gguf layer %u: a dimension exceeds 32 bits", layer);
     out->shape.hidden = static_cast<u32>(g.dims[0]);
     out->shape.inter = static_cast<u32>(g.dims[1]);

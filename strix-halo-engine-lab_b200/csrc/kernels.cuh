@@ -35,6 +35,9 @@ int launch_down_q8(const b200moe_down_view& v, cudaStream_t stream);
 // gemv_q4k.cu: Q4_K x A8 rows in the four-chain contract (routed Qwen-family experts; Q8_0 four-chain down)
 int launch_gate_up_q4k(const b200moe_gate_up_view& v, cudaStream_t stream);
 int launch_down_q4k(const b200moe_down_view& v, cudaStream_t stream);
+// gemv_ds41_any.cu: the DS41 family over any of its block types (Q8_0, Q2_K), one weight row per warp, weights read in place.
+int launch_gate_up_ds41_any(const b200moe_gate_up_view& v, cudaStream_t stream);
+int launch_down_ds41_any(const b200moe_down_view& v, cudaStream_t stream);
 int launch_down_q8_chain4(const b200moe_down_view& v, cudaStream_t stream);
 
 // gemv_q4k_stream.cu: the same Q4_K contracts as persistent kernels fed by bulk copies (decode windows up to 64 rows)

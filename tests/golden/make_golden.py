@@ -111,6 +111,17 @@ def format_vectors():
         assert not status.any()
         t = f"{gt}_{dt}"
         out.update({f"gate_{t}": g, f"up_{t}": u, f"down_{t}": d, f"x_{t}": x, f"ids_{t}": ids, f"raw_{t}": raw})
+    # Q2_K tensors of the DS41 family, alone and mixed with Q8_0 (reference_window, limit 7)
+    H2, I2 = 512, 256
+    out["shape_q2k"] = np.array([E, H2, I2, K])
+    for gt, dt in ((10, 10), (10, 8), (8, 10)):
+        g, u, d = synth.expert_tensors(rng, E, H2, I2, gt, dt)
+        x = rng.standard_normal((rows, H2), dtype=np.float32)
+        ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+        wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
+        win = ref.window_ds41(gt, dt, g, u, d, E, H2, I2, 7.0, x, ids, wts, None, split=E // 2)
+        t = f"{gt}_{dt}"
+        out.update({f"gate_{t}": g, f"up_{t}": u, f"down_{t}": d, f"x_{t}": x, f"ids_{t}": ids, f"raw_{t}": win["raw"], f"act_codes_{t}": win["act_codes"]})
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "formats_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -82,6 +82,11 @@ def test_argument_errors_come_first(lib):
     grouped = b200moe.RoutePolicy(1, 1, 0, 0, 256, 8, 8, 9, 1, 1, 1e-20, 1.0)  # topk_group > n_group
     r = b200moe.RouterView(policy=grouped, logits=1, ids=1, weights=1, bias=1)
     assert lib.b200moe_router(r, None) == b200moe.ERR_INVALID_ARGUMENT
+    for gt, dt in ((12, 10), (10, 12), (10, 7)):            # Q2_K belongs to the Q8_0 / Q2_K family on both sides
+        assert lib.b200moe_layer_workspace_bytes(b200moe.Shape(2048, 1024, 8, 2, gt, dt, float("inf")), 4) == 0
+    q2 = b200moe.Shape(2048, 1024, 8, 2, 10, 10, float("inf"))
+    assert lib.b200moe_layer_workspace_bytes(q2, 4) > 0 and lib.b200moe_gate_row_bytes(q2) == 8 * 84 and lib.b200moe_down_row_bytes(q2) == 4 * 84
+    assert lib.b200moe_layer_workspace_bytes(b200moe.Shape(2048 + 32, 1024, 8, 2, 10, 8, float("inf")), 4) == 0   # hidden not in super-blocks
     ok = b200moe.Shape(2048, 768, 128, 8, 12, 12, float("inf"))
     assert lib.b200moe_gate_row_bytes(ok) == 8 * 144 and lib.b200moe_down_row_bytes(ok) == 3 * 144
     assert lib.b200moe_expert_bytes(ok) == 2654208  # config 2's bytes per expert

@@ -476,6 +476,24 @@ def test_experts_q8_0_ds41_family(gpu, oracle):
                 b200moe.debug_set(b200moe.DEBUG_DECODE_FORM, b200moe.FORM_AUTO)
 
 
+def test_experts_q2_k_ds41_family(gpu, oracle):
+    """Q2_K tensors of the DS41 family (84-byte super-blocks, product_q2_k), alone and mixed with Q8_0, through the
+    family's generic form: every stage bit for bit, with restricted expert ranges and experts of more than eight entries."""
+    import b200moe
+    from b200moe import synth
+    rng = np.random.default_rng(17)
+    for E, H, I, K, rows, limit in ((6, 512, 256, 2, 5, 7.0), (4, 2048, 1024, 2, 19, math.inf)):
+        x = rng.standard_normal((rows, H), dtype=np.float32)
+        ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+        wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
+        shared = rng.standard_normal((rows, H), dtype=np.float32)
+        for gt, dt in ((10, 10), (10, 8), (8, 10)):
+            gate, up, down = synth.expert_tensors(rng, E, H, I, gt, dt)
+            sh, osh = shape_pair(H, I, E, K, gt, dt, limit)
+            run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_PARTS, shared=shared)
+            run_stages(gpu, oracle, sh, osh, gate, up, down, x, ids, wts, b200moe.COMBINE_PARTS, first=E // 4, end=E // 2 + 1)
+
+
 def test_experts_q4k_qwen_family(gpu, oracle):
     """Config-2 family (Q4_K gate/up, Q4_K or Q8_0 down, gfx1151-exp SwiGLU, fma merge)."""
     import b200moe

@@ -332,6 +332,27 @@ def test_window_q8_0_vs_reference(oracle, ref):
     assert same(got["raw"][own], part["raw"][own])
 
 
+def test_window_q2_k_vs_reference(oracle, ref):
+    """The family's Q2_K tensors (product_q2_k, src/ds41_formats.cpp:198-218) alone and mixed with Q8_0: the oracle's
+    window equals reference_window bit for bit in every intermediate."""
+    rng = np.random.default_rng(19)
+    E, H, I, K, rows = 6, 512, 256, 2, 4
+    x = rng.standard_normal((rows, H), dtype=np.float32)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(rows)]).astype(np.uint32)
+    wts = rng.uniform(0.05, 0.6, size=(rows, K)).astype(np.float32)
+    shared = rng.standard_normal((rows, H), dtype=np.float32)
+    codes, deltas, sums = oracle.quantize_a8(x)
+    for gt, dt in ((10, 10), (10, 8), (8, 10)):
+        gate, up, down = synth.expert_tensors(rng, E, H, I, gt, dt)
+        want = ref.window_ds41(gt, dt, gate, up, down, E, H, I, 7.0, x, ids, wts, shared, split=E // 2)
+        got = oracle.experts(L.Shape(H, I, E, K, gt, dt, 7.0), gate, up, down, ids, codes, deltas, sums, taps=True)
+        for k in ("gate", "up", "raw", "act_deltas"):
+            assert same(got[k], want[k]), (gt, dt, k)
+        assert np.array_equal(got["act_codes"], want["act_codes"]) and np.array_equal(got["act_sums"], want["act_sums"])
+        y = oracle.combine(L.COMBINE_PARTS, got["raw"], wts, ids, shared=shared, parts=2, part_experts=E // 2)
+        assert same(y, want["y"])
+
+
 def test_qwen_experts_vs_reference(oracle, ref):
     """Qwen-family job (reference_run and the threaded Executor, src/cpu/core/routed_expert.cpp:264-489): Q4_K
     gate/up, gfx1151 exp SwiGLU, A8 of h, Q8_0 four-chain down."""
@@ -441,3 +462,10 @@ def test_other_formats_golden_vectors(oracle):
         c, dl, s = oracle.quantize_a8(g[f"x_{t}"])
         ex = oracle.experts(L.Shape(H, I, E, K, gt, dt, np.inf), g[f"gate_{t}"], g[f"up_{t}"], g[f"down_{t}"], g[f"ids_{t}"], c, dl, s)
         assert same(ex["raw"], g[f"raw_{t}"])
+    # Q2_K tensors of the DS41 family (reference_window outputs)
+    E, H, I, K = (int(v) for v in g["shape_q2k"])
+    for gt, dt in ((10, 10), (10, 8), (8, 10)):
+        t = f"{gt}_{dt}"
+        c, dl, s = oracle.quantize_a8(g[f"x_{t}"])
+        ex = oracle.experts(L.Shape(H, I, E, K, gt, dt, 7.0), g[f"gate_{t}"], g[f"up_{t}"], g[f"down_{t}"], g[f"ids_{t}"], c, dl, s, taps=True)
+        assert same(ex["raw"], g[f"raw_{t}"]) and np.array_equal(ex["act_codes"], g[f"act_codes_{t}"])
