@@ -319,6 +319,41 @@ def lib():
         L.b200moe_select_owner_slots.argtypes = [vp, u64, u32, u32, vp, u32, u32, vp, vp]
         L.b200moe_canonical_sum.restype = C.c_int
         L.b200moe_canonical_sum.argtypes = [vp, vp, vp, u64, vp, vp]
+        # every pointer / handle argument is declared: an undeclared Python int would travel as a 32-bit C int
+        L.b200moe_registry.restype = u32
+        L.b200moe_registry.argtypes = [C.POINTER(C.POINTER(Registration))]
+        L.b200moe_enqueue.restype = C.c_int
+        L.b200moe_enqueue.argtypes = [C.POINTER(KernelArguments), vp]
+        L.b200moe_merge_first_error.restype = C.c_int
+        L.b200moe_merge_first_error.argtypes = [vp, vp, u32, vp]
+        L.b200moe_check_first_error.restype = C.c_int
+        L.b200moe_check_first_error.argtypes = [C.POINTER(FirstError)]
+        L.b200moe_planner_create.restype = C.c_int
+        L.b200moe_planner_create.argtypes = [C.POINTER(PlannerDesc), C.POINTER(vp)]
+        L.b200moe_planner_destroy.restype = None
+        L.b200moe_planner_destroy.argtypes = [vp]
+        L.b200moe_planner_seed.restype = C.c_int
+        L.b200moe_planner_seed.argtypes = [vp, u32, vp]
+        L.b200moe_planner_observe.restype = C.c_int
+        L.b200moe_planner_observe.argtypes = [vp, u32, vp, u32]
+        for n in ("b200moe_planner_end_step", "b200moe_planner_fill_from_seed"):
+            getattr(L, n).restype = C.c_int
+            getattr(L, n).argtypes = [vp]
+        L.b200moe_planner_plan.restype = C.c_int
+        L.b200moe_planner_plan.argtypes = [vp, C.POINTER(Move), u32, C.POINTER(u32)]
+        L.b200moe_planner_commit.restype = C.c_int
+        L.b200moe_planner_commit.argtypes = [vp, C.POINTER(Move)]
+        for n in ("b200moe_planner_table", "b200moe_planner_scores"):
+            getattr(L, n).restype = C.c_int
+            getattr(L, n).argtypes = [vp, u32, vp]
+        L.b200moe_planner_get_receipt.restype = C.c_int
+        L.b200moe_planner_get_receipt.argtypes = [vp, C.POINTER(PlannerReceipt)]
+        L.b200moe_residency_promote.restype = C.c_int
+        L.b200moe_residency_promote.argtypes = [vp, C.POINTER(Move), u32, vp]
+        L.b200moe_abi_version.restype = C.c_int
+        L.b200moe_abi_version.argtypes = []
+        L.b200moe_last_error.argtypes = []
+        L.b200moe_launch_count.argtypes = []
         _lib = L
     return _lib
 

@@ -30,6 +30,8 @@ def test_exports_match_header(lib):
     assert declared == set(b200moe.EXPORTS), declared ^ set(b200moe.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
+        # ctypes sends an undeclared Python int as a 32-bit C int: every export declares its arguments
+        assert getattr(lib, name).argtypes is not None, f"{name}: argtypes not declared in b200moe/__init__.py"
     assert lib.b200moe_abi_version() == b200moe.ABI_VERSION == header_abi_version()
 
 
