@@ -645,15 +645,8 @@ int b200moe_dense_ffn(const b200moe_dense_view* v, void* stream) {
         return fail(B200MOE_ERR_WORKSPACE, "dense_ffn: workspace of %llu bytes needed, %llu given", (unsigned long long)L.bytes, (unsigned long long)v->workspace_bytes);
     if (!device_ready()) return B200MOE_ERR_CUDA;
     cudaStream_t st = as_stream(stream);
-    // every row is one entry of the single expert: ids = 0, so slot = row
-    cudaError_t ce = cudaMemsetAsync(L.aux, 0, sizeof(u32) * v->rows, st);
-    if (ce == cudaSuccess) ce = cudaMemsetAsync(L.summary, 0, 16, st);
-    if (ce == cudaSuccess) ce = cudaMemsetAsync(L.row_status, 0, sizeof(u32) * v->rows, st);
-    if (ce != cudaSuccess) return fail(B200MOE_ERR_CUDA, "dense_ffn: cudaMemsetAsync: %s", cudaGetErrorString(ce));
-    b200moe_routes_view rv{};
-    rv.ids = L.aux; rv.rows = v->rows; rv.top_k = 1; rv.experts = 1; rv.split = 1;
-    rv.scratch = L.routes_scratch; rv.row_status = L.row_status; rv.out = L.routes;
-    if (int rc = launch_routes(rv, st)) return rc;
+    // every row is one entry of the single expert (slot = row): the routes are written directly, the status words with them
+    if (int rc = launch_dense_routes(L.routes, v->rows, L.row_status, L.summary, st)) return rc;
     b200moe_gate_up_view gu{};
     gu.shape = s; gu.weights = v->weights; gu.routes = L.routes; gu.max_union = 1; gu.x = v->x; gu.act = L.act;
     gu.row_status = L.row_status; gu.summary = L.summary;

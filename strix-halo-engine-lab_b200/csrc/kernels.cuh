@@ -19,6 +19,7 @@ int launch_router_select(const b200moe_router_view& v, cudaStream_t stream);
 // routes.cu
 u64 routes_scratch_words(u32 rows, u32 top_k, u32 experts);
 int launch_routes(const b200moe_routes_view& v, cudaStream_t stream);
+int launch_dense_routes(const b200moe_routes& out, u32 rows, u32* row_status, u32* summary4, cudaStream_t stream);
 // grouped (token-block) form of the Q4_K experts on the tensor cores (grouped_q4k.cu)
 bool grouped_fits(const b200moe_shape& s, bool have_sums);
 int launch_gate_up_q4k_grouped(const b200moe_gate_up_view& v, cudaStream_t stream);

@@ -82,6 +82,28 @@ __global__ void __launch_bounds__(1024) routes_fill_kernel(b200moe_routes_view v
     v.out.slots[pos] = s;
 }
 
+
+// The routes of a dense block (one expert, top-1: every row is one entry of expert 0, slot = row) written directly, with
+// the job's status words cleared in the same launch: what build_window_routes (src/ds41_moe.cpp:11-43) gives for ids = 0,
+// without the sort and without the memsets in front of it.
+__global__ void __launch_bounds__(256) dense_routes_kernel(b200moe_routes out, u32 rows, u32* row_status, u32* summary4) {
+    const u32 i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < rows) {
+        out.rows[i] = i;
+        out.slots[i] = i;
+        if (out.order) out.order[i] = i;
+        if (out.low_counts) out.low_counts[i] = 1u;  // id 0 < split 1
+        if (row_status) row_status[i] = 0u;
+    }
+    if (i == 0) {
+        out.experts[0] = 0u;
+        out.begins[0] = 0u;
+        out.begins[1] = rows;
+        out.counts[0] = 1u; out.counts[1] = rows; out.counts[2] = rows; out.counts[3] = 0u;
+        if (summary4) { summary4[0] = 0u; summary4[1] = 0u; summary4[2] = 0u; summary4[3] = 0u; }
+    }
+}
+
 }  // namespace
 
 u64 routes_scratch_words(u32 rows, u32 top_k, u32 experts) {
@@ -98,6 +120,11 @@ int launch_select_routes(const b200moe_router_view& r, const b200moe_routes_view
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(select_routes_small_kernel), smem)) return rc;
     select_routes_small_kernel<<<1, 1024, smem, stream>>>(r.logits, r.scores, r.bias, r.policy, r.rows, r.ids, r.weights, v, v.end ? v.end : v.experts);
     return after_launch("select_routes_small");
+}
+
+int launch_dense_routes(const b200moe_routes& out, u32 rows, u32* row_status, u32* summary4, cudaStream_t stream) {
+    dense_routes_kernel<<<(rows + 255) / 256, 256, 0, stream>>>(out, rows, row_status, summary4);
+    return after_launch("dense_routes");
 }
 
 int launch_routes(const b200moe_routes_view& v, cudaStream_t stream) {
