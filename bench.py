@@ -445,9 +445,14 @@ def gate_up_kernel_name(cfg, rows, form):
     return "gate_up_q4k_stream_kernel" if stream else "q4k_wide_kernel<gate/up>"
 
 
+def c4_phase(batch):
+    """Windows of 128 rows and more are token blocks (the routed experts then take the grouped tensor-core form)."""
+    return "prefill" if batch >= 128 else "decode"
+
+
 def c4_config(cfg, batch, world):
     """The `config` object both arms print (the driver compares them key by key)."""
-    return {"workload": f"c4: {cfg['desc']}, decode, global batch {batch}",
+    return {"workload": f"c4: {cfg['desc']}, {c4_phase(batch)}, global batch {batch}",
             "parallelism": f"ep x{world} ({cfg['experts'] // world} experts and {batch // world} home rows per rank)" if world > 1 else "1 gpu (all 256 experts)",
             "l2": "5.5 GB of distinct routed expert weights per step (far beyond the 126 MB L2)"}
 
@@ -767,14 +772,16 @@ def large_arm(args, cfg, rank, world, dev):
     peak, peak_kind = peaks()
     achieved = float(allr[slow, 3])
     line = {
-        "metric": METRIC, "value": tokens / (dev_ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "metric": METRIC.replace("decode", c4_phase(B)), "value": tokens / (dev_ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": dev_ms / (K * reps), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8xint4->int32, fp32 chains", "data": "synthetic", "config": c4_config(cfg, B, world),
         "clocks": sampler.summary(),
         "e2e": {"value": B * K / (host_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
                 "ms_per_step": host_ms / K},
         "gpu_launches": int(round(launches_per_step * K)),
-        "roofline": {"kernel": "q4k_wide_kernel<gate/up> (routed experts, segment-streaming GEMV)", "bound": "hbm", "achieved": achieved, "peak": peak,
+        "roofline": {"kernel": "q4k_wide_kernel<gate/up> (routed experts, segment-streaming GEMV)" if B < 128 else
+                               "grouped_q4k_kernel<gate/up> (routed experts over a token block, tcgen05; quoted against HBM on its distinct-expert bytes)",
+                     "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy", "frac_of_nominal_8tbs": achieved / 8000.0,
                      "traffic": float(allr[slow, 4]) * C4_TRAFFIC_RATIO,
                      "traffic_note": "scaled by distinct experts from the ncu capture of a reduced layer (x 1.03 algorithmic): profiles/wide_kernels_c4_decode.md",
