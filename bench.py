@@ -566,7 +566,14 @@ def c4_cpu_arm(model, x, target_s):
     what = (f"{reps} x {x.shape[0]} tokens of one step ({sec:.1f} s): reference row kernels (isa {ref.isa()}) for the routed experts on the sample's routes + "
             "reference gemv_q8_0_a8 for the shared expert, own threaded driver with a kept pool; group-limited router from the CPU oracle "
             "(the reference has none)") if have_ref else f"{reps} x {x.shape[0]} tokens of one step through the CPU oracle port ({sec:.1f} s)"
-    return value, {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": what}
+    base = {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": what}
+    if have_ref:
+        # what the arm streamed per second (the sample's distinct experts + the shared expert, once per repetition) beside the
+        # host's pure-read ceiling over the same tensors
+        streamed = (g.nbytes + u.nbytes + d.nbytes + sum(a.nbytes for a in model.shared)) * reps
+        base["weights_gbs"] = streamed / sec / 1e9
+        base["host_read_gbs"] = ref.host_read_gbs(g, threads)
+    return value, base
 
 
 def c4_reference_arm(args, cfg, rank, world):

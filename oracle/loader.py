@@ -483,6 +483,15 @@ class Ref:
         keys = ("active_bytes", "hit_bytes", "promoted_bytes", "promotions", "evictions", "steps")
         return per_step, tables, dict(zip(keys, (int(v) for v in receipt)))
 
+    def host_read_gbs(self, data, threads, reps=3):
+        """Read bandwidth of the host over `data` (a uint8 array far larger than the caches) with `threads` threads, GB/s."""
+        data = np.ascontiguousarray(data, np.uint8).reshape(-1)
+        self.lib.ref_time_read.restype = C.c_double
+        self.lib.ref_time_read.argtypes = [C.c_void_p, C.c_size_t, C.c_uint, C.c_uint32, C.c_void_p]
+        self.lib.ref_time_read(data.ctypes.data, data.size, threads, 1, None)          # warm the pool and the pages
+        sec = self.lib.ref_time_read(data.ctypes.data, data.size, threads, reps, None)
+        return data.size * reps / sec / 1e9
+
     def isa(self):
         """Row-kernel table of the routed-expert executor on this host."""
         return self.lib.ref_expert_isa().decode()

@@ -558,4 +558,24 @@ double ref_time_gemv_q8_0_a8(const u8* weight, u32 row_bytes, u32 width, u32 cou
     return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
 }
 
+// Pure read of `bytes` bytes with all host threads (64-bit sums over 1 MiB pieces), `reps` times: the host's read-bandwidth
+// ceiling that the timed CPU arm is quoted beside (the reference's own bench prints the same figure first,
+// scripts/bench/residency/cpu_expert_bench.cpp:168-177). Returns seconds; *sink receives the sum so the reads are kept.
+double ref_time_read(const u8* buf, std::size_t bytes, unsigned threads, u32 reps, std::uint64_t* sink) {
+    Pool& pool = pool_of(threads);
+    const std::size_t piece = std::size_t(1) << 20, pieces = (bytes + piece - 1) / piece;
+    std::atomic<std::uint64_t> total{0};
+    const auto t0 = std::chrono::steady_clock::now();
+    for (u32 rep = 0; rep < reps; ++rep)
+        pool.run(static_cast<u32>(pieces), [&](u32 item) {
+            const std::size_t b = item * piece, e = std::min(bytes, b + piece);
+            std::uint64_t s = 0;
+            for (std::size_t i = b; i + 8 <= e; i += 8) { std::uint64_t v; std::memcpy(&v, buf + i, 8); s += v; }
+            total.fetch_add(s, std::memory_order_relaxed);
+        });
+    const double sec = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if (sink) *sink = total.load();
+    return sec;
+}
+
 }  // extern "C"
